@@ -1,0 +1,96 @@
+/*
+ * intent_b200 - C ABI of the sm_100a quantized-contraction library.
+ *
+ * Calling convention (every entry point):
+ *   - Slot order follows the reference's native ABI for CPU providers
+ *     (lib/Serialization/NativeABI.cpp:77-99, python/intent/runtime/native.py:56-120):
+ *     for each public parameter in declaration order a view contributes
+ *     `void* aP`, then one int64 extent per axis (`aP_dA`), then one int64
+ *     ELEMENT stride per axis (`aP_sA`); a scalar contributes one slot.
+ *   - Two things are added to that convention: the compile-time constants of
+ *     the program (group size, zero point, ...) follow the parameters as int32
+ *     slots, then a trailing `void* stream` (a cudaStream_t; NULL = the legacy
+ *     default stream), and every entry returns an `int` status instead of void.
+ *   - All pointers are DEVICE pointers, borrowed for the duration of the call.
+ *     The library never frees or retains them.  Launches are asynchronous on
+ *     `stream`; no entry synchronises the device or allocates device memory.
+ *   - No exceptions, no exit(), no device traps.  Status 0 is success.
+ */
+#ifndef INTENT_B200_H
+#define INTENT_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define INTENT_B200_API __attribute__((visibility("default")))
+#else
+#define INTENT_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum intent_b200_status {
+  INTENT_B200_OK = 0,
+  INTENT_B200_ERR_SHAPE = 1,        /* extents disagree with each other or with a constant */
+  INTENT_B200_ERR_LAYOUT = 2,       /* strides are not the canonical contiguous ones / pointer misaligned */
+  INTENT_B200_ERR_UNSUPPORTED = 3,  /* legal program, but no kernel specialisation covers it */
+  INTENT_B200_ERR_TIMEOUT = 4,      /* a bounded device-side wait gave up (read back from the status word) */
+  INTENT_B200_ERR_WORKSPACE = 5,    /* workspace missing or too small */
+  INTENT_B200_ERR_NULL = 6,         /* a required pointer is NULL */
+  INTENT_B200_ERR_CUDA = 1000       /* 1000 + cudaError_t of a failed runtime call */
+};
+
+#define INTENT_B200_VIEW1(p) void* p, int64_t p##_d0, int64_t p##_s0
+#define INTENT_B200_VIEW2(p) void* p, int64_t p##_d0, int64_t p##_d1, int64_t p##_s0, int64_t p##_s1
+#define INTENT_B200_VIEW3(p) void* p, int64_t p##_d0, int64_t p##_d1, int64_t p##_d2, \
+                             int64_t p##_s0, int64_t p##_s1, int64_t p##_s2
+
+/* Library identity: returns a static string "intent_b200 <version> sm_100a". */
+INTENT_B200_API const char* intent_b200_version(void);
+/* Human-readable name of a status code (static string). */
+INTENT_B200_API const char* intent_b200_status_string(int status);
+/* Number of kernels this library has launched in the calling process (all
+ * entries, all streams).  Used by the benchmark to report its launch count. */
+INTENT_B200_API int64_t intent_b200_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * weight_only_int4_matmul  (W4A16)
+ * Replaces the provider lowering of
+ *   examples/kernels/contraction/weight_only_int4.py:18-51
+ *   (torch-CPU reference experiments/cpu/baselines/pytorch/cpu_runtime.py:97-102).
+ *   a0 activation   [M, K]   f16 | bf16, row-major contiguous
+ *   a1 packed       [K/8, N] i32, N contiguous; nibble j of a word = k%8 == j
+ *   a2 scales       [K/G, N] same dtype as the activation
+ *   a3 output       [M, N]   same dtype as the activation
+ *   group_size G: 32-multiple dividing K (reference constant 64; benchmark 128)
+ *   zero_point: -1 = two's-complement nibble (the reference's decoding),
+ *                8 = unsigned nibble minus 8 (benchmark configurations)
+ * Y[m,n] = T( sum_k f32(X[m,k]) * f32(w[k,n]) ), f32 accumulation.
+ * The plain entries pick the kernel from M (skinny bandwidth kernel for
+ * M <= 32, tcgen05 tensor-core kernel above); the _gemv / _gemm entries force
+ * one of the two.
+ * ------------------------------------------------------------------------ */
+INTENT_B200_API int intent_b200_weight_only_int4_matmul_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                            INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                            int32_t group_size, int32_t zero_point, void* stream);
+INTENT_B200_API int intent_b200_weight_only_int4_matmul_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                             INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                             int32_t group_size, int32_t zero_point, void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemv_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                               INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                               int32_t group_size, int32_t zero_point, void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemv_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                int32_t group_size, int32_t zero_point, void* stream);
+/* Launch-shape override of the skinny kernel for measurement sweeps:
+ * warps along N per CTA (1|2|4), warps along K (1..8), K-split = cluster size
+ * (1|2|4|8).  0 restores the built-in choice for that field.  Process-global,
+ * not thread-safe against concurrent launches. */
+INTENT_B200_API int intent_b200_w4a16_gemv_configure(int32_t warps_n, int32_t warps_k, int32_t split_k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INTENT_B200_H */

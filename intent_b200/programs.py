@@ -1,0 +1,82 @@
+"""The shipped programs (kernel definitions).
+
+Each definition carries the reference program's name and parameter order, so
+code written against the reference's examples binds the same way:
+
+    artifact = intent_b200.compile(programs.weight_only_int4_matmul,
+                                   target=B200Target(device=0),
+                                   constexprs={"GROUP_SIZE": 128, "ZERO_POINT": 8})
+    y = artifact.run(x, packed, scales)
+"""
+from __future__ import annotations
+
+from . import dtypes
+from .compiler import KernelDefinition
+from .errors import CompilationStageError
+from .runtime.artifact import NativeProgram
+from .runtime.interface import PublicInterface, ScalarParameter, ViewKind, ViewParameter
+
+IN, OUT, INOUT = ViewKind.IN, ViewKind.OUT, ViewKind.INOUT
+
+
+def _act_dtype(constants, name="ACT_DTYPE"):
+    element = dtypes.dtype(constants[name])
+    if element not in (dtypes.f16, dtypes.bf16):
+        raise CompilationStageError("provider_native_compilation",
+                                    f"{name} must be f16 or bf16, got {element}")
+    return element
+
+
+def _rule(condition, message):
+    def check(d):
+        if not condition(d):
+            raise ValueError(message(d) if callable(message) else message)
+    return check
+
+
+# ---------------------------------------------------------------------------------
+# weight_only_int4_matmul (W4A16)
+# ---------------------------------------------------------------------------------
+def _lower_w4a16(constants, device):
+    act = _act_dtype(constants)
+    group = int(constants["GROUP_SIZE"])
+    if group not in (32, 64, 128):
+        raise CompilationStageError("provider_native_compilation",
+                                    f"GROUP_SIZE {group} has no kernel specialisation (32, 64, 128)")
+    zero_point = constants["ZERO_POINT"]
+    if zero_point in ("twos_complement", None, -1):
+        zp = -1
+    elif zero_point == 8:
+        zp = 8
+    else:
+        raise CompilationStageError("provider_native_compilation",
+                                    "ZERO_POINT must be 'twos_complement' or 8")
+    kernel = constants["KERNEL"]
+    stem = {"auto": "weight_only_int4_matmul", "gemv": "w4a16_gemv", "gemm": "w4a16_gemm"}.get(kernel)
+    if stem is None:
+        raise CompilationStageError("frontend_kir", "KERNEL must be 'auto', 'gemv' or 'gemm'")
+    interface = PublicInterface((
+        ViewParameter(0, "activation", act, ("M", "K"), IN),
+        ViewParameter(1, "packed_weight", dtypes.i32, ("P", "N"), IN),
+        ViewParameter(2, "scales", act, ("G", "N"), IN),
+        ViewParameter(3, "output", act, ("M", "N"), OUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["P"] * 8 == d["K"],
+              lambda d: f"packed_weight.shape[0] must be K/8 = {d['K'] // 8}, got {d['P']}"),
+        _rule(lambda d: d["K"] % group == 0 and d["G"] * group == d["K"],
+              lambda d: f"scales.shape[0] must be K/GROUP_SIZE with K a multiple of {group}"),
+    ))
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
+                         constants=(group, zp), device=device,
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+weight_only_int4_matmul = KernelDefinition(
+    name="weight_only_int4_matmul",
+    constexprs={"GROUP_SIZE": 64, "ZERO_POINT": "twos_complement", "ACT_DTYPE": "f16", "KERNEL": "auto"},
+    lower=_lower_w4a16,
+    reference="examples/kernels/contraction/weight_only_int4.py:18-51",
+    summary="Y = X @ dequant(int4 packed along K, per-group scales); f32 accumulation",
+)
+
+ALL = {d.name: d for d in (weight_only_int4_matmul,)}

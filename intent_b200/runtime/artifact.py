@@ -1,0 +1,265 @@
+"""The callable artifact: same call surface as the reference's
+``CompiledArtifact`` / ``PreparedCall`` (python/intent/runtime/artifact.py:22-53,
+98-237; GPU program python/intent/runtime/gpu/program.py:33-131).
+
+  artifact.run(*inputs)            allocate Out buffers, launch, return None / Out / tuple
+  artifact(*all) / .launch(*all)   every parameter supplied, returns None
+  artifact.prepare(*inputs, outputs=...) -> PreparedCall(.compile/.launch/.result)
+  artifact.as_torch_op("ns::name") -> torch.library.CustomOpDef
+
+Launches are asynchronous on torch's current CUDA stream of the artifact's
+device.  ``PreparedCall.launch`` neither allocates nor synchronises, so it can
+be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+from ..errors import CompilationStageError
+from . import native
+from .interface import BoundArguments, PublicInterface, ScalarParameter, ViewParameter
+
+
+@dataclass(frozen=True, slots=True)
+class NativeObservation:
+    """Facts about the latest invocation of an entry (never an estimate)."""
+
+    provider: str
+    entry: str
+    stage: str
+    constants: tuple
+    arguments: tuple          # per view: (name, shape, strides)
+    workspace_bytes: int
+    status: int
+
+
+class PreparedCall:
+    """Arguments bound to one C entry; ``launch`` replays the same call."""
+
+    def __init__(self, program: "NativeProgram", bound: BoundArguments) -> None:
+        self.program = program
+        self.invocation = bound
+        self._workspace = program.allocate_workspace(bound)
+        self._slots = program.marshal(bound, self._workspace)
+        self._observation: NativeObservation | None = None
+        self._skip = program.is_empty(bound)
+
+    @property
+    def outputs(self) -> tuple:
+        return self.invocation.outputs
+
+    def result(self):
+        return self.invocation.result()
+
+    @property
+    def observation(self) -> NativeObservation | None:
+        return self._observation
+
+    def inspect_configurations(self):
+        raise NotImplementedError("this provider does not export structured tuning configurations")
+
+    def compile(self) -> None:
+        """Nothing is compiled at run time; this resolves the exported symbol."""
+        self.program.function()
+
+    def launch(self) -> None:
+        import torch
+
+        program = self.program
+        if self._skip:
+            return
+        if torch.cuda.current_device() != program.device:
+            with torch.cuda.device(program.device):
+                self._invoke()
+        else:
+            self._invoke()
+
+    __call__ = launch
+
+    def _invoke(self) -> None:
+        import torch
+
+        program = self.program
+        stream = torch.cuda.current_stream(program.device).cuda_stream
+        status = program.function()(*self._slots, ctypes.c_void_p(stream))
+        observation = NativeObservation(
+            "b200", program.entry_name, "launched" if status == 0 else "failed", program.constants,
+            tuple((p.name, f.shape, f.strides) for p, f in zip(program.interface.parameters, self.invocation.views)
+                  if f is not None),
+            sum(w.numel() * w.element_size() for w in self._workspace), int(status))
+        self._observation = observation
+        program._observation = observation
+        native.check(status, program.entry_name, observation)
+
+
+class NativeProgram:
+    """Provider runtime of one program specialisation bound to one device."""
+
+    def __init__(self, *, interface: PublicInterface, entry_name: str, constants: tuple = (),
+                 device: int, workspace=None, empty=None, scalar_carriers=None) -> None:
+        self.interface = interface
+        self.entry_name = entry_name
+        self.constants = tuple(int(c) for c in constants)
+        self.device = device
+        self._workspace_spec = workspace     # callable(dimensions) -> tuple[(shape, torch dtype)]
+        self._empty = empty                  # callable(dimensions) -> bool
+        self._observation: NativeObservation | None = None
+        carriers = []
+        for parameter in interface.parameters:
+            if isinstance(parameter, ViewParameter):
+                rank = len(parameter.shape)
+                carriers += ["ptr"] + ["i64"] * (2 * rank)
+            else:
+                carriers.append((scalar_carriers or {}).get(parameter.name) or _scalar_carrier(parameter))
+        carriers += ["i32"] * len(self.constants)
+        self._carriers_head = tuple(carriers)
+        self._function = None
+        self._workspace_count = None
+
+    # ---- C entry -----------------------------------------------------------------
+    def function(self, workspace_count: int | None = None):
+        if workspace_count is None:
+            workspace_count = self._workspace_count or 0
+        if self._function is None or self._workspace_count != workspace_count:
+            carriers = self._carriers_head + ("ptr", "i64") * workspace_count
+            self._function = native.entry(self.entry_name, carriers)
+            self._workspace_count = workspace_count
+        return self._function
+
+    @property
+    def observation(self):
+        return self._observation
+
+    @property
+    def _torch_device(self):
+        import torch
+
+        return torch.device("cuda", self.device)
+
+    def is_empty(self, bound: BoundArguments) -> bool:
+        return bool(self._empty(bound.dimensions)) if self._empty is not None else False
+
+    def allocate_workspace(self, bound: BoundArguments) -> tuple:
+        import torch
+
+        if self._workspace_spec is None:
+            return ()
+        return tuple(torch.empty(shape, dtype=dtype, device=self._torch_device)
+                     for shape, dtype in self._workspace_spec(bound.dimensions))
+
+    def marshal(self, bound: BoundArguments, workspace: tuple) -> tuple:
+        slots = []
+        for parameter, value, facts in zip(self.interface.parameters, bound.arguments, bound.views):
+            if isinstance(parameter, ViewParameter):
+                slots.append(ctypes.c_void_p(facts.pointer))
+                slots += [ctypes.c_int64(int(e)) for e in facts.shape]
+                slots += [ctypes.c_int64(int(s)) for s in facts.strides]
+            else:
+                slots.append(value)
+        slots += [ctypes.c_int32(c) for c in self.constants]
+        for buffer in workspace:
+            slots.append(ctypes.c_void_p(buffer.data_ptr()))
+            slots.append(ctypes.c_int64(buffer.numel() * buffer.element_size()))
+        self.function(len(workspace))
+        return tuple(slots)
+
+    # ---- call modes ----------------------------------------------------------------
+    def prepare(self, *arguments, outputs: tuple | None = None, explicit_outputs: bool = False) -> PreparedCall:
+        if outputs is not None:
+            arguments = self.interface.explicit_arguments(tuple(arguments), tuple(outputs))
+            explicit_outputs = True
+        bound = self.interface.bind(tuple(arguments), device=self._torch_device,
+                                    explicit_outputs=explicit_outputs)
+        return PreparedCall(self, bound)
+
+    def prepare_call(self, arguments: tuple, *, outputs: tuple | None = None) -> PreparedCall:
+        return self.prepare(*arguments, outputs=outputs)
+
+    def run(self, *arguments):
+        call = self.prepare(*arguments)
+        call.launch()
+        return call.result()
+
+    def launch(self, *arguments) -> None:
+        self.prepare(*arguments, explicit_outputs=True).launch()
+
+    def infer_outputs(self, arguments: tuple):
+        """Shape inference for fake tensors: no pointers, no launch."""
+        device = arguments and next((a.device for a in arguments if hasattr(a, "device")), None)
+        return self.interface.bind(tuple(arguments), device=device or self._torch_device, abstract=True).result()
+
+
+def _scalar_carrier(parameter: ScalarParameter) -> str:
+    name = parameter.dtype.name
+    if name in ("i8", "i16", "i32", "i64", "f32", "f64", "bool"):
+        return name
+    raise NotImplementedError(f"native scalar carrier for {name}")
+
+
+@dataclass(slots=True)
+class CompiledArtifact:
+    source: str
+    mlir: str
+    device: int
+    runtime: Any = field(repr=False)
+    device_type: str = field(default="cuda", kw_only=True)
+    cache_directory: Path | None = field(default=None, kw_only=True)
+    backend_ir: dict = field(default_factory=dict, init=False)
+
+    @property
+    def observation(self):
+        """Latest native invocation snapshot, or None before the first launch."""
+        return getattr(self.runtime, "observation", None)
+
+    @property
+    def entry(self):
+        return self.__call__
+
+    @property
+    def ir(self) -> dict:
+        return {"intent": self.mlir, **self.backend_ir}
+
+    @property
+    def interface(self) -> PublicInterface:
+        return self.runtime.interface
+
+    def run(self, *arguments: Any):
+        """Allocate declared Out buffers and execute with inputs in declaration order."""
+        return self._invoke(self.runtime.run, arguments)
+
+    def prepare(self, *arguments: Any, outputs: tuple | None = None) -> PreparedCall:
+        """Bind arguments and allocate outputs/workspace without executing."""
+        return self._invoke(lambda *args: self.runtime.prepare_call(args, outputs=outputs), arguments)
+
+    def launch(self, *arguments: Any) -> None:
+        """Execute with every runtime argument, including explicit Out buffers."""
+        self._invoke(self.runtime.launch, arguments)
+
+    __call__ = launch
+
+    def as_torch_op(self, name: str):
+        from .torch_op import register_operator
+
+        return register_operator(self, name)
+
+    def tuning_configurations(self, *arguments: Any):
+        raise NotImplementedError("this provider does not export structured tuning configurations")
+
+    def inspect_configurations(self, *arguments: Any, outputs: tuple | None = None):
+        return self.prepare(*arguments, outputs=outputs).inspect_configurations()
+
+    def _invoke(self, function, arguments: tuple):
+        import torch
+
+        expected = torch.device(self.device_type, self.device)
+        for index, argument in enumerate(arguments):
+            if isinstance(argument, torch.Tensor) and argument.device != expected:
+                raise ValueError(f"compiled artifact is bound to {expected}, but tensor argument "
+                                 f"{index} is on {argument.device}")
+        if torch.cuda.current_device() == self.device:
+            return function(*arguments)
+        with torch.cuda.device(self.device):
+            return function(*arguments)

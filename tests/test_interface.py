@@ -1,0 +1,135 @@
+"""Host-side call surface on CPU: binder checks, output allocation, error types
+(the reference raises and never coerces: python/intent/runtime/invocation.py:94-150,
+torch_views.py:32-43, native_requirements.py:66-91)."""
+import pytest
+import torch
+
+import intent_b200 as ib
+from intent_b200.runtime.interface import PublicInterface, ViewKind, ViewParameter
+
+CPU = torch.device("cpu")
+
+
+@pytest.fixture(scope="module")
+def artifact():
+    return ib.compile(ib.programs.weight_only_int4_matmul, constexprs={"GROUP_SIZE": 128, "ZERO_POINT": 8},
+                      resolve_target=False)
+
+
+def _inputs(M=4, K=256, N=64, dtype=torch.float16):
+    return ib.workloads.w4a16_inputs(M, K, N, dtype=dtype)
+
+
+def test_interface_declaration(artifact):
+    interface = artifact.interface
+    assert [p.name for p in interface.parameters] == ["activation", "packed_weight", "scales", "output"]
+    assert [p.name for p in interface.inputs] == ["activation", "packed_weight", "scales"]
+    assert [p.name for p in interface.outputs] == ["output"]
+    assert interface.mutable_inputs == ()
+    assert "weight_only_int4.py" in artifact.source and artifact.mlir
+    assert artifact.device_type == "cuda" and artifact.entry == artifact.__call__
+
+
+def test_bind_allocates_outputs(artifact):
+    x, p, s = _inputs()
+    bound = artifact.interface.bind((x, p, s), device=CPU)
+    assert bound.result().shape == (4, 64) and bound.result().dtype == torch.float16
+    assert bound.dimensions == {"M": 4, "K": 256, "P": 32, "N": 64, "G": 2}
+
+
+def test_bind_errors(artifact):
+    interface = artifact.interface
+    x, p, s = _inputs()
+    with pytest.raises(TypeError):
+        interface.bind((x, p), device=CPU)                       # argument count
+    with pytest.raises(TypeError):
+        interface.bind((x.numpy(), p, s), device=CPU)             # not a tensor
+    with pytest.raises(TypeError):
+        interface.bind((x.float(), p, s), device=CPU)             # dtype is never coerced
+    with pytest.raises(ValueError):
+        interface.bind((x[0], p, s), device=CPU)                  # rank
+    with pytest.raises(ValueError):
+        interface.bind((x, p, s[:, :32].contiguous()), device=CPU)  # N relation
+    with pytest.raises(ValueError):
+        interface.bind((x, p[:16].contiguous(), s), device=CPU)     # P * 8 == K
+    with pytest.raises(ValueError):
+        interface.bind((x, p, torch.cat((s, s))), device=CPU)       # G * group == K
+    with pytest.raises(NotImplementedError):
+        interface.bind((x.t().contiguous().t(), p, s), device=CPU)  # non-canonical strides
+    with pytest.raises(ValueError):
+        interface.bind((x, p, s), device=torch.device("meta"))      # device
+
+
+def test_bind_alignment_and_overlap(artifact):
+    interface = artifact.interface
+    x, p, s = _inputs()
+    storage = torch.zeros(4 * 256 + 8, dtype=torch.float16)
+    misaligned = storage[1:1 + 4 * 256].view(4, 256)
+    assert misaligned.data_ptr() % 16 != 0
+    with pytest.raises(ValueError, match="alignment"):
+        interface.bind((misaligned, p, s), device=CPU)
+    # explicit output that overlaps an input
+    shared = torch.zeros(4 * 256, dtype=torch.float16)
+    xin = shared.view(4, 256)
+    out = shared[:4 * 64].view(4, 64)
+    with pytest.raises(NotImplementedError, match="nonoverlapping"):
+        interface.bind((xin, p, s, out), device=CPU, explicit_outputs=True)
+
+
+def test_explicit_outputs_and_argument_merge(artifact):
+    interface = artifact.interface
+    x, p, s = _inputs()
+    out = torch.empty((4, 64), dtype=torch.float16)
+    merged = interface.explicit_arguments((x, p, s), (out,))
+    assert merged[3] is out
+    bound = interface.bind(merged, device=CPU, explicit_outputs=True)
+    assert bound.outputs[0] is out
+    with pytest.raises(ValueError):
+        interface.bind((x, p, s, torch.empty((4, 32), dtype=torch.float16)), device=CPU, explicit_outputs=True)
+    with pytest.raises(TypeError):
+        interface.explicit_arguments((x, p, s), ())
+
+
+def test_unallocatable_output():
+    interface = PublicInterface((
+        ViewParameter(0, "a", ib.dtypes.f32, ("M",), ViewKind.IN),
+        ViewParameter(1, "b", ib.dtypes.f32, ("Q",), ViewKind.OUT),
+    ))
+    with pytest.raises(NotImplementedError, match="explicit output"):
+        interface.bind((torch.zeros(4),), device=CPU)
+    bound = interface.bind((torch.zeros(4), torch.zeros(7)), device=CPU, explicit_outputs=True)
+    assert bound.dimensions == {"M": 4, "Q": 7}
+
+
+def test_abstract_binding_has_no_addresses(artifact):
+    x, p, s = _inputs()
+    bound = artifact.interface.bind((x, p, s), device=CPU, abstract=True)
+    assert all(f is None or f.pointer is None for f in bound.views)
+    assert bound.result().shape == (4, 64)
+
+
+def test_compile_errors():
+    with pytest.raises(ib.CompilationStageError) as info:
+        ib.compile(ib.programs.weight_only_int4_matmul, constexprs={"NOPE": 1}, resolve_target=False)
+    assert info.value.stage == "frontend_kir"
+    with pytest.raises(ib.CompilationStageError) as info:
+        ib.compile(ib.programs.weight_only_int4_matmul, constexprs={"GROUP_SIZE": 48}, resolve_target=False)
+    assert info.value.stage == "provider_native_compilation"
+    with pytest.raises(ib.CompilationStageError) as info:
+        ib.compile(lambda: None, resolve_target=False)
+    assert info.value.stage == "frontend_kir"
+    if not torch.cuda.is_available():
+        with pytest.raises(ib.CompilationStageError) as info:
+            ib.compile(ib.programs.weight_only_int4_matmul)
+        assert info.value.stage == "target_resolution"
+
+
+def test_tuning_is_declined(artifact):
+    with pytest.raises(NotImplementedError):
+        artifact.tuning_configurations()
+
+
+def test_artifact_rejects_wrong_device(artifact):
+    x, p, s = _inputs()
+    with pytest.raises(ValueError, match="bound to"):
+        artifact.run(x, p, s)          # CPU tensors handed to a CUDA artifact

@@ -1,0 +1,149 @@
+"""The oracle restatements against the golden vectors produced by the
+reference's own torch-CPU implementations (tests/golden/generate.py)."""
+import pytest
+import torch
+
+import oracle
+from conftest import load_golden
+
+
+@pytest.mark.parametrize("tag", ["small", "ragged_m", "wide"])
+def test_w4a16_matches_reference(tag):
+    g = load_golden(f"w4a16_{tag}")
+    out = oracle.weight_only_int4_matmul(g["activation"], g["packed"], g["scales"])  # defaults = reference constants
+    assert out.dtype == torch.float16
+    assert torch.equal(out, g["output"])
+
+
+def test_w4a16_zero_point_form_equals_signed_form():
+    g = load_golden("w4a16_small")
+    flipped = g["packed"] ^ torch.tensor(-2004318072, dtype=torch.int32)  # 0x88888888
+    out = oracle.weight_only_int4_matmul(g["activation"], flipped, g["scales"], group_size=64, zero_point=8)
+    assert torch.equal(out, g["output"])
+
+
+def test_w4a16_rounded_contract_is_within_reference_tolerance():
+    g = load_golden("w4a16_wide")
+    rounded = oracle.weight_only_int4_matmul_rounded(g["activation"], g["packed"], g["scales"])
+    assert (rounded.float() - g["output"].float()).abs().max() <= 4e-2  # reference Tolerance(atol=4e-2)
+
+
+def test_pack_unpack_roundtrip():
+    q = torch.randint(0, 16, (64, 24), dtype=torch.int32, generator=torch.Generator().manual_seed(1))
+    assert torch.equal(oracle.unpack_int4(oracle.pack_int4(q)), q)
+    signed = torch.randint(-8, 8, (64, 24), dtype=torch.int32, generator=torch.Generator().manual_seed(2))
+    nib = oracle.unpack_int4(oracle.pack_int4(signed))
+    assert torch.equal(nib - ((nib & 8) << 1), signed)
+
+
+@pytest.mark.parametrize("tag", ["small", "odd"])
+def test_gemm_i8_matches_reference(tag):
+    g = load_golden(f"gemm_i8_{tag}")
+    assert torch.equal(oracle.gemm_i8(g["a"], g["b"], g["bias"]), g["output"])
+    assert torch.equal(oracle.gemm_i8_exact_f64(g["a"], g["b"], g["bias"]), g["output"])
+
+
+def test_gemm_i8_extreme_values_exact():
+    a = torch.full((8, 8192), -128, dtype=torch.int8)
+    b = torch.full((8192, 16), -128, dtype=torch.int8)
+    out = oracle.gemm_i8(a, b)
+    assert torch.equal(out, torch.full((8, 16), 8192 * 128 * 128, dtype=torch.int32))
+
+
+def test_w8a8_epilogue_definition():
+    g = load_golden("gemm_i8_small")
+    sa = torch.rand(16) * 0.01 + 1e-3
+    sb = torch.rand(64) * 0.01 + 1e-3
+    out, acc = oracle.w8a8_scaled_gemm(g["a"], g["b"], sa, sb)
+    assert torch.equal(acc, g["output"] - g["bias"][None, :])
+    assert out.dtype == torch.bfloat16
+    assert torch.equal(out, ((acc.float() * sa[:, None]) * sb[None, :]).bfloat16())
+
+
+@pytest.mark.parametrize("tag", ["ref_pattern", "small"])
+def test_moe_align_matches_reference(tag):
+    g = load_golden(f"moe_align_{tag}")
+    block, experts = int(g["block"]), int(g["experts"])
+    sorted_ids, expert_ids, total, offsets = oracle.moe_align_block_size(g["topk_ids"], block, experts)
+    assert torch.equal(sorted_ids, g["sorted_ids"])
+    assert torch.equal(total, g["total"])
+    blocks = int(total) // block
+    assert torch.equal(expert_ids[:blocks], g["expert_ids"])
+    assert torch.equal(oracle.moe_count_routes(g["topk_ids"], experts), g["counts"])
+    assert int(offsets[-1]) == int(total) and int(offsets[0]) == 0
+    # the canonical (order-free) view is the identity on a stable alignment
+    canonical, _, _ = oracle.canonical_alignment(sorted_ids, expert_ids, total, block_size=block, num_experts=experts)
+    assert torch.equal(canonical, sorted_ids[:int(total)])
+
+
+def test_insertion_top_k_matches_reference():
+    g = load_golden("insertion_top_k")
+    values, indices = oracle.insertion_top_k(g["logits"], 8)
+    assert torch.equal(values, g["values"]) and torch.equal(indices, g["indices"])
+    # ties: lower index first
+    assert indices[3, 0] == 10 and indices[3, 1] == 50
+    assert indices[7].tolist() == list(range(8))
+    # k = 2 is a prefix of k = 8
+    v2, i2 = oracle.insertion_top_k(g["logits"], 2)
+    assert torch.equal(i2, g["indices"][:, :2]) and torch.equal(v2, g["values"][:, :2])
+
+
+def test_softmax_matches_reference():
+    g = load_golden("softmax_f32")
+    assert torch.equal(oracle.softmax_f32(g["x"]), g["output"])
+
+
+def test_router_top2_logits_vs_probabilities_agree_on_seeded_inputs():
+    logits = torch.randn((4096, 64), generator=torch.Generator().manual_seed(0))
+    ids, weights = oracle.moe_route_top2(logits)
+    _, by_probability = oracle.insertion_top_k(oracle.softmax_f32(logits), 2)
+    assert torch.equal(ids, by_probability)
+    assert torch.all(ids[:, 0] != ids[:, 1])
+    assert torch.all(weights[:, 0] >= weights[:, 1])
+
+
+def test_silu_gate_matches_reference_within_its_tolerance():
+    g = load_golden("silu_and_mul_packed")
+    out = oracle.silu_and_mul(g["packed"], out_dtype=torch.bfloat16)
+    # the reference rounds silu to bf16 before the product (two roundings), the oracle rounds once;
+    # reference tolerance for this kernel: atol 2e-2, rtol 1e-2 (providers/mojo/activation.py:43-47)
+    assert torch.allclose(out.float(), g["output"].float(), atol=2e-2, rtol=1e-2)
+
+
+def test_ragged_grouped_gemm_matches_reference():
+    g = load_golden("ragged_grouped_gemm")
+    out = oracle.ragged_grouped_gemm(g["x"], g["offsets"], g["weight"])
+    assert torch.equal(out, g["output"])
+
+
+def test_routed_projection_matches_reference():
+    g = load_golden("routed_expert_projection_bf16")
+    out = oracle.routed_expert_projection(g["x"], g["offsets"], g["member_routes"], g["weight"])
+    assert torch.equal(out, g["output"])
+
+
+def test_moe_expert_ffn_matches_reference():
+    g = load_golden("moe_expert_ffn")
+    y = oracle.moe_expert_ffn(g["x"], g["route_offsets"], g["member_routes"], g["route_token"],
+                              g["route_weights"], g["w1"], g["w2"], torch.zeros_like(g["y"]))
+    assert torch.equal(y, g["y"])
+
+
+def test_moe_w4a16_swiglu_ffn_consistent_with_dense_form():
+    """The W4A16 SiLU-gated FFN equals the dense per-expert formula on dequantised weights."""
+    import intent_b200.workloads as wl
+
+    data = wl.moe_inputs(32, 128, 4, 128, dtype=torch.bfloat16, seed=3)
+    ids, weights = oracle.moe_route_top2(data["logits"])
+    y = oracle.moe_w4a16_swiglu_ffn(data["x"], ids, weights, data["up_gate_packed"], data["up_gate_scales"],
+                                    data["down_packed"], data["down_scales"], round_hidden=False)
+    expected = torch.zeros_like(y)
+    for t in range(32):
+        for c in range(2):
+            e = int(ids[t, c])
+            wu = oracle.dequantize_int4(data["up_gate_packed"][e], data["up_gate_scales"][e], group_size=128, zero_point=8)
+            wd = oracle.dequantize_int4(data["down_packed"][e], data["down_scales"][e], group_size=128, zero_point=8)
+            gu = data["x"][t].float() @ wu
+            h = torch.nn.functional.silu(gu[:128]) * gu[128:]
+            expected[t] += weights[t, c] * (h @ wd)
+    assert torch.allclose(y, expected, rtol=1e-4, atol=1e-6)

@@ -1,0 +1,141 @@
+"""W4A16 parity on the GPU, through the artifact surface (which calls the C ABI).
+
+Tolerances: the benchmark's criterion  max|y - ref| <= 2e-2 * max|ref|  against
+the f32-accumulate dequant oracle, and the reference's own Tolerance(atol=4e-2)
+on its own case recipe (experiments/cpu/providers/mojo/contraction.py:190-198).
+"""
+import pytest
+import torch
+
+import intent_b200 as ib
+import oracle
+from conftest import load_golden, max_abs_rel
+
+pytestmark = pytest.mark.gpu
+
+BENCH_TOL = 2e-2
+
+
+def _compile(dtype="f16", group=128, zero_point=8, kernel="auto"):
+    return ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(0),
+                      constexprs={"GROUP_SIZE": group, "ZERO_POINT": zero_point, "ACT_DTYPE": dtype,
+                                  "KERNEL": kernel})
+
+
+@pytest.mark.parametrize("tag", ["small", "ragged_m"])
+def test_golden_reference_layout(cuda_device, tag):
+    """The reference's own constants (group 64, two's-complement nibbles, f16) on golden vectors."""
+    g = load_golden(f"w4a16_{tag}")
+    artifact = _compile("f16", 64, "twos_complement")
+    out = artifact.run(g["activation"].to(cuda_device), g["packed"].to(cuda_device), g["scales"].to(cuda_device))
+    torch.cuda.synchronize()
+    assert out.dtype == torch.float16 and out.shape == g["output"].shape
+    assert (out.cpu().float() - g["output"].float()).abs().max() <= 4e-2      # reference tolerance
+    assert max_abs_rel(out.cpu(), g["output"]) <= BENCH_TOL
+    assert max_abs_rel(out.cpu(), g["output"]) <= 2e-3                         # what the kernel really achieves
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 14336), (1, 14336, 4096), (4, 4096, 14336), (8, 14336, 4096),
+                                   (16, 4096, 4096), (3, 256, 68), (8, 128, 4), (32, 512, 200), (17, 1024, 64)])
+def test_skinny_matches_oracle(cuda_device, dtype, M, K, N):
+    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=dtype, group_size=128, seed=0)
+    artifact = _compile("f16" if dtype == torch.float16 else "bf16", 128, 8, "gemv")
+    out = artifact.run(x.to(cuda_device), p.to(cuda_device), s.to(cuda_device))
+    torch.cuda.synchronize()
+    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
+    assert out.dtype == dtype
+    assert max_abs_rel(out.cpu(), ref) <= BENCH_TOL
+    # rounding of the result to 16 bits dominates: a few ulp of the output type
+    assert max_abs_rel(out.cpu(), ref) <= (2e-3 if dtype == torch.float16 else 1.6e-2)
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_group_sizes_and_auto_dispatch(cuda_device, group):
+    x, p, s = ib.workloads.w4a16_inputs(5, 512, 96, dtype=torch.float16, group_size=group, seed=4)
+    artifact = _compile("f16", group, 8, "auto")
+    out = artifact.run(x.to(cuda_device), p.to(cuda_device), s.to(cuda_device))
+    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=group, zero_point=8)
+    assert max_abs_rel(out.cpu(), ref) <= 2e-3
+
+
+def test_launch_shapes_give_identical_bits(cuda_device):
+    """Every launch shape sums in a fixed order; different shapes agree to rounding and
+    the same shape is bit-reproducible."""
+    from intent_b200.runtime import native
+
+    lib = native.library()
+    x, p, s = ib.workloads.w4a16_inputs(4, 4096, 1024, dtype=torch.float16, seed=7)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    artifact = _compile("f16", 128, 8, "gemv")
+    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
+    try:
+        for wn, wk, split in [(1, 4, 1), (2, 4, 2), (4, 2, 4), (2, 2, 8), (1, 8, 1), (4, 1, 2)]:
+            assert lib.intent_b200_w4a16_gemv_configure(wn, wk, split) == 0
+            first = artifact.run(xd, pd, sd)
+            second = artifact.run(xd, pd, sd)
+            torch.cuda.synchronize()
+            assert torch.equal(first, second)
+            assert max_abs_rel(first.cpu(), ref) <= 2e-3, (wn, wk, split)
+    finally:
+        lib.intent_b200_w4a16_gemv_configure(0, 0, 0)
+
+
+def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
+    x, p, s = ib.workloads.w4a16_inputs(4, 1024, 256, dtype=torch.float16, seed=2)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    artifact = _compile()
+    expected = artifact.run(xd, pd, sd)
+    # explicit outputs
+    out = torch.zeros_like(expected)
+    assert artifact(xd, pd, sd, out) is None
+    assert torch.equal(out, expected)
+    # prepared call: no launch at prepare/compile/result, replayable, graph-capturable
+    call = artifact.prepare(xd, pd, sd)
+    call.compile()
+    held = call.result()
+    held.zero_()
+    call.launch()
+    torch.cuda.synchronize()
+    assert torch.equal(held, expected)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call.launch()                      # warm up on the side stream before capture
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    held.zero_()
+    with torch.cuda.graph(graph, stream=side):
+        call.launch()
+    held.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(held, expected)
+    assert artifact.observation is not None and artifact.observation.status == 0
+    # torch custom operator with a fake implementation
+    op = artifact.as_torch_op("intent_b200_test::w4a16")
+    assert torch.equal(op(xd, pd, sd), expected)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        fake = op(torch.empty((4, 1024), dtype=torch.float16, device="cuda"),
+                  torch.empty((128, 256), dtype=torch.int32, device="cuda"),
+                  torch.empty((8, 256), dtype=torch.float16, device="cuda"))
+        assert fake.shape == (4, 256) and fake.dtype == torch.float16
+
+
+def test_errors_and_edges_on_device(cuda_device):
+    artifact = _compile()
+    x, p, s = ib.workloads.w4a16_inputs(2, 256, 64, dtype=torch.float16)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    with pytest.raises(TypeError):
+        artifact.run(xd.float(), pd, sd)
+    with pytest.raises(ValueError):
+        artifact.run(xd, pd, sd.cpu())
+    # zero rows: nothing is launched, an empty result comes back
+    empty = artifact.run(xd[:0], pd, sd)
+    assert empty.shape == (0, 64)
+    # an unsupported column count is reported by the C entry as a status, not a crash
+    x2, p2, s2 = ib.workloads.w4a16_inputs(2, 256, 66, dtype=torch.float16)
+    with pytest.raises(ib.CompilationStageError) as info:
+        artifact.run(x2.to(cuda_device), p2.to(cuda_device), s2.to(cuda_device))
+    assert info.value.stage == "provider_invocation" and info.value.status == 3
