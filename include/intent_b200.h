@@ -85,10 +85,18 @@ INTENT_B200_API int intent_b200_w4a16_gemv_bf16(INTENT_B200_VIEW2(a0), INTENT_B2
                                 INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
                                 int32_t group_size, int32_t zero_point, void* stream);
 /* Launch-shape override of the skinny kernel for measurement sweeps:
- * warps along N per CTA (1|2|4), warps along K (1..8), K-split = cluster size
+ * warps along N per CTA (1|2), warps along K (4|8|16), K-split = cluster size
  * (1|2|4|8).  0 restores the built-in choice for that field.  Process-global,
  * not thread-safe against concurrent launches. */
 INTENT_B200_API int intent_b200_w4a16_gemv_configure(int32_t warps_n, int32_t warps_k, int32_t split_k);
+/* Launch-latency overlap of the skinny kernel (programmatic dependent launch).
+ * When enabled, a launch may start and prefetch its packed weights and scales
+ * while the kernel before it on the stream is still running; it waits for that
+ * kernel before it reads the activations or writes the output.  Only enable it
+ * when the weights and scales are not written by the kernel launched immediately
+ * before (they are static model state in a decode loop).  Process-global; off by
+ * default. */
+INTENT_B200_API int intent_b200_w4a16_gemv_overlap(int32_t enable);
 
 #ifdef __cplusplus
 }

@@ -70,15 +70,23 @@ def test_launch_shapes_give_identical_bits(cuda_device):
     artifact = _compile("f16", 128, 8, "gemv")
     ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
     try:
-        for wn, wk, split in [(1, 4, 1), (2, 4, 2), (4, 2, 4), (2, 2, 8), (1, 8, 1), (4, 1, 2)]:
+        for wn, wk, split in [(1, 8, 1), (1, 16, 2), (2, 4, 2), (2, 8, 4), (1, 8, 8), (2, 4, 1)]:
             assert lib.intent_b200_w4a16_gemv_configure(wn, wk, split) == 0
             first = artifact.run(xd, pd, sd)
             second = artifact.run(xd, pd, sd)
             torch.cuda.synchronize()
             assert torch.equal(first, second)
             assert max_abs_rel(first.cpu(), ref) <= 2e-3, (wn, wk, split)
+        # launch overlap on: same bits as with it off (back-to-back launches on one stream)
+        lib.intent_b200_w4a16_gemv_configure(0, 0, 0)
+        plain = artifact.run(xd, pd, sd)
+        assert lib.intent_b200_w4a16_gemv_overlap(1) == 0
+        outs = [artifact.run(xd, pd, sd) for _ in range(4)]
+        torch.cuda.synchronize()
+        assert all(torch.equal(o, plain) for o in outs)
     finally:
         lib.intent_b200_w4a16_gemv_configure(0, 0, 0)
+        lib.intent_b200_w4a16_gemv_overlap(0)
 
 
 def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
