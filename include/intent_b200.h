@@ -68,35 +68,40 @@ INTENT_B200_API int64_t intent_b200_launch_count(void);
  *   zero_point: -1 = two's-complement nibble (the reference's decoding),
  *                8 = unsigned nibble minus 8 (benchmark configurations)
  * Y[m,n] = T( sum_k f32(X[m,k]) * f32(w[k,n]) ), f32 accumulation.
- * The plain entries pick the kernel from M (skinny bandwidth kernel for
- * M <= 32, tcgen05 tensor-core kernel above); the _gemv / _gemm entries force
- * one of the two.
+ * The plain entries pick the kernel from M (bandwidth kernel for M <= 32,
+ * tcgen05 tensor-core kernel above); the _gemv / _gemm entries force one.
+ *
+ * workspace: device scratch of at least ..._workspace_bytes(M, K, N) bytes,
+ * 16-byte aligned (NULL / 0 when that query returns 0).  It must be zero-filled
+ * once after allocation; every launch leaves it zero-filled again, so it can be
+ * reused by later launches on the SAME stream.  Launches that may overlap on
+ * the GPU (different streams) need separate workspaces.  Byte 0..3 is a status
+ * word: a launch whose bounded device wait expired stores INTENT_B200_ERR_TIMEOUT
+ * there.
  * ------------------------------------------------------------------------ */
-INTENT_B200_API int intent_b200_weight_only_int4_matmul_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
-                                            INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
-                                            int32_t group_size, int32_t zero_point, void* stream);
-INTENT_B200_API int intent_b200_weight_only_int4_matmul_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
-                                             INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
-                                             int32_t group_size, int32_t zero_point, void* stream);
-INTENT_B200_API int intent_b200_w4a16_gemv_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
-                               INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
-                               int32_t group_size, int32_t zero_point, void* stream);
-INTENT_B200_API int intent_b200_w4a16_gemv_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
-                                INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
-                                int32_t group_size, int32_t zero_point, void* stream);
-/* Launch-shape override of the skinny kernel for measurement sweeps:
- * warps along N per CTA (1|2), warps along K (4|8|16), K-split = cluster size
- * (1|2|4|8).  0 restores the built-in choice for that field.  Process-global,
- * not thread-safe against concurrent launches. */
-INTENT_B200_API int intent_b200_w4a16_gemv_configure(int32_t warps_n, int32_t warps_k, int32_t split_k);
-/* Launch-latency overlap of the skinny kernel (programmatic dependent launch).
- * When enabled, a launch may start and prefetch its packed weights and scales
+#define INTENT_B200_W4A16_SLOTS                                                                   \
+  INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),     \
+      int32_t group_size, int32_t zero_point, void *workspace, int64_t workspace_bytes, void *stream
+INTENT_B200_API int intent_b200_weight_only_int4_matmul_f16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int intent_b200_weight_only_int4_matmul_bf16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int intent_b200_w4a16_gemv_f16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int intent_b200_w4a16_gemv_bf16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int intent_b200_w4a16_gemm_f16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int intent_b200_w4a16_gemm_bf16(INTENT_B200_W4A16_SLOTS);
+INTENT_B200_API int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N);
+INTENT_B200_API int64_t intent_b200_w4a16_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N);
+/* Launch-latency overlap of the bandwidth kernel (programmatic dependent
+ * launch).  When enabled, a launch may start and request its packed weights
  * while the kernel before it on the stream is still running; it waits for that
- * kernel before it reads the activations or writes the output.  Only enable it
- * when the weights and scales are not written by the kernel launched immediately
- * before (they are static model state in a decode loop).  Process-global; off by
- * default. */
+ * kernel before it reads the activations or writes the output.  Only enable it when the packed weights are not written by the kernel
+ * launched immediately before (they are static model state in a decode loop).
+ * Process-global; off by default. */
 INTENT_B200_API int intent_b200_w4a16_gemv_overlap(int32_t enable);
+/* Number of CTAs of the bandwidth kernel (0 = one per SM).  For measurement
+ * sweeps; process-global. */
+INTENT_B200_API int intent_b200_w4a16_gemv_grid(int32_t ctas);
+/* Warps per CTA of the bandwidth kernel (8 or 16).  For measurement sweeps; process-global. */
+INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
 
 #ifdef __cplusplus
 }

@@ -66,8 +66,19 @@ def _lower_w4a16(constants, device):
         _rule(lambda d: d["K"] % group == 0 and d["G"] * group == d["K"],
               lambda d: f"scales.shape[0] must be K/GROUP_SIZE with K a multiple of {group}"),
     ))
+    def workspace_bytes(d):
+        import ctypes
+
+        from .runtime import native
+
+        query = native.library().intent_b200_weight_only_int4_matmul_workspace_bytes
+        query.restype = ctypes.c_int64
+        query.argtypes = [ctypes.c_int64] * 3
+        rows = d["M"] if kernel != "gemm" else 1 << 30
+        return int(query(rows, d["K"], d["N"])) if kernel != "gemm" else 0
+
     return NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
-                         constants=(group, zp), device=device,
+                         constants=(group, zp), device=device, workspace=workspace_bytes,
                          empty=lambda d: d["M"] == 0 or d["N"] == 0)
 
 

@@ -39,10 +39,10 @@ class NativeObservation:
 class PreparedCall:
     """Arguments bound to one C entry; ``launch`` replays the same call."""
 
-    def __init__(self, program: "NativeProgram", bound: BoundArguments) -> None:
+    def __init__(self, program: "NativeProgram", bound: BoundArguments, workspace: tuple | None = None) -> None:
         self.program = program
         self.invocation = bound
-        self._workspace = program.allocate_workspace(bound)
+        self._workspace = program.allocate_workspace(bound) if workspace is None else workspace
         self._slots = program.marshal(bound, self._workspace)
         self._observation: NativeObservation | None = None
         self._skip = program.is_empty(bound)
@@ -104,7 +104,8 @@ class NativeProgram:
         self.entry_name = entry_name
         self.constants = tuple(int(c) for c in constants)
         self.device = device
-        self._workspace_spec = workspace     # callable(dimensions) -> tuple[(shape, torch dtype)]
+        self._workspace_spec = workspace     # callable(dimensions) -> workspace bytes (0 = none)
+        self._stream_workspaces: dict = {}   # stream handle -> zero-initialised buffer reused by run()
         self._empty = empty                  # callable(dimensions) -> bool
         self._observation: NativeObservation | None = None
         carriers = []
@@ -142,13 +143,26 @@ class NativeProgram:
     def is_empty(self, bound: BoundArguments) -> bool:
         return bool(self._empty(bound.dimensions)) if self._empty is not None else False
 
-    def allocate_workspace(self, bound: BoundArguments) -> tuple:
+    def allocate_workspace(self, bound: BoundArguments, *, per_stream: bool = False) -> tuple:
+        """Scratch for one binding.  Entries keep their scratch zero-filled across
+        launches, so it is zeroed once here.  ``per_stream`` reuses one buffer for
+        successive calls on the current stream (what ``run`` does); a prepared
+        call owns a private buffer."""
         import torch
 
         if self._workspace_spec is None:
             return ()
-        return tuple(torch.empty(shape, dtype=dtype, device=self._torch_device)
-                     for shape, dtype in self._workspace_spec(bound.dimensions))
+        size = int(self._workspace_spec(bound.dimensions))
+        if size <= 0:
+            return (torch.empty((0,), dtype=torch.uint8, device=self._torch_device),)
+        if not per_stream:
+            return (torch.zeros((size,), dtype=torch.uint8, device=self._torch_device),)
+        key = torch.cuda.current_stream(self.device).cuda_stream
+        cached = self._stream_workspaces.get(key)
+        if cached is None or cached.numel() < size:
+            cached = torch.zeros((max(size, 1 << 16),), dtype=torch.uint8, device=self._torch_device)
+            self._stream_workspaces[key] = cached
+        return (cached,)
 
     def marshal(self, bound: BoundArguments, workspace: tuple) -> tuple:
         slots = []
@@ -161,7 +175,7 @@ class NativeProgram:
                 slots.append(value)
         slots += [ctypes.c_int32(c) for c in self.constants]
         for buffer in workspace:
-            slots.append(ctypes.c_void_p(buffer.data_ptr()))
+            slots.append(ctypes.c_void_p(buffer.data_ptr() if buffer.numel() else None))
             slots.append(ctypes.c_int64(buffer.numel() * buffer.element_size()))
         self.function(len(workspace))
         return tuple(slots)
@@ -179,7 +193,8 @@ class NativeProgram:
         return self.prepare(*arguments, outputs=outputs)
 
     def run(self, *arguments):
-        call = self.prepare(*arguments)
+        bound = self.interface.bind(tuple(arguments), device=self._torch_device)
+        call = PreparedCall(self, bound, self.allocate_workspace(bound, per_stream=True))
         call.launch()
         return call.result()
 
