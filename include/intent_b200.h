@@ -100,7 +100,8 @@ INTENT_B200_API int intent_b200_w4a16_gemv_overlap(int32_t enable);
 /* Number of CTAs of the bandwidth kernel (0 = one per SM).  For measurement
  * sweeps; process-global. */
 INTENT_B200_API int intent_b200_w4a16_gemv_grid(int32_t ctas);
-/* Warps per CTA of the bandwidth kernel (8 or 16).  For measurement sweeps; process-global. */
+/* Warps per CTA of the bandwidth kernel for M <= 8 (16 or 32; 0 = built-in choice).
+ * For measurement sweeps; process-global. */
 INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
 
 #ifdef __cplusplus

@@ -37,7 +37,7 @@ def test_golden_reference_layout(cuda_device, tag):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,K,N", [(1, 4096, 14336), (1, 14336, 4096), (4, 4096, 14336), (8, 14336, 4096),
-                                   (16, 4096, 4096), (3, 256, 68), (8, 128, 4), (16, 512, 200), (9, 1024, 64), (2, 128, 8)])
+                                   (16, 4096, 4096), (3, 256, 72), (8, 128, 8), (16, 512, 200), (9, 1024, 64), (2, 128, 8)])
 def test_skinny_matches_oracle(cuda_device, dtype, M, K, N):
     x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=dtype, group_size=128, seed=0)
     artifact = _compile("f16" if dtype == torch.float16 else "bf16", 128, 8, "gemv")
@@ -100,9 +100,9 @@ def test_workspace_stays_clean_and_status_word_is_zero(cuda_device):
     torch.cuda.synchronize()
     (workspace,) = call._workspace
     assert workspace.numel() > 0
-    header = workspace[:4096].cpu()
-    assert int(header.view(torch.int32)[0]) == 0                     # status word
-    assert not header.any()                                          # ticket counters are back at zero
+    header = workspace[:256 + 4 * (256 // 32)].cpu()               # status word + one ticket counter per 32 columns
+    assert int(header[:4].view(torch.int32)[0]) == 0                # status word
+    assert not header.any()                                         # ticket counters are back at zero
 
 
 def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
@@ -159,7 +159,7 @@ def test_errors_and_edges_on_device(cuda_device):
     empty = artifact.run(xd[:0], pd, sd)
     assert empty.shape == (0, 64)
     # an unsupported column count is reported by the C entry as a status, not a crash
-    x2, p2, s2 = ib.workloads.w4a16_inputs(2, 256, 66, dtype=torch.float16)
+    x2, p2, s2 = ib.workloads.w4a16_inputs(2, 256, 68, dtype=torch.float16)
     with pytest.raises(ib.CompilationStageError) as info:
         artifact.run(x2.to(cuda_device), p2.to(cuda_device), s2.to(cuda_device))
     assert info.value.stage == "provider_invocation" and info.value.status == 3
