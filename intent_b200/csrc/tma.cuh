@@ -85,22 +85,24 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll; the thread is parked by the hardware until the phase completes or the
+// suspend-time hint (in nanoseconds) runs out, so waiting warps do not compete for issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t suspend_ns = 20000u) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(suspend_ns)
       : "memory");
   return done != 0;
 }
 
-// Bounded wait: gives up after `limit` polls (each poll itself blocks for a
-// hardware-defined time slice) and returns false; the caller records the failure
-// and leaves the kernel in an orderly way instead of hanging the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 1u << 22) {
+// Bounded wait: gives up after `limit` polls and returns false; the caller records the
+// failure and leaves the kernel in an orderly way instead of hanging the GPU.  With the
+// default hint the bound is of the order of a second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 1u << 16) {
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
