@@ -39,6 +39,7 @@ enum intent_b200_status {
   INTENT_B200_ERR_TIMEOUT = 4,      /* a bounded device-side wait gave up (read back from the status word) */
   INTENT_B200_ERR_WORKSPACE = 5,    /* workspace missing or too small */
   INTENT_B200_ERR_NULL = 6,         /* a required pointer is NULL */
+  INTENT_B200_ERR_SCRATCH_LIMIT = 7,/* problem needs more scratch than the built-in array of a no-allocation entry */
   INTENT_B200_ERR_CUDA = 1000       /* 1000 + cudaError_t of a failed runtime call */
 };
 
@@ -103,6 +104,34 @@ INTENT_B200_API int intent_b200_w4a16_gemv_grid(int32_t ctas);
 /* Warps per CTA of the bandwidth kernel for M <= 8 (16 or 32; 0 = built-in choice).
  * For measurement sweeps; process-global. */
 INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
+
+/* ------------------------------------------------------------------------
+ * W4A16 bandwidth kernel (f16) without any workspace argument.
+ * This entry has no counterpart in the reference.  It exists for callers that
+ * cannot allocate device memory on behalf of the library: a host that runs
+ * with a frozen memory pool, a plugin ABI that carries only an operator's
+ * inputs and outputs, or code between stream-capture begin and end, where
+ * cudaMalloc is not allowed.  Same arguments and result as
+ * intent_b200_w4a16_gemv_f16 minus the workspace pair; the scratch is a fixed
+ * 8 MiB device array inside the library image (held by every GPU that loads
+ * the library until the process exits).
+ *   - Problems whose scratch need (intent_b200_w4a16_gemv_workspace_bytes)
+ *     exceeds 8 MiB return INTENT_B200_ERR_SCRATCH_LIMIT; nothing is launched.
+ *   - The entry calls no cudaMalloc / cudaFree and no allocating library
+ *     routine.  It clears the part of the array that must start at zero with
+ *     a cudaMemsetAsync on `stream`, then launches the kernel on `stream`.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, that device current); make that first call
+ *     before any stream capture begins.
+ *   - All calls on one device share the one array: calls that can overlap on
+ *     the GPU (different streams, or different host threads on unordered
+ *     streams) race on it and produce wrong results.  Order them on one
+ *     stream or use the workspace entries.
+ * ------------------------------------------------------------------------ */
+INTENT_B200_API int intent_b200_w4a16_gemv_f16_builtin_scratch(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                               INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                                               int32_t group_size, int32_t zero_point,
+                                                               void* stream);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,7 @@ extern "C" const char* intent_b200_status_string(int status) {
     case INTENT_B200_ERR_TIMEOUT: return "bounded device wait expired";
     case INTENT_B200_ERR_WORKSPACE: return "workspace missing or too small";
     case INTENT_B200_ERR_NULL: return "null pointer";
+    case INTENT_B200_ERR_SCRATCH_LIMIT: return "problem exceeds the built-in scratch of the no-allocation entry";
     default: break;
   }
   if (status >= INTENT_B200_ERR_CUDA) return cudaGetErrorString(static_cast<cudaError_t>(status - INTENT_B200_ERR_CUDA));

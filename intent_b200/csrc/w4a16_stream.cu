@@ -34,6 +34,7 @@
 // warp that takes the last ticket adds the tile's partials in chunk order and
 // writes Y.  No CTA-wide barrier after start-up, no spin waits between CTAs, a
 // fixed summation order => bitwise reproducible.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -509,4 +510,66 @@ extern "C" int intent_b200_w4a16_gemv_warps(int32_t warps) {
   if (warps != 0 && warps != 16 && warps != 32) return INTENT_B200_ERR_UNSUPPORTED;
   ib200::g_warps_override = warps;
   return INTENT_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// Entry point that performs no allocation at all.
+//
+// Some hosts cannot hand this library a workspace: a serving loop that has frozen its
+// memory pool, a plugin interface that passes only the operator's inputs and outputs, or
+// code that runs between cudaStreamBeginCapture and EndCapture, where cudaMalloc is not
+// permitted.  For them the scratch of the bandwidth kernel lives in the library image
+// itself: a fixed device array that every GPU loading the library holds until the
+// process exits.
+// ---------------------------------------------------------------------------------
+namespace ib200 {
+
+constexpr size_t kBuiltinScratchBytes = size_t(8) << 20;  // 8 MiB: the decode shapes up to M = 8
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+// In host code `g_builtin_scratch` is only a handle for the symbol, not an address a kernel
+// could use; the device address is looked up once per device (with that device current).
+static int builtin_scratch_address(void** address) {
+  static std::mutex lock;
+  static void* per_device[64] = {};
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (device < 0 || device >= 64) return INTENT_B200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> guard(lock);
+  if (!per_device[device]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_builtin_scratch);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (!p) return INTENT_B200_ERR_NULL;
+    per_device[device] = p;
+  }
+  *address = per_device[device];
+  return INTENT_B200_OK;
+}
+
+}  // namespace ib200
+
+extern "C" int intent_b200_w4a16_gemv_f16_builtin_scratch(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                          INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                                          int32_t group_size, int32_t zero_point, void* stream) {
+  using namespace ib200;
+  const int64_t M = a0_d0, K = a0_d1, N = a1_d1;
+  if (M == 0 || N == 0) return INTENT_B200_OK;
+  if (M < 0 || M > 16 || K <= 0 || N < 0 || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
+  const int sms = g_grid_override > 0 ? g_grid_override : device_sms();
+  Plan plan;
+  if (sms <= 0 || !make_plan(int(M), int(K), int(N), M <= 8 ? 1 : 2, sms, M <= 8 ? g_warps_override : 0, &plan))
+    return INTENT_B200_ERR_UNSUPPORTED;
+  if (plan.workspace_bytes > kBuiltinScratchBytes) return INTENT_B200_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  int status = builtin_scratch_address(&scratch);
+  if (status != INTENT_B200_OK) return status;
+  // The array keeps whatever the previous call left: the status word and the ticket counters
+  // must start at zero, the partial sums behind them are overwritten before they are read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, plan.scratch_offset, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_status(e);
+  return w4a16_stream_f16(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2), IB200_VIEW2_ARG(a3),
+                          group_size, zero_point, scratch, int64_t(kBuiltinScratchBytes),
+                          static_cast<cudaStream_t>(stream));
 }
