@@ -91,6 +91,9 @@ INTENT_B200_API int intent_b200_w4a16_gemm_f16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int intent_b200_w4a16_gemm_bf16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N);
 INTENT_B200_API int64_t intent_b200_w4a16_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N);
+/* Status word of the tensor-core W4A16 kernel: 0, or INTENT_B200_ERR_TIMEOUT if a bounded
+ * device-side wait expired in an earlier launch.  Synchronises the device and clears the word. */
+INTENT_B200_API int intent_b200_w4a16_gemm_device_status(void);
 /* Launch-latency overlap of the bandwidth kernel (programmatic dependent
  * launch).  When enabled, a launch may start and request its packed weights
  * while the kernel before it on the stream is still running; it waits for that

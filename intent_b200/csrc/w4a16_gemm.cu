@@ -1,6 +1,343 @@
-// placeholder until the tcgen05 kernel lands
+// W4A16 prefill GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   Y[m, n] = T( sum_k f32(X[m, k]) * f32( T( (q[k, n] - 8) * S[k / G, n] ) ) )
+//
+// Program: weight_only_int4_matmul, reference kernel body
+// examples/kernels/contraction/weight_only_int4.py:18-51 (the dequantised weight is
+// rounded to the activation type before the f32-accumulated product, as at :42-47).
+//
+// One persistent CTA per SM walks 128 x 256 output tiles; 14 warps in four roles:
+//   warp 0        TMA producer: per 64-wide k block one 128B-swizzled box of X
+//                 (128 rows x 64 k), one box of packed weights (8 packed rows x 256
+//                 columns, raw int32) and one box of scales, 4 stages deep.
+//   warps 6..13   dequantisers: thread n owns weight column n of the tile; per k block
+//                 it expands its 8 packed words to 64 values of T with the magic-number
+//                 trick (prmt + lop3, exact subtract, one rounding multiply by the
+//                 scale) and writes them as the 128-byte row n of the K-major,
+//                 128B-swizzled B operand tile (3 stages).
+//   warp 1        MMA issuer: one thread issues four tcgen05.mma (M128 N256 K16,
+//                 kind::f16, f32 accumulation in TMEM) per k block and commits to the
+//                 mbarriers that free the stages.
+//   warps 2..5    epilogue: tcgen05.ld the accumulator (each warp its 32-lane TMEM
+//                 quadrant), convert to T, store.  Two accumulators (2 x 256 TMEM
+//                 columns) let the epilogue of a tile overlap the next tile's MMAs.
+// Every wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT and the
+// CTA drains and frees its TMEM.
+#include <type_traits>
+
 #include "common.cuh"
+#include "tma.cuh"
+#include "umma.cuh"
+
 namespace ib200 {
-int w4a16_gemm_f16(View2, View2, View2, View2, int, int, cudaStream_t) { return INTENT_B200_ERR_UNSUPPORTED; }
-int w4a16_gemm_bf16(View2, View2, View2, View2, int, int, cudaStream_t) { return INTENT_B200_ERR_UNSUPPORTED; }
+
+__device__ int g_w4a16_gemm_status = 0;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int LOAD_STAGES = 4, B_STAGES = 3;
+constexpr int A_BYTES = BM * BK * 2;         // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;         // 32 KiB
+constexpr int RAW_BYTES = (BK / 8) * BN * 4; // 8 KiB
+constexpr int SCALE_BYTES = 1024;            // up to 2 rows x 256 columns x 2 bytes
+constexpr int DEQUANT_WARPS = 8;
+constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
+constexpr int SMEM_BYTES = 1024 + LOAD_STAGES * (A_BYTES + RAW_BYTES + SCALE_BYTES) + B_STAGES * B_BYTES + 256;
+
+struct GemmParams {
+  void* y;
+  int M, N, K;
+  int k_blocks;          // ceil(K / 64)
+  int m_tiles, n_tiles;
+  int group_size;
+  int scale_rows;        // scale rows per k block: max(1, 64 / G)
+  int twos_complement;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_s, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = smem_a + LOAD_STAGES * A_BYTES;
+  const uint32_t smem_raw_w = smem_b + B_STAGES * B_BYTES;
+  const uint32_t smem_sc = smem_raw_w + LOAD_STAGES * RAW_BYTES;
+  const uint32_t bars = smem_sc + LOAD_STAGES * SCALE_BYTES;
+  // barrier layout (8 bytes each)
+  const uint32_t full_load = bars;                         // [LOAD_STAGES] TMA bytes landed
+  const uint32_t empty_load = full_load + 8 * LOAD_STAGES; // [LOAD_STAGES] MMA done with A + dequantisers done with raw
+  const uint32_t full_b = empty_load + 8 * LOAD_STAGES;    // [B_STAGES] dequantised tile written
+  const uint32_t empty_b = full_b + 8 * B_STAGES;          // [B_STAGES] MMA done with it
+  const uint32_t tmem_full = empty_b + 8 * B_STAGES;       // [2] accumulator complete
+  const uint32_t tmem_empty = tmem_full + 16;              // [2] accumulator drained
+  const uint32_t tmem_slot = tmem_empty + 16;              // TMEM base address written by tcgen05.alloc
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + (tmem_slot - base));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int tiles = p.m_tiles * p.n_tiles;
+
+  if (tid == 0) {
+    for (int s = 0; s < LOAD_STAGES; ++s) {
+      mbar_init(full_load + 8 * s, 1);
+      mbar_init(empty_load + 8 * s, 1 + DEQUANT_WARPS);
+    }
+    for (int s = 0; s < B_STAGES; ++s) {
+      mbar_init(full_b + 8 * s, DEQUANT_WARPS);
+      mbar_init(empty_b + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tmem_full + 8 * s, 1);
+      mbar_init(tmem_empty + 8 * s, 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % LOAD_STAGES, phase = (it / LOAD_STAGES) & 1;
+          if (!mbar_wait(empty_load + 8 * s, phase ^ 1)) { ok = false; break; }
+          const uint32_t bar = full_load + 8 * s;
+          mbar_expect_tx(bar, A_BYTES + RAW_BYTES + uint32_t(p.scale_rows) * BN * 2);
+          tma_load_2d(smem_a + s * A_BYTES, &map_x, kb * BK, m_tile * BM, bar);
+          tma_load_2d(smem_raw_w + s * RAW_BYTES, &map_w, n_tile * BN, kb * (BK / 8), bar);
+          tma_load_2d(smem_sc + s * SCALE_BYTES, &map_s, n_tile * BN, (kb * BK) / p.group_size, bar);
+        }
+      }
+      if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t fmt = std::is_same<T, __half>::value ? 0u : 1u;
+      constexpr uint32_t idesc = umma_idesc(1, fmt, fmt, 0, 0, BM, BN);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t acc = local & 1;
+        if (!mbar_wait(tmem_empty + 8 * acc, ((local >> 1) & 1) ^ 1)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % LOAD_STAGES, t = it % B_STAGES;
+          if (!mbar_wait(full_load + 8 * s, (it / LOAD_STAGES) & 1) ||
+              !mbar_wait(full_b + 8 * t, (it / B_STAGES) & 1)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint64_t desc_a = umma_desc_k_major_sw128(smem_a + s * A_BYTES);
+          const uint64_t desc_b = umma_desc_k_major_sw128(smem_b + t * B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements of 2 bytes = 32 bytes = 2 descriptor units
+            umma_f16(tmem_d, desc_a + uint64_t(2 * kk), desc_b + uint64_t(2 * kk), idesc, (kb | kk) != 0);
+          umma_commit(empty_load + 8 * s);
+          umma_commit(empty_b + 8 * t);
+        }
+        if (ok) umma_commit(tmem_full + 8 * acc);
+      }
+      if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+    }
+  } else if (warp < 6) {
+    // ------------------------------ epilogue -----------------------------------
+    const int quadrant = warp & 3;  // TMEM lanes 32*quadrant .. +31 are the ones this warp may read
+    uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+      const uint32_t acc = local & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full + 8 * acc, (local >> 1) & 1))) {
+        if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = m_tile * BM + quadrant * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quadrant * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_load_32x32(taddr + c * 32, v);
+        tmem_load_wait();
+        const int col = n_tile * BN + c * 32;
+        if (row < p.M) {
+          uint16_t* dst = y + size_t(row) * p.N + col;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (col + q * 8 < p.N) {  // N is a multiple of 8
+              uint4 o;
+              o.x = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 0]))) |
+                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 1]))) << 16);
+              o.y = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 2]))) |
+                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 3]))) << 16);
+              o.z = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 4]))) |
+                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 5]))) << 16);
+              o.w = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 6]))) |
+                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 7]))) << 16);
+              *reinterpret_cast<uint4*>(dst + q * 8) = o;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+    }
+  } else {
+    // ------------------------------ dequantisers --------------------------------
+    const int n = tid - 6 * 32;  // weight column of the tile owned by this thread, 0..255
+    const uint32_t magic = Elem<T>::kMagic2 ^ (p.twos_complement ? 0x00080008u : 0u);
+    const uint32_t row_off = uint32_t(n) * 128u;
+    const uint32_t swz = uint32_t(n & 7);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        const uint32_t s = it % LOAD_STAGES, t = it % B_STAGES;
+        ok = mbar_wait(full_load + 8 * s, (it / LOAD_STAGES) & 1) &&
+             mbar_wait(empty_b + 8 * t, ((it / B_STAGES) & 1) ^ 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t raw = smem_raw_w + s * RAW_BYTES + uint32_t(n) * 4u;
+        const uint32_t sc = smem_sc + s * SCALE_BYTES + uint32_t(n) * 2u;
+        const uint32_t dst = smem_b + t * B_BYTES + row_off;
+        uint32_t s_lo, s_hi;  // scale of k 0..31 and of k 32..63 of this block, duplicated into both halves
+        {
+          uint16_t a, b;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(a) : "r"(sc));
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b) : "r"(sc + (p.scale_rows > 1 ? BN * 2 : 0)));
+          s_lo = uint32_t(a) | (uint32_t(a) << 16);
+          s_hi = uint32_t(b) | (uint32_t(b) << 16);
+        }
+#pragma unroll
+        for (int r = 0; r < BK / 8; ++r) {
+          uint32_t w;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(raw + r * BN * 4));
+          const uint32_t w4 = w >> 4;
+          const uint32_t scale2 = r < 4 ? s_lo : s_hi;
+          uint4 o;
+          o.x = lop3_and_xor_u32(prmt(w, w4, 0x0400), 0x000F000Fu, magic);  // (k0, k1)
+          o.y = lop3_and_xor_u32(prmt(w, w4, 0x0501), 0x000F000Fu, magic);  // (k2, k3)
+          o.z = lop3_and_xor_u32(prmt(w, w4, 0x0602), 0x000F000Fu, magic);  // (k4, k5)
+          o.w = lop3_and_xor_u32(prmt(w, w4, 0x0703), 0x000F000Fu, magic);  // (k6, k7)
+          o.x = Elem<T>::mul2(Elem<T>::sub2(o.x, Elem<T>::kBias2), scale2);
+          o.y = Elem<T>::mul2(Elem<T>::sub2(o.y, Elem<T>::kBias2), scale2);
+          o.z = Elem<T>::mul2(Elem<T>::sub2(o.z, Elem<T>::kBias2), scale2);
+          o.w = Elem<T>::mul2(Elem<T>::sub2(o.w, Elem<T>::kBias2), scale2);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + ((uint32_t(r) ^ swz) << 4)), "r"(o.x),
+                       "r"(o.y), "r"(o.z), "r"(o.w)
+                       : "memory");
+        }
+        fence_proxy_async();  // the tensor core reads this tile through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(full_b + 8 * t);
+          mbar_arrive(empty_load + 8 * s);
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
+int device_sms() {
+  static int sms = [] {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return value;
+  }();
+  return sms;
+}
+
+template <typename T>
+int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cudaStream_t stream) {
+  const int64_t M = x.d0, K = x.d1, N = w.d1;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
+  if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
+  if (K % group_size != 0 || w.d0 * 8 != K || s.d0 * group_size != K || s.d1 != N || y.d0 != M || y.d1 != N)
+    return INTENT_B200_ERR_SHAPE;
+  if (M == 0 || N == 0) return INTENT_B200_OK;
+  if (!x.p || !w.p || !s.p || !y.p) return INTENT_B200_ERR_NULL;
+  if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(y)) return INTENT_B200_ERR_LAYOUT;
+  if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
+  if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
+  const int sms = device_sms();
+  if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
+
+  const CUtensorMapDataType type =
+      std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  GemmParams p{};
+  p.y = y.p;
+  p.M = int(M);
+  p.N = int(N);
+  p.K = int(K);
+  p.k_blocks = int((K + BK - 1) / BK);
+  p.m_tiles = int((M + BM - 1) / BM);
+  p.n_tiles = int((N + BN - 1) / BN);
+  p.group_size = group_size;
+  p.scale_rows = group_size >= BK ? 1 : BK / group_size;
+  p.twos_complement = zero_point == -1 ? 1 : 0;
+
+  CUtensorMap map_x, map_w, map_s;
+  if (!make_tensor_map_2d(&map_x, type, x.p, uint64_t(M), uint64_t(K), uint64_t(K) * 2, BM, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, w.p, uint64_t(K / 8), uint64_t(N), uint64_t(N) * 4,
+                          BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+      !make_tensor_map_2d(&map_s, type, s.p, uint64_t(K / group_size), uint64_t(N), uint64_t(N) * 2,
+                          uint32_t(p.scale_rows), BN, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return INTENT_B200_ERR_UNSUPPORTED;
+
+  auto kernel = w4a16_gemm_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_status(e);
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_x, map_w, map_s, p);
+  note_launch();
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace ib200
+
+namespace ib200 {
+int w4a16_gemm_f16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream) {
+  return run<__half>(x, w, s, y, g, zp, stream);
+}
+int w4a16_gemm_bf16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream) {
+  return run<__nv_bfloat16>(x, w, s, y, g, zp, stream);
+}
+}  // namespace ib200
+
+// Reads (and clears) the status word of the tensor-core W4A16 kernel; synchronises the device.
+extern "C" int intent_b200_w4a16_gemm_device_status(void) {
+  int value = 0, zero = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return ib200::cuda_status(e);
+  e = cudaMemcpyFromSymbol(&value, ib200::g_w4a16_gemm_status, sizeof(int));
+  if (e != cudaSuccess) return ib200::cuda_status(e);
+  if (value != 0) cudaMemcpyToSymbol(ib200::g_w4a16_gemm_status, &zero, sizeof(int));
+  return value;
 }

@@ -1,0 +1,80 @@
+"""W4A16 tensor-core (tcgen05) GEMM parity through the artifact surface.
+
+Tolerance: the benchmark criterion max|y - ref| <= 2e-2 * max|ref| against the
+f32-accumulate dequant oracle; the kernel rounds the dequantised weight to the
+activation type first (the reference kernel body's order), which the second
+oracle form reproduces to accumulation-order noise.
+"""
+import pytest
+import torch
+
+import intent_b200 as ib
+import oracle
+from intent_b200.runtime import native
+from conftest import load_golden, max_abs_rel
+
+pytestmark = pytest.mark.gpu
+
+
+def _compile(dtype, group, zero_point, kernel="gemm"):
+    return ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(0),
+                      constexprs={"GROUP_SIZE": group, "ZERO_POINT": zero_point, "ACT_DTYPE": dtype,
+                                  "KERNEL": kernel})
+
+
+def _device_status():
+    lib = native.library()
+    return lib.intent_b200_w4a16_gemm_device_status()
+
+
+@pytest.mark.parametrize("dtype,M,K,N,group", [
+    (torch.bfloat16, 128, 256, 256, 128),
+    (torch.float16, 128, 256, 256, 128),
+    (torch.bfloat16, 200, 512, 264, 128),      # ragged M and N tiles
+    (torch.float16, 77, 1024, 512, 64),
+    (torch.bfloat16, 300, 384, 256, 32),       # two scale rows per k block, K not a multiple of 128
+    (torch.bfloat16, 1024, 4096, 1024, 128),
+    (torch.float16, 16, 4096, 4096, 128),      # the CPU-runnable benchmark configuration forced onto tensor cores
+])
+def test_gemm_matches_oracle(cuda_device, dtype, M, K, N, group):
+    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=dtype, group_size=group, seed=5)
+    artifact = _compile("f16" if dtype == torch.float16 else "bf16", group, 8)
+    out = artifact.run(x.to(cuda_device), p.to(cuda_device), s.to(cuda_device))
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=group, zero_point=8)
+    rounded = oracle.weight_only_int4_matmul_rounded(x, p, s, group_size=group, zero_point=8)
+    assert out.dtype == dtype and out.shape == (M, N)
+    assert max_abs_rel(out.cpu(), ref) <= 2e-2
+    assert max_abs_rel(out.cpu(), rounded) <= (2e-3 if dtype == torch.float16 else 1.6e-2)
+
+
+def test_gemm_golden_reference_layout(cuda_device):
+    """Reference constants (group 64, two's-complement nibbles, f16), M = 33 golden vector."""
+    g = load_golden("w4a16_wide")
+    for kernel in ("gemm", "auto"):
+        artifact = _compile("f16", 64, "twos_complement", kernel)
+        out = artifact.run(g["activation"].to(cuda_device), g["packed"].to(cuda_device), g["scales"].to(cuda_device))
+        torch.cuda.synchronize()
+        assert (out.cpu().float() - g["output"].float()).abs().max() <= 4e-2      # the reference's own tolerance
+        assert max_abs_rel(out.cpu(), g["output"]) <= 2e-2
+    assert _device_status() == 0
+
+
+def test_gemm_full_size_prefill_rows(cuda_device):
+    """Benchmark configuration 2 (8192^3, bf16): rows sampled across M tiles against the oracle,
+    plus linearity in X (a size-independent property): f(2x) == 2 f(x) exactly."""
+    M = K = N = 8192
+    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=128, seed=0)
+    artifact = _compile("bf16", 128, 8)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    out = artifact.run(xd, pd, sd)
+    doubled = artifact.run(xd * 2, pd, sd)
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    assert torch.equal(doubled, out * 2)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 6000, 8191])
+    ref = oracle.weight_only_int4_matmul(x[rows], p, s, group_size=128, zero_point=8)
+    assert max_abs_rel(out[rows.to(cuda_device)].cpu(), ref) <= 2e-2
+    # every tile was written: no element is left at the fill value
+    assert torch.isfinite(out).all()
