@@ -109,6 +109,24 @@ INTENT_B200_API int intent_b200_w4a16_gemv_grid(int32_t ctas);
 INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
 
 /* ------------------------------------------------------------------------
+ * gemm_i8: C[m,n] = i32(sum_k A[m,k] * B[k,n]) + bias[n], wrapping int32.
+ * Replaces the provider lowering of examples/kernels/contraction/gemm.py:29-39.
+ *   a0 A [M,K] i8 (K contiguous)   a1 B [K,N] i8 (N contiguous)
+ *   a2 bias [N] i32 (pointer may be NULL = zero bias)   a3 C [M,N] i32
+ * K and N must be multiples of 16.
+ * ------------------------------------------------------------------------ */
+INTENT_B200_API int intent_b200_gemm_i8(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW1(a2),
+                                        INTENT_B200_VIEW2(a3), void* stream);
+/* w8a8_gemm: Y[m,n] = bf16( (f32(acc[m,n]) * sa[m]) * sb[n] ) on the exact int32
+ * accumulator of gemm_i8 (the benchmark's per-token x per-channel epilogue; nearest
+ * reference precedent: the per-channel scale of quantized_gemm, gemm.py:83-106).
+ *   a0 A [M,K] i8   a1 B [K,N] i8   a2 sa [M] f32   a3 sb [N] f32   a4 Y [M,N] bf16 */
+INTENT_B200_API int intent_b200_w8a8_gemm_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW1(a2),
+                                               INTENT_B200_VIEW1(a3), INTENT_B200_VIEW2(a4), void* stream);
+/* Status word of the int8 tensor-core kernel (see intent_b200_w4a16_gemm_device_status). */
+INTENT_B200_API int intent_b200_i8_gemm_device_status(void);
+
+/* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.
  * This entry has no counterpart in the reference.  It exists for callers that
  * cannot allocate device memory on behalf of the library: a host that runs

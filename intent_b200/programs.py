@@ -90,4 +90,54 @@ weight_only_int4_matmul = KernelDefinition(
     summary="Y = X @ dequant(int4 packed along K, per-group scales); f32 accumulation",
 )
 
-ALL = {d.name: d for d in (weight_only_int4_matmul,)}
+
+
+# ---------------------------------------------------------------------------------
+# gemm_i8 and the scaled W8A8 form
+# ---------------------------------------------------------------------------------
+def _i8_rules():
+    return (
+        _rule(lambda d: d["K"] % 16 == 0 and d["N"] % 16 == 0,
+              "this backend requires K and N to be multiples of 16 for int8 operands"),
+    )
+
+
+def _lower_gemm_i8(constants, device):
+    interface = PublicInterface((
+        ViewParameter(0, "a", dtypes.i8, ("M", "K"), IN),
+        ViewParameter(1, "b", dtypes.i8, ("K", "N"), IN),
+        ViewParameter(2, "bias", dtypes.i32, ("N",), IN),
+        ViewParameter(3, "c", dtypes.i32, ("M", "N"), OUT),
+    ), dimension_rules=_i8_rules())
+    return NativeProgram(interface=interface, entry_name="intent_b200_gemm_i8", device=device,
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+gemm_i8 = KernelDefinition(
+    name="gemm_i8", constexprs={}, lower=_lower_gemm_i8,
+    reference="examples/kernels/contraction/gemm.py:29-39",
+    summary="C = i32(A @ B) + bias, exact wrapping integers",
+)
+
+
+def _lower_w8a8(constants, device):
+    if dtypes.dtype(constants["OUT_DTYPE"]) is not dtypes.bf16:
+        raise CompilationStageError("provider_native_compilation", "OUT_DTYPE must be bf16")
+    interface = PublicInterface((
+        ViewParameter(0, "a", dtypes.i8, ("M", "K"), IN),
+        ViewParameter(1, "b", dtypes.i8, ("K", "N"), IN),
+        ViewParameter(2, "a_scales", dtypes.f32, ("M",), IN),
+        ViewParameter(3, "b_scales", dtypes.f32, ("N",), IN),
+        ViewParameter(4, "output", dtypes.bf16, ("M", "N"), OUT),
+    ), dimension_rules=_i8_rules())
+    return NativeProgram(interface=interface, entry_name="intent_b200_w8a8_gemm_bf16", device=device,
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+w8a8_gemm = KernelDefinition(
+    name="w8a8_gemm", constexprs={"OUT_DTYPE": "bf16"}, lower=_lower_w8a8,
+    reference="examples/kernels/contraction/gemm.py:29-39 (+ per-channel scale precedent :83-106)",
+    summary="Y = bf16((i32(A @ B) * sa[m]) * sb[n])",
+)
+
+ALL = {d.name: d for d in (weight_only_int4_matmul, gemm_i8, w8a8_gemm)}
