@@ -127,6 +127,57 @@ INTENT_B200_API int intent_b200_w8a8_gemm_bf16(INTENT_B200_VIEW2(a0), INTENT_B20
 INTENT_B200_API int intent_b200_i8_gemm_device_status(void);
 
 /* ------------------------------------------------------------------------
+ * MoE router, route alignment, permutation and grouped int4 contractions.
+ * Integer outputs are bit-exact and deterministic.
+ * ------------------------------------------------------------------------ */
+/* Top-2 experts per token by logit, ties to the lower expert id (strict '>' insertion,
+ * examples/kernels/sampling/top_k.py:10-33), and their f32 softmax probabilities
+ * (examples/kernels/normalization/softmax.py:23-37).
+ *   a0 logits [T,E] f32 -> a1 ids [T,2] i32, a2 weights [T,2] f32 */
+INTENT_B200_API int intent_b200_moe_route_top2(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                               void* stream);
+/* examples/kernels/routing/moe_align.py:14-29: a0 topk_ids [T,K] i32, a1 expert_counts [E] i32 (accumulated) */
+INTENT_B200_API int intent_b200_moe_count_routes(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), void* stream);
+/* moe_align.py:32-49: a0 counts [E] -> a1 offsets [E+1] (block-padded exclusive prefix), a2 total_padded [1] */
+INTENT_B200_API int intent_b200_moe_prefix_routes(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                  int32_t block_size, void* stream);
+/* moe_align.py:52-73: a0 topk_ids [T,K], a1 offsets [E+1], a2 cursors [E] (InOut: += count),
+ * a3 sorted_route_ids [capacity] (InOut).  Stable: ascending route id inside each expert span (the order of
+ * the reference's torch implementation, cpu_runtime.py:1081-1097); span padding is set to T*K. */
+INTENT_B200_API int intent_b200_moe_scatter_routes(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                   INTENT_B200_VIEW1(a3), void* stream);
+/* moe_align.py:76-86: a0 offsets [E+1] -> a1 expert_blocks [B] (blocks past the padded total are not written) */
+INTENT_B200_API int intent_b200_moe_mark_expert_blocks(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1),
+                                                       int32_t block_size, void* stream);
+/* Inverse of the alignment: a0 sorted_route_ids [capacity], a1 total_padded [1] -> a2 route_positions [R] */
+INTENT_B200_API int intent_b200_moe_route_positions(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1),
+                                                    INTENT_B200_VIEW1(a2), void* stream);
+/* Token rows in expert-sorted order (the I.gather of examples/kernels/ragged/moe.py:34-36):
+ * a0 x [T,H] 16-bit, a1 sorted_route_ids [P], a2 total_padded [1] -> a3 rows [P,H]; padding rows are zero. */
+INTENT_B200_API int intent_b200_moe_gather_rows(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                INTENT_B200_VIEW2(a3), int32_t top_k, void* stream);
+/* Grouped int4 contractions over expert-sorted rows padded to 128 per expert (tcgen05 kernel of
+ * weight_only_int4_matmul with a per-block expert; reference programs
+ * examples/kernels/ragged/grouped_gemm.py:42-70 and examples/kernels/ragged/moe.py:37-47):
+ *   a0 rows [P,K] T, a1 expert_blocks [B] i32, a2 total_padded [1] i32, a3 packed [E,K/8,WN] i32,
+ *   a4 scales [E,K/G,WN] T, a5 output.
+ * upgate_silu: WN = 2*I, columns 0..I-1 gate and I..2I-1 up (I a multiple of 128);
+ *              output [P,I] T = T(silu(gate) * up), f32 evaluation, one rounding.
+ * down_f32:    output [P,WN] f32. */
+#define INTENT_B200_GROUPED_SLOTS                                                                          \
+  INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3),              \
+      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point, void *stream
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_bf16(INTENT_B200_GROUPED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_f16(INTENT_B200_GROUPED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_bf16(INTENT_B200_GROUPED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_f16(INTENT_B200_GROUPED_SLOTS);
+/* Weighted combine (the scatter_reduce add of moe.py:48-53, made order-fixed):
+ * y[t,:] += sum over choices c in order of weights[t,c] * rows[route_positions[t*K + c], :]
+ *   a0 rows [P,H] f32, a1 route_positions [T*K] i32, a2 weights [T,K] f32, a3 y [T,H] f32 (InOut) */
+INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW2(a2),
+                                            INTENT_B200_VIEW2(a3), void* stream);
+
+/* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.
  * This entry has no counterpart in the reference.  It exists for callers that
  * cannot allocate device memory on behalf of the library: a host that runs

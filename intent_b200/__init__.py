@@ -1,6 +1,6 @@
 """intent_b200: sm_100a quantized-contraction programs behind IntentDSL's
 artifact call surface (``run`` / ``__call__`` / ``prepare`` / ``as_torch_op``)."""
-from . import dtypes, programs, runtime, workloads  # noqa: F401
+from . import dtypes, moe, programs, runtime, workloads  # noqa: F401
 from .compiler import KernelDefinition, compile  # noqa: F401
 from .errors import CompilationStageError  # noqa: F401
 from .runtime.artifact import CompiledArtifact, NativeObservation, PreparedCall  # noqa: F401

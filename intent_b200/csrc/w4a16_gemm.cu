@@ -23,6 +23,15 @@
 //                 columns) let the epilogue of a tile overlap the next tile's MMAs.
 // Every wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT and the
 // CTA drains and frees its TMEM.
+//
+// The same kernel serves the MoE grouped contractions (reference programs
+// examples/kernels/ragged/grouped_gemm.py:11-70 and examples/kernels/ragged/moe.py:12-53 with
+// int4 expert weights): rows are sorted by expert and padded to 128 per expert, so an M tile
+// belongs to one expert, read from the block -> expert table of the route alignment; the
+// number of M tiles is read from device memory (no host round trip).
+//   MODE 1  up|gate projection: the N tile is 128 gate columns + the matching 128 up columns,
+//           the epilogue writes T( silu(gate) * up ).
+//   MODE 2  down projection with f32 output rows (combined per token by a later kernel).
 #include <type_traits>
 
 #include "common.cuh"
@@ -53,9 +62,15 @@ struct GemmParams {
   int group_size;
   int scale_rows;        // scale rows per k block: max(1, 64 / G)
   int twos_complement;
+  int second_box_offset;     // column distance of the second 128-column weight box (128, or I for up|gate)
+  int out_cols;              // columns of the output matrix
+  const int* total_rows;     // grouped modes: device pointer to the padded row count (multiple of 128)
+  const int* tile_expert;    // grouped modes: expert of each 128-row block
 };
 
-template <typename T>
+constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
+
+template <typename T, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const __grid_constant__ CUtensorMap map_s, const GemmParams p) {
@@ -81,7 +96,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int m_tiles = MODE == MODE_DENSE ? p.m_tiles : min(p.m_tiles, (*p.total_rows + BM - 1) / BM);
+  const int tiles = m_tiles * p.n_tiles;
 
   if (tid == 0) {
     for (int s = 0; s < LOAD_STAGES; ++s) {
@@ -110,15 +126,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+        const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[m_tile];
+        // weight columns of the two 128-wide boxes of this N tile
+        const int col0 = MODE == MODE_UPGATE_SILU ? n_tile * 128 : n_tile * BN;
+        const int col1 = col0 + p.second_box_offset;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % LOAD_STAGES, phase = (it / LOAD_STAGES) & 1;
           if (!mbar_wait(empty_load + 8 * s, phase ^ 1)) { ok = false; break; }
           const uint32_t bar = full_load + 8 * s;
+          const int scale_row = (kb * BK) / p.group_size;
           mbar_expect_tx(bar, A_BYTES + RAW_BYTES + uint32_t(p.scale_rows) * BN * 2);
           tma_load_2d(smem_a + s * A_BYTES, &map_x, kb * BK, m_tile * BM, bar);
-          tma_load_2d(smem_raw_w + s * RAW_BYTES, &map_w, n_tile * BN, kb * (BK / 8), bar);
-          tma_load_2d(smem_sc + s * SCALE_BYTES, &map_s, n_tile * BN, (kb * BK) / p.group_size, bar);
+          tma_load_3d(smem_raw_w + s * RAW_BYTES, &map_w, col0, kb * (BK / 8), expert, bar);
+          tma_load_3d(smem_raw_w + s * RAW_BYTES + RAW_BYTES / 2, &map_w, col1, kb * (BK / 8), expert, bar);
+          tma_load_3d(smem_sc + s * SCALE_BYTES, &map_s, col0, scale_row, expert, bar);
+          tma_load_3d(smem_sc + s * SCALE_BYTES + p.scale_rows * 256, &map_s, col1, scale_row, expert, bar);
         }
       }
       if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -158,7 +181,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
     uint32_t local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-      const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+      const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
       const uint32_t acc = local & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(tmem_full + 8 * acc, (local >> 1) & 1))) {
         if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -167,27 +190,66 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       tcgen05_fence_after();
       const int row = m_tile * BM + quadrant * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quadrant * 32) << 16);
+      if (MODE == MODE_UPGATE_SILU) {
+        // accumulator columns 0..127 = gate, 128..255 = the matching up columns
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_load_32x32(taddr + c * 32, v);
-        tmem_load_wait();
-        const int col = n_tile * BN + c * 32;
-        if (row < p.M) {
-          uint16_t* dst = y + size_t(row) * p.N + col;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t gate[32], up[32];
+          tmem_load_32x32(taddr + c * 32, gate);
+          tmem_load_32x32(taddr + 128 + c * 32, up);
+          tmem_load_wait();
+          const int col = n_tile * 128 + c * 32;
+          if (row < p.M) {
+            uint16_t* dst = y + size_t(row) * p.out_cols + col;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (col + q * 8 < p.N) {  // N is a multiple of 8
-              uint4 o;
-              o.x = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 0]))) |
-                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 1]))) << 16);
-              o.y = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 2]))) |
-                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 3]))) << 16);
-              o.z = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 4]))) |
-                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 5]))) << 16);
-              o.w = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 6]))) |
-                    (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 7]))) << 16);
-              *reinterpret_cast<uint4*>(dst + q * 8) = o;
+            for (int q = 0; q < 4; ++q) {
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float h[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const float gv = __uint_as_float(gate[8 * q + 2 * j + e]);
+                  const float uv = __uint_as_float(up[8 * q + 2 * j + e]);
+                  h[e] = gv * (1.0f / (1.0f + __expf(-gv))) * uv;  // silu(gate) * up in f32, one rounding
+                }
+                o[j] = uint32_t(Elem<T>::from_float(h[0])) | (uint32_t(Elem<T>::from_float(h[1])) << 16);
+              }
+              if (col + q * 8 < p.out_cols) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_load_32x32(taddr + c * 32, v);
+          tmem_load_wait();
+          const int col = n_tile * BN + c * 32;
+          if (row < p.M) {
+            if (MODE == MODE_GROUPED_F32) {
+              float* dst = reinterpret_cast<float*>(p.y) + size_t(row) * p.out_cols + col;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (col + q * 4 < p.out_cols)
+                  *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              uint16_t* dst = y + size_t(row) * p.out_cols + col;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (col + q * 8 < p.out_cols) {  // the column count is a multiple of 8
+                  uint4 o;
+                  o.x = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 0]))) |
+                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 1]))) << 16);
+                  o.y = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 2]))) |
+                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 3]))) << 16);
+                  o.z = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 4]))) |
+                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 5]))) << 16);
+                  o.w = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 6]))) |
+                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 7]))) << 16);
+                  *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                }
+              }
             }
           }
         }
@@ -211,21 +273,23 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
              mbar_wait(empty_b + 8 * t, ((it / B_STAGES) & 1) ^ 1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint32_t raw = smem_raw_w + s * RAW_BYTES + uint32_t(n) * 4u;
-        const uint32_t sc = smem_sc + s * SCALE_BYTES + uint32_t(n) * 2u;
+        // the tile's 256 columns arrive as two boxes of 128 columns
+        const uint32_t raw = smem_raw_w + s * RAW_BYTES + uint32_t(n >> 7) * (RAW_BYTES / 2) + uint32_t(n & 127) * 4u;
+        const uint32_t sc = smem_sc + s * SCALE_BYTES + uint32_t(n >> 7) * uint32_t(p.scale_rows * 256) +
+                            uint32_t(n & 127) * 2u;
         const uint32_t dst = smem_b + t * B_BYTES + row_off;
         uint32_t s_lo, s_hi;  // scale of k 0..31 and of k 32..63 of this block, duplicated into both halves
         {
           uint16_t a, b;
           asm volatile("ld.shared.u16 %0, [%1];" : "=h"(a) : "r"(sc));
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b) : "r"(sc + (p.scale_rows > 1 ? BN * 2 : 0)));
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b) : "r"(sc + (p.scale_rows > 1 ? 256 : 0)));
           s_lo = uint32_t(a) | (uint32_t(a) << 16);
           s_hi = uint32_t(b) | (uint32_t(b) << 16);
         }
 #pragma unroll
         for (int r = 0; r < BK / 8; ++r) {
           uint32_t w;
-          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(raw + r * BN * 4));
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(raw + r * 512));
           const uint32_t w4 = w >> 4;
           const uint32_t scale2 = r < 4 ? s_lo : s_hi;
           uint4 o;
@@ -271,6 +335,52 @@ int device_sms() {
   return sms;
 }
 
+// x: [rows, K] activations; w: [E, K/8, WN] packed; s: [E, K/G, WN] scales; out: [rows, out_cols].
+template <typename T, int MODE>
+int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t experts, int64_t WN,
+                void* out, int64_t out_cols, int group_size, int zero_point, const int* total_rows,
+                const int* tile_expert, cudaStream_t stream) {
+  const int sms = device_sms();
+  if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
+  const CUtensorMapDataType type =
+      std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  GemmParams p{};
+  p.y = out;
+  p.M = int(rows);
+  p.N = int(WN);
+  p.K = int(K);
+  p.k_blocks = int((K + BK - 1) / BK);
+  p.m_tiles = int((rows + BM - 1) / BM);
+  p.n_tiles = MODE == MODE_UPGATE_SILU ? int(out_cols / 128) : int((out_cols + BN - 1) / BN);
+  p.group_size = group_size;
+  p.scale_rows = group_size >= BK ? 1 : BK / group_size;
+  p.twos_complement = zero_point == -1 ? 1 : 0;
+  p.second_box_offset = MODE == MODE_UPGATE_SILU ? int(out_cols) : 128;
+  p.out_cols = int(out_cols);
+  p.total_rows = total_rows;
+  p.tile_expert = tile_expert;
+
+  CUtensorMap map_x, map_w, map_s;
+  if (!make_tensor_map_2d(&map_x, type, x, uint64_t(rows), uint64_t(K), uint64_t(K) * 2, BM, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_3d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, w, uint64_t(experts), uint64_t(K / 8), uint64_t(WN),
+                          uint64_t(WN) * 4, uint64_t(K / 8) * uint64_t(WN) * 4, BK / 8, 128,
+                          CU_TENSOR_MAP_SWIZZLE_NONE) ||
+      !make_tensor_map_3d(&map_s, type, s, uint64_t(experts), uint64_t(K / group_size), uint64_t(WN),
+                          uint64_t(WN) * 2, uint64_t(K / group_size) * uint64_t(WN) * 2, uint32_t(p.scale_rows), 128,
+                          CU_TENSOR_MAP_SWIZZLE_NONE))
+    return INTENT_B200_ERR_UNSUPPORTED;
+
+  auto kernel = w4a16_gemm_kernel<T, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_status(e);
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_x, map_w, map_s, p);
+  note_launch();
+  return launch_status();
+}
+
 template <typename T>
 int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cudaStream_t stream) {
   const int64_t M = x.d0, K = x.d1, N = w.d1;
@@ -283,40 +393,32 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
   if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(y)) return INTENT_B200_ERR_LAYOUT;
   if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
   if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
-  const int sms = device_sms();
-  if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
+  return launch_gemm<T, MODE_DENSE>(x.p, M, K, w.p, s.p, 1, N, y.p, N, group_size, zero_point, nullptr, nullptr,
+                                    stream);
+}
 
-  const CUtensorMapDataType type =
-      std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  GemmParams p{};
-  p.y = y.p;
-  p.M = int(M);
-  p.N = int(N);
-  p.K = int(K);
-  p.k_blocks = int((K + BK - 1) / BK);
-  p.m_tiles = int((M + BM - 1) / BM);
-  p.n_tiles = int((N + BN - 1) / BN);
-  p.group_size = group_size;
-  p.scale_rows = group_size >= BK ? 1 : BK / group_size;
-  p.twos_complement = zero_point == -1 ? 1 : 0;
-
-  CUtensorMap map_x, map_w, map_s;
-  if (!make_tensor_map_2d(&map_x, type, x.p, uint64_t(M), uint64_t(K), uint64_t(K) * 2, BM, BK,
-                          CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, w.p, uint64_t(K / 8), uint64_t(N), uint64_t(N) * 4,
-                          BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-      !make_tensor_map_2d(&map_s, type, s.p, uint64_t(K / group_size), uint64_t(N), uint64_t(N) * 2,
-                          uint32_t(p.scale_rows), BN, CU_TENSOR_MAP_SWIZZLE_NONE))
+// Grouped contractions over expert-sorted, 128-padded rows.
+//   x [P, K]; tile_expert [>= P/128]; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; out [P, out_cols]
+template <typename T, int MODE>
+int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2 out, int group_size, int zero_point,
+                cudaStream_t stream) {
+  const int64_t P = x.d0, K = x.d1, E = w.d0, WN = w.d2;
+  const int64_t out_cols = MODE == MODE_UPGATE_SILU ? WN / 2 : WN;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
+  if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
+  if (K % group_size != 0 || w.d1 * 8 != K || s.d0 != E || s.d1 * group_size != K || s.d2 != WN || out.d0 != P ||
+      out.d1 != out_cols || total.d0 < 1 || tile_expert.d0 * BM < P)
+    return INTENT_B200_ERR_SHAPE;
+  if (P == 0 || WN == 0 || E == 0) return INTENT_B200_OK;
+  if (!x.p || !w.p || !s.p || !out.p || !tile_expert.p || !total.p) return INTENT_B200_ERR_NULL;
+  if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(out) || !contiguous(tile_expert))
+    return INTENT_B200_ERR_LAYOUT;
+  if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(out.p)) return INTENT_B200_ERR_LAYOUT;
+  if (K == 0 || WN % 8 != 0 || (MODE == MODE_UPGATE_SILU && (WN % 256 != 0)) ||
+      P > (1 << 24) || K > (1 << 24) || WN > (1 << 24))
     return INTENT_B200_ERR_UNSUPPORTED;
-
-  auto kernel = w4a16_gemm_kernel<T>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return cuda_status(e);
-  const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_x, map_w, map_s, p);
-  note_launch();
-  return launch_status();
+  return launch_gemm<T, MODE>(x.p, P, K, w.p, s.p, E, WN, out.p, out_cols, group_size, zero_point,
+                              static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
 }
 
 }  // namespace
@@ -341,3 +443,16 @@ extern "C" int intent_b200_w4a16_gemm_device_status(void) {
   if (value != 0) cudaMemcpyToSymbol(ib200::g_w4a16_gemm_status, &zero, sizeof(int));
   return value;
 }
+
+#define IB200_GROUPED_ENTRY(NAME, TYPE, MODE)                                                                   \
+  extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3), \
+                      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point,      \
+                      void* stream) {                                                                            \
+    return ib200::run_grouped<TYPE, ib200::MODE>(IB200_VIEW2_ARG(a0), IB200_VIEW1_ARG(a1), IB200_VIEW1_ARG(a2),  \
+                                                 IB200_VIEW3_ARG(a3), IB200_VIEW3_ARG(a4), IB200_VIEW2_ARG(a5),  \
+                                                 group_size, zero_point, static_cast<cudaStream_t>(stream));     \
+  }
+IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_bf16, __nv_bfloat16, MODE_UPGATE_SILU)
+IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_f16, __half, MODE_UPGATE_SILU)
+IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_bf16, __nv_bfloat16, MODE_GROUPED_F32)
+IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_f16, __half, MODE_GROUPED_F32)

@@ -1,0 +1,166 @@
+"""Host-side compositions of the MoE programs.
+
+``MoEAlignment`` mirrors the reference's multi-kernel host program
+(examples/programs/composition.py:98-174): the same four artifacts, the same
+workspace reset, the same ``run`` / ``run_into`` / ``prepare`` results
+``(sorted_route_ids, expert_blocks, total_padded)``.
+
+``MoEW4A16FFN`` chains router -> alignment -> row gather -> grouped up|gate
+projection with the SiLU gate -> grouped down projection -> weighted combine, the
+benchmark's MoE configuration (the reference's dense-weight counterpart is
+examples/kernels/ragged/moe.py:12-53).  Everything runs on the current stream;
+no step reads a device value back to the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from . import programs
+from .compiler import compile as _compile
+from .targets import B200Target
+
+
+@dataclass
+class MoEAlignmentCall:
+    count: object
+    prefix: object
+    scatter: object
+    mark: object
+    sorted_routes: object
+    expert_blocks: object
+    total_padded: object
+    counts: object
+    cursors: object
+    routes: int
+
+    def compile(self):
+        for call in (self.count, self.prefix, self.scatter, self.mark):
+            call.compile()
+
+    def launch(self):
+        self.counts.zero_()
+        self.cursors.zero_()
+        self.sorted_routes.fill_(self.routes)
+        self.count.launch()
+        self.prefix.launch()
+        self.scatter.launch()
+        self.mark.launch()
+
+    def result(self):
+        return self.sorted_routes, self.expert_blocks, self.total_padded
+
+
+@dataclass
+class MoEAlignment:
+    count: object
+    prefix: object
+    scatter: object
+    mark: object
+    tokens: int = 4096
+    top_k: int = 2
+    experts: int = 64
+    block_size: int = 128
+
+    @classmethod
+    def build(cls, *, tokens=4096, top_k=2, experts=64, block_size=128, target=None, resolve_target=True):
+        constexprs = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": block_size}
+        artifacts = [_compile(definition, target=target, constexprs=constexprs, resolve_target=resolve_target)
+                     for definition in (programs.moe_count_routes, programs.moe_prefix_routes,
+                                        programs.moe_scatter_routes, programs.moe_mark_expert_blocks)]
+        return cls(*artifacts, tokens=tokens, top_k=top_k, experts=experts, block_size=block_size)
+
+    @property
+    def routes(self) -> int:
+        return self.tokens * self.top_k
+
+    @property
+    def padded_routes(self) -> int:
+        return self.routes + self.experts * (self.block_size - 1)
+
+    def _validate_ids(self, ids):
+        if len(ids.shape) != 2 or ids.shape[1] != self.top_k or ids.shape[0] > self.tokens:
+            raise ValueError(f"MoEAlignment requires at most {self.tokens} tokens with top-k {self.top_k}")
+
+    def _workspace(self, ids):
+        import torch
+
+        counts = torch.empty((self.experts,), dtype=torch.int32, device=ids.device)
+        cursors = torch.empty((self.experts,), dtype=torch.int32, device=ids.device)
+        sorted_routes = torch.empty((self.padded_routes,), dtype=torch.int32, device=ids.device)
+        return counts, cursors, sorted_routes
+
+    def run_into(self, ids, counts, cursors, sorted_routes):
+        self._validate_ids(ids)
+        counts.zero_()
+        cursors.zero_()
+        sorted_routes.fill_(self.routes)          # padding sentinel (composition.py:98-101)
+        self.count.run(ids, counts)
+        offsets, total_padded = self.prefix.run(counts)
+        self.scatter.run(ids, offsets, cursors, sorted_routes)
+        expert_blocks = self.mark.run(offsets)
+        return sorted_routes, expert_blocks, total_padded
+
+    def run(self, ids):
+        return self.run_into(ids, *self._workspace(ids))
+
+    def prepare(self, ids):
+        self._validate_ids(ids)
+        counts, cursors, sorted_routes = self._workspace(ids)
+        count = self.count.prepare(ids, counts)
+        prefix = self.prefix.prepare(counts)
+        offsets, total_padded = prefix.result()
+        scatter = self.scatter.prepare(ids, offsets, cursors, sorted_routes)
+        mark = self.mark.prepare(offsets)
+        return MoEAlignmentCall(count, prefix, scatter, mark, sorted_routes, mark.result(), total_padded,
+                                counts, cursors, self.routes)
+
+
+class MoEW4A16FFN:
+    """SiLU-gated MoE FFN with int4 group-quantised expert weights on one GPU.
+
+    ``experts`` is the number of experts held on this GPU; ``tokens`` the number of
+    token rows it routes per call (after any expert-parallel exchange this is the
+    number of received rows with ``top_k = 1``)."""
+
+    def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
+                 act_dtype="bf16", block_size=128, target: B200Target | None = None):
+        self.tokens, self.hidden, self.intermediate = tokens, hidden, intermediate
+        self.experts, self.top_k = experts, top_k
+        self.alignment = MoEAlignment.build(tokens=tokens, top_k=top_k, experts=experts, block_size=block_size,
+                                            target=target)
+        align = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": block_size}
+        quant = {"GROUP_SIZE": group_size, "ZERO_POINT": zero_point, "ACT_DTYPE": act_dtype}
+        self.router = _compile(programs.moe_route_top2, target=target)
+        self.positions = _compile(programs.moe_route_positions, target=target, constexprs=align)
+        self.gather = _compile(programs.moe_gather_rows, target=target,
+                               constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k})
+        self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=quant)
+        self.down = _compile(programs.moe_grouped_down, target=target, constexprs=quant)
+        self.combine = _compile(programs.moe_combine, target=target)
+
+    def route(self, logits):
+        """logits [T, E_total] f32 -> (ids [T,2] i32, weights [T,2] f32)."""
+        return self.router.run(logits)
+
+    def experts_forward(self, x, topk_ids, up_gate_packed, up_gate_scales, down_packed, down_scales):
+        """Rows of the down projection in the expert-sorted layout plus the inverse map:
+        returns (rows f32 [P, H], route_positions i32 [T*top_k])."""
+        sorted_routes, expert_blocks, total = self.alignment.run(topk_ids)
+        positions = self.positions.run(sorted_routes, total)
+        rows = self.gather.run(x, sorted_routes, total)
+        hidden = self.up_gate.run(rows, expert_blocks, total, up_gate_packed, up_gate_scales)
+        out = self.down.run(hidden, expert_blocks, total, down_packed, down_scales)
+        return out, positions
+
+    def forward(self, x, topk_ids, topk_weights, up_gate_packed, up_gate_scales, down_packed, down_scales, y=None):
+        """y[t] (+)= sum_c topk_weights[t, c] * FFN_{topk_ids[t, c]}(x[t]); y f32 [T, H]."""
+        import torch
+
+        rows, positions = self.experts_forward(x, topk_ids, up_gate_packed, up_gate_scales, down_packed,
+                                               down_scales)
+        if y is None:
+            y = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+        self.combine.run(rows, positions, topk_weights, y)
+        return y
+
+    __call__ = forward

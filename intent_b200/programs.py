@@ -141,3 +141,186 @@ w8a8_gemm = KernelDefinition(
 )
 
 ALL = {d.name: d for d in (weight_only_int4_matmul, gemm_i8, w8a8_gemm)}
+
+
+# ---------------------------------------------------------------------------------
+# MoE routing and route alignment.  The reference fixes TOKENS / TOP_K / EXPERTS /
+# BLOCK_SIZE as module constants (examples/kernels/routing/moe_align.py:5-11); here
+# they are compile-time constants of each program.
+# ---------------------------------------------------------------------------------
+from .runtime.interface import Derived  # noqa: E402
+
+_ALIGN_CONSTEXPRS = {"TOKENS": 4096, "TOP_K": 2, "EXPERTS": 64, "BLOCK_SIZE": 128}
+
+
+def _align_sizes(c):
+    tokens, top_k, experts, block = (int(c[k]) for k in ("TOKENS", "TOP_K", "EXPERTS", "BLOCK_SIZE"))
+    if min(tokens, top_k, experts, block) <= 0:
+        raise CompilationStageError("frontend_kir", "TOKENS, TOP_K, EXPERTS and BLOCK_SIZE must be positive")
+    routes = tokens * top_k
+    padded = routes + experts * (block - 1)
+    return tokens, top_k, experts, block, routes, padded, padded // block + 1
+
+
+def _lower_count(c, device):
+    tokens, top_k, experts, *_ = _align_sizes(c)
+    interface = PublicInterface((
+        ViewParameter(0, "topk_ids", dtypes.i32, ("T", top_k), IN, alignment=4),
+        ViewParameter(1, "expert_counts", dtypes.i32, (experts,), INOUT, alignment=4),
+    ), dimension_rules=(_rule(lambda d: d["T"] <= tokens, f"at most {tokens} tokens (TOKENS constexpr)"),))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_count_routes", device=device)
+
+
+def _lower_prefix(c, device):
+    _, _, experts, block, *_ = _align_sizes(c)
+    interface = PublicInterface((
+        ViewParameter(0, "expert_counts", dtypes.i32, (experts,), IN, alignment=4),
+        ViewParameter(1, "expert_offsets", dtypes.i32, (experts + 1,), OUT, alignment=4),
+        ViewParameter(2, "total_padded", dtypes.i32, (1,), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_prefix_routes", constants=(block,),
+                         device=device)
+
+
+def _lower_scatter(c, device):
+    tokens, top_k, experts, _, _, padded, _ = _align_sizes(c)
+    interface = PublicInterface((
+        ViewParameter(0, "topk_ids", dtypes.i32, ("T", top_k), IN, alignment=4),
+        ViewParameter(1, "expert_offsets", dtypes.i32, (experts + 1,), IN, alignment=4),
+        ViewParameter(2, "expert_cursors", dtypes.i32, (experts,), INOUT, alignment=4),
+        ViewParameter(3, "sorted_route_ids", dtypes.i32, (padded,), INOUT, alignment=4),
+    ), dimension_rules=(_rule(lambda d: d["T"] <= tokens, f"at most {tokens} tokens (TOKENS constexpr)"),))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_scatter_routes", device=device)
+
+
+def _lower_mark(c, device):
+    _, _, experts, block, _, _, blocks = _align_sizes(c)
+    interface = PublicInterface((
+        ViewParameter(0, "expert_offsets", dtypes.i32, (experts + 1,), IN, alignment=4),
+        ViewParameter(1, "expert_blocks", dtypes.i32, (blocks,), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_mark_expert_blocks", constants=(block,),
+                         device=device)
+
+
+def _lower_positions(c, device):
+    _, _, _, _, routes, padded, _ = _align_sizes(c)
+    interface = PublicInterface((
+        ViewParameter(0, "sorted_route_ids", dtypes.i32, (padded,), IN, alignment=4),
+        ViewParameter(1, "total_padded", dtypes.i32, (1,), IN, alignment=4),
+        ViewParameter(2, "route_positions", dtypes.i32, (routes,), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_route_positions", device=device)
+
+
+_MOE_ALIGN_REF = "examples/kernels/routing/moe_align.py"
+moe_count_routes = KernelDefinition("moe_count_routes", dict(_ALIGN_CONSTEXPRS), _lower_count,
+                                    f"{_MOE_ALIGN_REF}:14-29", "counts[e] += routes to e")
+moe_prefix_routes = KernelDefinition("moe_prefix_routes", dict(_ALIGN_CONSTEXPRS), _lower_prefix,
+                                     f"{_MOE_ALIGN_REF}:32-49", "block-padded exclusive offsets and padded total")
+moe_scatter_routes = KernelDefinition("moe_scatter_routes", dict(_ALIGN_CONSTEXPRS), _lower_scatter,
+                                      f"{_MOE_ALIGN_REF}:52-73", "stable partition of route ids by expert")
+moe_mark_expert_blocks = KernelDefinition("moe_mark_expert_blocks", dict(_ALIGN_CONSTEXPRS), _lower_mark,
+                                          f"{_MOE_ALIGN_REF}:76-86", "expert of every padded block")
+moe_route_positions = KernelDefinition("moe_route_positions", dict(_ALIGN_CONSTEXPRS), _lower_positions,
+                                       "examples/kernels/ragged/moe.py:24-33 (member_routes indirection, inverted)",
+                                       "slot of every route in the sorted layout")
+
+
+def _lower_route_top2(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "logits", dtypes.f32, ("T", "E"), IN, alignment=4),
+        ViewParameter(1, "topk_ids", dtypes.i32, ("T", 2), OUT, alignment=4),
+        ViewParameter(2, "topk_weights", dtypes.f32, ("T", 2), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_route_top2", device=device,
+                         empty=lambda d: d["T"] == 0)
+
+
+moe_route_top2 = KernelDefinition(
+    "moe_route_top2", {}, _lower_route_top2,
+    "examples/kernels/sampling/top_k.py:10-33, examples/kernels/normalization/softmax.py:23-37",
+    "top-2 experts by logit (ties: lower id) and their softmax probabilities")
+
+
+# ---------------------------------------------------------------------------------
+# MoE data path: row gather, grouped W4A16 projections, weighted combine
+# ---------------------------------------------------------------------------------
+def _lower_gather(c, device):
+    act = _act_dtype(c)
+    interface = PublicInterface((
+        ViewParameter(0, "x", act, ("T", "H"), IN),
+        ViewParameter(1, "sorted_route_ids", dtypes.i32, ("P",), IN, alignment=4),
+        ViewParameter(2, "total_padded", dtypes.i32, (1,), IN, alignment=4),
+        ViewParameter(3, "rows", act, ("P", "H"), OUT),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_gather_rows",
+                         constants=(int(c["TOP_K"]),), device=device)
+
+
+moe_gather_rows = KernelDefinition("moe_gather_rows", {"ACT_DTYPE": "bf16", "TOP_K": 2}, _lower_gather,
+                                   "examples/kernels/ragged/moe.py:34-36 (I.gather of token rows)",
+                                   "rows[p] = x[sorted[p] // TOP_K], zero rows for padding")
+
+
+def _grouped_constants(c):
+    group = int(c["GROUP_SIZE"])
+    if group not in (32, 64, 128):
+        raise CompilationStageError("provider_native_compilation", f"GROUP_SIZE {group} has no kernel specialisation")
+    zero_point = c["ZERO_POINT"]
+    zp = -1 if zero_point in ("twos_complement", None, -1) else zero_point
+    if zp not in (-1, 8):
+        raise CompilationStageError("provider_native_compilation", "ZERO_POINT must be 'twos_complement' or 8")
+    return group, zp
+
+
+def _lower_grouped(c, device, *, gated):
+    act = _act_dtype(c)
+    group, zp = _grouped_constants(c)
+    out_cols = Derived("I", lambda d: d["WN"] // 2) if gated else "WN"
+    interface = PublicInterface((
+        ViewParameter(0, "rows", act, ("P", "K"), IN),
+        ViewParameter(1, "expert_blocks", dtypes.i32, ("B",), IN, alignment=4),
+        ViewParameter(2, "total_padded", dtypes.i32, (1,), IN, alignment=4),
+        ViewParameter(3, "packed_weight", dtypes.i32, ("E", "KP", "WN"), IN),
+        ViewParameter(4, "scales", act, ("E", "KG", "WN"), IN),
+        ViewParameter(5, "output", act if gated else dtypes.f32, ("P", out_cols), OUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
+              "packed_weight / scales do not match K and GROUP_SIZE"),
+        _rule(lambda d: d["B"] * 128 >= d["P"], "expert_blocks must cover every 128-row block of rows"),
+    ))
+    stem = "upgate_silu" if gated else "down_f32"
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_{stem}_{act.name}",
+                         constants=(group, zp), device=device)
+
+
+_GROUPED_CONSTEXPRS = {"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16"}
+moe_grouped_upgate_silu = KernelDefinition(
+    "moe_grouped_upgate_silu", dict(_GROUPED_CONSTEXPRS), lambda c, d: _lower_grouped(c, d, gated=True),
+    "examples/kernels/ragged/grouped_gemm.py:42-70, examples/kernels/ragged/moe.py:37-42, "
+    "examples/kernels/activation/swiglu.py:27-46",
+    "hidden = silu(rows @ Wgate[e]) * (rows @ Wup[e]) per expert block, int4 weights")
+moe_grouped_down = KernelDefinition(
+    "moe_grouped_down", dict(_GROUPED_CONSTEXPRS), lambda c, d: _lower_grouped(c, d, gated=False),
+    "examples/kernels/ragged/grouped_gemm.py:42-70, examples/kernels/ragged/moe.py:43-47",
+    "out = hidden @ Wdown[e] per expert block, f32 rows")
+
+
+def _lower_combine(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "rows", dtypes.f32, ("P", "H"), IN),
+        ViewParameter(1, "route_positions", dtypes.i32, ("R",), IN, alignment=4),
+        ViewParameter(2, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
+        ViewParameter(3, "y", dtypes.f32, ("T", "H"), INOUT),
+    ), dimension_rules=(_rule(lambda d: d["R"] == d["T"] * d["TOP_K"], "route_positions must have T * TOP_K entries"),))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_combine", device=device)
+
+
+moe_combine = KernelDefinition("moe_combine", {}, _lower_combine,
+                               "examples/kernels/ragged/moe.py:48-53 (weighted scatter_reduce add)",
+                               "y[t] += sum_c weight[t,c] * rows[position[t,c]] in choice order")
+
+ALL.update({d.name: d for d in (moe_count_routes, moe_prefix_routes, moe_scatter_routes, moe_mark_expert_blocks,
+                                moe_route_positions, moe_route_top2, moe_gather_rows, moe_grouped_upgate_silu,
+                                moe_grouped_down, moe_combine)})

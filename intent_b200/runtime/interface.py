@@ -29,6 +29,18 @@ class ViewKind(IntEnum):
     INOUT = 2
 
 
+@dataclass(frozen=True)
+class Derived:
+    """An extent computed from other symbolic dimensions (e.g. ``I = WN // 2``).
+    Supplied views are checked against it, omitted Out buffers are sized by it."""
+
+    name: str
+    function: object
+
+    def __call__(self, dimensions: dict) -> int:
+        return int(self.function(dimensions))
+
+
 @dataclass(frozen=True, slots=True)
 class ScalarParameter:
     position: int
@@ -41,7 +53,7 @@ class ViewParameter:
     position: int
     name: str
     dtype: DType
-    shape: tuple            # per axis: int (static extent) or str (symbolic dimension)
+    shape: tuple            # per axis: int (static extent), str (symbolic dimension) or Derived
     access: ViewKind
     alignment: int = 16     # bytes; entry requirement
     layout: str = "contiguous"
@@ -218,10 +230,14 @@ class PublicInterface:
         facts: list = [None] * len(self.parameters)
         dimensions: dict = {}
 
+        deferred: list = []
+
         def relate(parameter: ViewParameter, observed: ViewFacts) -> None:
             for axis, extent in enumerate(parameter.shape):
                 message = f"{parameter.name}.shape[{axis}] violates the declared interface relation"
-                if isinstance(extent, int):
+                if isinstance(extent, Derived):
+                    deferred.append((extent, observed.shape[axis], message))
+                elif isinstance(extent, int):
                     self._check_relation(observed.shape[axis], extent, message, abstract)
                 elif extent in dimensions:
                     self._check_relation(observed.shape[axis], dimensions[extent], message, abstract)
@@ -240,12 +256,19 @@ class PublicInterface:
                     raise TypeError(f"{parameter.name} must be a Python scalar")
                 if parameter.dtype.category in ("int", "uint") and not isinstance(value, (int, torch.SymInt)):
                     raise TypeError(f"{parameter.name} must be an integer")
+        for extent, actual, message in deferred:
+            try:
+                expected = extent(dimensions)
+            except KeyError:
+                continue        # depends on a dimension only an omitted output would bind
+            self._check_relation(actual, expected, message, abstract)
         if not abstract:
             for rule in self.dimension_rules:
                 rule(dimensions)
         if not explicit_outputs:
             for parameter in self.outputs:
-                shape = tuple(extent if isinstance(extent, int) else dimensions[extent]
+                shape = tuple(extent if isinstance(extent, int) else
+                              (extent(dimensions) if isinstance(extent, Derived) else dimensions[extent])
                               for extent in parameter.shape)
                 value = torch.empty(shape, dtype=torch_dtype(parameter.dtype), device=device)
                 observed = self._observe(parameter, value, device, abstract)

@@ -1,0 +1,120 @@
+"""MoE router / alignment (bit-exact) and the grouped int4 FFN (2e-2 * max|ref|)."""
+import pytest
+import torch
+
+import intent_b200 as ib
+import oracle
+from intent_b200.moe import MoEAlignment, MoEW4A16FFN
+from intent_b200.runtime import native
+from conftest import load_golden, max_abs_rel
+
+pytestmark = pytest.mark.gpu
+
+
+def test_router_top2_bit_exact(cuda_device):
+    logits = ib.workloads.moe_inputs(16384, 64, 64, 128, seed=0)["logits"]       # benchmark router input
+    logits[5, 7] = logits[5, 40] = logits[5].max() + 1.0                         # exact tie: lower id first
+    logits[9, :] = 0.5                                                           # all equal: ids 0, 1
+    router = ib.compile(ib.programs.moe_route_top2, target=ib.B200Target(0))
+    ids, weights = router.run(logits.to(cuda_device))
+    torch.cuda.synchronize()
+    ref_ids, ref_weights = oracle.moe_route_top2(logits)
+    assert ids.dtype == torch.int32 and torch.equal(ids.cpu(), ref_ids)
+    assert ids[5].tolist() == [7, 40] and ids[9].tolist() == [0, 1]
+    assert torch.allclose(weights.cpu(), ref_weights, rtol=2e-6, atol=0)
+    g = load_golden("insertion_top_k")                                           # reference golden, k = 8 -> first two
+    ids, _ = router.run(g["logits"].to(cuda_device))
+    assert torch.equal(ids.cpu(), g["indices"][:, :2])
+
+
+@pytest.mark.parametrize("tag", ["ref_pattern", "small"])
+def test_alignment_matches_reference_golden(cuda_device, tag):
+    g = load_golden(f"moe_align_{tag}")
+    block, experts = int(g["block"]), int(g["experts"])
+    tokens = g["topk_ids"].shape[0]
+    alignment = MoEAlignment.build(tokens=tokens, top_k=2, experts=experts, block_size=block, target=ib.B200Target(0))
+    ids = g["topk_ids"].to(cuda_device)
+    sorted_ids, expert_blocks, total = alignment.run(ids)
+    torch.cuda.synchronize()
+    assert torch.equal(total.cpu(), g["total"])
+    assert torch.equal(sorted_ids.cpu(), g["sorted_ids"])                       # stable order: no canonicalisation needed
+    blocks = int(total) // block
+    assert torch.equal(expert_blocks[:blocks].cpu(), g["expert_ids"])
+    # prepared form: same results on relaunch, workspace reset included
+    call = alignment.prepare(ids)
+    call.compile()
+    call.launch()
+    call.launch()
+    torch.cuda.synchronize()
+    again, blocks_again, total_again = call.result()
+    assert torch.equal(again, sorted_ids) and torch.equal(total_again, total)
+    assert torch.equal(call.counts.cpu(), g["counts"]) and torch.equal(call.cursors.cpu(), g["counts"])
+
+
+def test_alignment_benchmark_size_properties(cuda_device):
+    """16384 tokens, 64 experts: equal to the oracle, every route appears once, spans are sorted."""
+    logits = ib.workloads.moe_inputs(16384, 64, 64, 128, seed=0)["logits"]
+    ids, _ = oracle.moe_route_top2(logits)
+    alignment = MoEAlignment.build(tokens=16384, top_k=2, experts=64, block_size=128, target=ib.B200Target(0))
+    sorted_ids, expert_blocks, total = alignment.run(ids.to(cuda_device))
+    ref_sorted, ref_blocks, ref_total, _ = oracle.moe_align_block_size(ids, 128, 64)
+    assert torch.equal(total.cpu(), ref_total) and torch.equal(sorted_ids.cpu(), ref_sorted)
+    n = int(total) // 128
+    assert torch.equal(expert_blocks[:n].cpu(), ref_blocks[:n])
+    real = sorted_ids[sorted_ids < 32768]
+    assert real.numel() == 32768 and torch.equal(torch.sort(real).values.cpu(), torch.arange(32768, dtype=torch.int32))
+
+
+def _ffn_case(tokens, hidden, intermediate, experts, dtype, seed):
+    data = ib.workloads.moe_inputs(tokens, hidden, experts, intermediate, dtype=dtype, seed=seed)
+    ids, weights = oracle.moe_route_top2(data["logits"])
+    return data, ids, weights
+
+
+@pytest.mark.parametrize("dtype,tokens,hidden,intermediate,experts", [
+    (torch.bfloat16, 256, 512, 256, 8),
+    (torch.float16, 300, 256, 128, 4),
+    (torch.bfloat16, 1024, 1024, 384, 16),
+])
+def test_moe_ffn_matches_oracle(cuda_device, dtype, tokens, hidden, intermediate, experts):
+    data, ids, weights = _ffn_case(tokens, hidden, intermediate, experts, dtype, seed=11)
+    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts,
+                      act_dtype="bf16" if dtype == torch.bfloat16 else "f16", target=ib.B200Target(0))
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    got_ids, got_weights = ffn.route(dev["logits"])
+    assert torch.equal(got_ids.cpu(), ids)
+    y = ffn(dev["x"], got_ids, got_weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
+            dev["down_scales"])
+    torch.cuda.synchronize()
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 0
+    ref = oracle.moe_w4a16_swiglu_ffn(data["x"], ids, weights, data["up_gate_packed"], data["up_gate_scales"],
+                                      data["down_packed"], data["down_scales"])
+    assert y.dtype == torch.float32 and y.shape == (tokens, hidden)
+    assert max_abs_rel(y.cpu(), ref) <= 2e-2
+    # deterministic: a second run gives the same bits
+    y2 = ffn(dev["x"], got_ids, got_weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
+             dev["down_scales"])
+    assert torch.equal(y, y2)
+
+
+def test_grouped_projection_stage_by_stage(cuda_device):
+    """The up|gate stage alone against the oracle's grouped product + SiLU gate."""
+    tokens, hidden, intermediate, experts = 200, 256, 128, 4
+    data, ids, weights = _ffn_case(tokens, hidden, intermediate, experts, torch.bfloat16, seed=2)
+    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts, target=ib.B200Target(0))
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    sorted_routes, expert_blocks, total = ffn.alignment.run(ids.to(cuda_device))
+    rows = ffn.gather.run(dev["x"], sorted_routes, total)
+    hidden_act = ffn.up_gate.run(rows, expert_blocks, total, dev["up_gate_packed"], dev["up_gate_scales"])
+    torch.cuda.synchronize()
+    n = int(total)
+    sorted_cpu = sorted_routes[:n].cpu().long()
+    real = sorted_cpu < tokens * 2
+    x_sorted = torch.zeros((n, hidden), dtype=torch.bfloat16)
+    x_sorted[real] = data["x"][sorted_cpu[real] // 2]
+    assert torch.equal(rows[:n].cpu(), x_sorted)
+    expert_of_row = expert_blocks[: n // 128].cpu().long().repeat_interleave(128)
+    gate_up = oracle.grouped_w4a16_gemm(x_sorted, expert_of_row, data["up_gate_packed"], data["up_gate_scales"],
+                                        group_size=128, zero_point=8)
+    ref = oracle.silu_and_mul(gate_up)
+    assert max_abs_rel(hidden_act[:n].float().cpu(), ref) <= 2e-2
