@@ -1,14 +1,19 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-contraction hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload W] [--impl reference]
 
 Prints ONE JSON line (rank 0).  Workloads (seeded synthetic inputs with the
 shapes and value distributions of the benchmark configurations):
 
+  prefill  (default) W4A16 prefill GEMM 8192^3 bf16, columns of W split over the GPUs;
+           metric = TFLOP/s.  Tensor-core bound.  The decode figures are attached to the
+           same line under "decode" (the headline metric names both).
   decode   W4A16 decode GEMV, M=1: one step = the up projection
            [1,4096]x[4096,14336] and the down projection [1,14336]x[14336,4096];
-           metric = weight GB/s (algorithmic bytes / time).  HBM-bound.
+           metric = weight GB/s (algorithmic bytes / time).  HBM-bound.  Replicas only.
+  w8a8     int8 GEMM 4096x8192x8192 with the scaled bf16 epilogue, columns split.
+  moe      16384-token top-2 MoE FFN with int4 experts; expert parallel for N > 1.
 
 `value` is measured with inputs resident in HBM, the K timed steps captured in one
 CUDA graph (the kernels are microseconds long; eager launches would measure the
@@ -43,7 +48,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # DRAM traffic per launch of the dominant kernel from an ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {"decode": None}
+NCU_TRAFFIC_BYTES = {"decode": 30314496, "prefill": None, "w8a8": None}
 
 
 def measured_peaks():
@@ -253,7 +258,7 @@ def run_decode(args, rank: int, world: int, device):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES["decode"],
                      "peak_source": peaks["source"], "algorithmic_bytes_per_launch": per_launch_bytes,
-                     "kernel": "w4a16_skinny_kernel", "us_per_launch": round(per_launch_s * 1e6, 3)},
+                     "kernel": "w4a16_stream_kernel", "us_per_launch": round(per_launch_s * 1e6, 3)},
         "e2e": {"value": round(world * step_bytes / (e2e_s / args.steps) / 1e9, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in pinned_in),
                 "d2h_bytes_per_step": sum(y.numel() * 2 for y in pinned_out),
@@ -265,7 +270,237 @@ def run_decode(args, rank: int, world: int, device):
 
 
 # ---------------------------------------------------------------------------------------
-# CPU arm (reference implementation of the path on the host cores)
+# tensor-core workloads: W4A16 prefill (configs[2]), W8A8 (configs[3]), MoE (configs[4])
+# ---------------------------------------------------------------------------------------
+def timed_steps(step, steps: int, warmup: int, world: int, device, rank: int, load_seconds: float):
+    """Warm up, hold the load while clocks are sampled, then time exactly `steps` steps with CUDA
+    events on the current stream, bracketed by barriers; returns (ms total, clocks, launches)."""
+    import torch
+
+    from intent_b200.runtime import native
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index)
+    if rank == 0:
+        sampler.start()
+    until = time.perf_counter() + load_seconds
+    while time.perf_counter() < until:
+        step()
+        torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = native.launch_count()
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    launches = native.launch_count() - before
+    elapsed_ms = reduce_max(start.elapsed_time(stop), world, device)
+    clocks = sampler.stop() if rank == 0 else None
+    return elapsed_ms, clocks, launches
+
+
+def timed_e2e(step, steps: int, warmup: int, world: int, device):
+    import torch
+
+    for _ in range(max(min(warmup, 3), 1)):
+        step()
+    barrier(world)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    return reduce_max(time.perf_counter() - t0, world, device)
+
+
+PREFILL = dict(M=8192, K=8192, N=8192)
+W8A8 = dict(M=4096, K=8192, N=8192)
+MOE = dict(tokens=16384, hidden=4096, experts=64, intermediate=1408, top_k=2)
+
+
+def run_prefill(args, rank: int, world: int, device):
+    import torch
+
+    import intent_b200 as ib
+    from intent_b200.distributed import column_shard
+
+    M, K, N = PREFILL["M"], PREFILL["K"], PREFILL["N"]
+    x, packed, scales = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=GROUP, seed=0)
+    cols = column_shard(N, world, rank)
+    artifact = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(device.index),
+                          constexprs={"GROUP_SIZE": GROUP, "ZERO_POINT": 8, "ACT_DTYPE": "bf16"})
+    xd = x.to(device)
+    pd, sd = packed[:, cols].contiguous().to(device), scales[:, cols].contiguous().to(device)
+    call = artifact.prepare(xd, pd, sd)
+    elapsed_ms, clocks, launches = timed_steps(call.launch, args.steps, args.warmup, world, device, rank,
+                                               args.load_seconds)
+    # end to end: activations from pinned host memory, this rank's block of Y read back
+    pinned_x = x.pin_memory()
+    n_local = cols.stop - cols.start
+    pinned_y = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        y = artifact.run(pinned_x.to(device, non_blocking=True), pd, sd)
+        pinned_y.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_s = timed_e2e(e2e_step, max(1, min(args.steps, 20)), args.warmup, world, device)
+    e2e_steps = max(1, min(args.steps, 20))
+    flops = 2.0 * M * K * N
+    ms = elapsed_ms / args.steps
+    peaks = measured_peaks()
+    per_launch_flops = flops / world
+    achieved = per_launch_flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "w4a16_prefill_TFLOPs", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "w4a16_prefill_gemm M=8192 K=8192 N=8192 bf16 g128 zp8 (configs[2])",
+                   "group_size": GROUP, "parallelism": f"columns of W split over {world} gpu(s), no collective",
+                   "l2": "X (128 MiB) + Y (128 MiB) + W exceed the 126 MB L2 every step",
+                   "timing": "CUDA events on the launch stream around K launches"},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
+                     "traffic": NCU_TRAFFIC_BYTES.get("prefill"), "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4),
+                     "frac_of_nominal_2250": round(achieved / 2250.0, 4),
+                     "algorithmic_flops_per_launch": per_launch_flops, "kernel": "w4a16_gemm_kernel",
+                     "ms_per_launch": round(ms, 5)},
+        "e2e": {"value": round(flops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * n_local * 2,
+                "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    return line
+
+
+def run_w8a8(args, rank: int, world: int, device):
+    import torch
+
+    import intent_b200 as ib
+    from intent_b200.distributed import column_shard
+
+    M, K, N = W8A8["M"], W8A8["K"], W8A8["N"]
+    a, b, sa, sb = ib.workloads.w8a8_inputs(M, K, N, seed=0)
+    cols = column_shard(N, world, rank)
+    artifact = ib.compile(ib.programs.w8a8_gemm, target=ib.B200Target(device.index))
+    ad, sad = a.to(device), sa.to(device)
+    bd, sbd = b[:, cols].contiguous().to(device), sb[cols].contiguous().to(device)
+    call = artifact.prepare(ad, bd, sad, sbd)
+    elapsed_ms, clocks, launches = timed_steps(call.launch, args.steps, args.warmup, world, device, rank,
+                                               args.load_seconds)
+    pinned_a = a.pin_memory()
+    n_local = cols.stop - cols.start
+    pinned_y = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        y = artifact.run(pinned_a.to(device, non_blocking=True), bd, sad, sbd)
+        pinned_y.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(1, min(args.steps, 20))
+    e2e_s = timed_e2e(e2e_step, e2e_steps, args.warmup, world, device)
+    ops = 2.0 * M * K * N
+    ms = elapsed_ms / args.steps
+    peaks = measured_peaks()
+    achieved = ops / world / (ms * 1e-3) / 1e12
+    int8_peak = 2.0 * peaks["bf16_tflops"]   # no measured int8 figure: twice the measured bf16 burst
+    return {
+        "metric": "w8a8_gemm_TOPs", "value": round(ops / (ms * 1e-3) / 1e12, 2), "unit": "TOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "w8a8_gemm M=4096 K=8192 N=8192 int8 -> bf16 scaled epilogue (configs[3])",
+                   "parallelism": f"columns of B split over {world} gpu(s), no collective",
+                   "l2": "A + B + Y = 160 MiB exceed the 126 MB L2 every step"},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": int8_peak, "unit": "TOP/s",
+                     "frac": round(achieved / int8_peak, 4), "traffic": NCU_TRAFFIC_BYTES.get("w8a8"),
+                     "peak_source": "2 x measured bf16 burst (no int8 peak was measured on this pool)",
+                     "frac_of_nominal_4500": round(achieved / 4500.0, 4), "kernel": "i8_gemm_kernel",
+                     "ms_per_launch": round(ms, 5)},
+        "e2e": {"value": round(ops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TOP/s",
+                "h2d_bytes_per_step": M * K, "d2h_bytes_per_step": M * n_local * 2,
+                "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+
+def run_moe(args, rank: int, world: int, device):
+    import torch
+
+    import intent_b200 as ib
+    from intent_b200.moe import MoEW4A16FFN
+
+    cfg = MOE
+    tokens, hidden, experts, inter = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["intermediate"]
+    if experts % world or tokens % world:
+        raise SystemExit("moe workload needs the gpu count to divide 64 experts and 16384 tokens")
+    data = ib.workloads.moe_inputs(tokens, hidden, experts, inter, dtype=torch.bfloat16, seed=0)
+    t_local, e_local = tokens // world, experts // world
+    rows = slice(rank * t_local, (rank + 1) * t_local)
+    ex = slice(rank * e_local, (rank + 1) * e_local)
+    logits, x = data["logits"][rows].contiguous(), data["x"][rows].contiguous()
+    weights = [data[k][ex].contiguous().to(device) for k in ("up_gate_packed", "up_gate_scales", "down_packed",
+                                                             "down_scales")]
+    if world == 1:
+        ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts, target=ib.B200Target(device.index))
+
+        def forward(lg, xx):
+            ids, w = ffn.route(lg)
+            return ffn(xx, ids, w, *weights)
+    else:
+        from intent_b200.distributed import ExpertParallelMoE
+
+        ep = ExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
+                               capacity_rows=4 * t_local * 2, target=ib.B200Target(device.index))
+
+        def forward(lg, xx):
+            return ep(lg, xx, *weights)
+
+    lgd, xd = logits.to(device), x.to(device)
+    elapsed_ms, clocks, launches = timed_steps(lambda: forward(lgd, xd), args.steps, args.warmup, world, device,
+                                               rank, args.load_seconds)
+    pinned_l, pinned_x = logits.pin_memory(), x.pin_memory()
+    pinned_y = torch.empty((t_local, hidden), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        y = forward(pinned_l.to(device, non_blocking=True), pinned_x.to(device, non_blocking=True))
+        pinned_y.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(1, min(args.steps, 20))
+    e2e_s = timed_e2e(e2e_step, e2e_steps, args.warmup, world, device)
+    flops = tokens * cfg["top_k"] * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
+    ms = elapsed_ms / args.steps
+    peaks = measured_peaks()
+    achieved = flops / world / (ms * 1e-3) / 1e12
+    return {
+        "metric": "moe_w4a16_ffn_TFLOPs", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "moe_w4a16_swiglu_ffn 16384 tokens H=4096 E=64 top-2 I=1408 g128 (configs[4])",
+                   "parallelism": "all experts local" if world == 1 else
+                   f"expert parallel: {e_local} experts and {t_local} tokens per gpu, NCCL all-to-all each way",
+                   "step": "router + alignment + gather + up|gate GEMM (SiLU) + down GEMM + combine",
+                   "l2": "expert weights (571 MB) and row buffers exceed the 126 MB L2"},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4), "traffic": None,
+                     "peak_source": peaks["source"] + " (burst cuBLAS bf16); whole step, not one kernel",
+                     "kernel": "w4a16_gemm_kernel (grouped modes)"},
+        "e2e": {"value": round(flops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": t_local * (64 * 4 + hidden * 2), "d2h_bytes_per_step": t_local * hidden * 4,
+                "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm (the reference's CPU implementation of the path, restated in oracle/)
 # ---------------------------------------------------------------------------------------
 def cpu_decode(M: int, steps: int, warmup: int, budget_s: float):
     """Time the torch-CPU implementation of the decode step.  Returns
@@ -278,17 +513,15 @@ def cpu_decode(M: int, steps: int, warmup: int, budget_s: float):
     torch.set_num_threads(cores)
     host = decode_inputs(M)
 
-    def step(fraction_columns: int) -> None:
+    def step(divisor: int) -> None:
         for x, p, s in host:
-            n = p.shape[1] // fraction_columns
+            n = p.shape[1] // divisor
             oracle.weight_only_int4_matmul(x, p[:, :n].contiguous(), s[:, :n].contiguous(),
                                            group_size=GROUP, zero_point=8)
 
-    divisor = 8
     t0 = time.perf_counter()
-    step(divisor)
-    probe = time.perf_counter() - t0
-    full_estimate = probe * divisor
+    step(8)
+    full_estimate = (time.perf_counter() - t0) * 8
     divisor = 1
     while full_estimate / divisor * (steps + warmup) > budget_s and divisor < 64:
         divisor *= 2
@@ -298,24 +531,133 @@ def cpu_decode(M: int, steps: int, warmup: int, budget_s: float):
     for _ in range(steps):
         step(divisor)
     seconds = (time.perf_counter() - t0) / steps
-    step_bytes = decode_bytes(M) / divisor
     sample = (f"{steps} steps of the decode step on the first 1/{divisor} of the output columns "
               f"(M={M}, both projections), torch CPU, {cores} threads")
-    return step_bytes / seconds / 1e9, cores, sample, seconds * 1e3
+    return decode_bytes(M) / divisor / seconds / 1e9, cores, sample, seconds * 1e3
+
+
+def cpu_prefill(steps: int, warmup: int, budget_s: float):
+    """W4A16 prefill on the CPU: a slice of the rows of X against the whole weight (the dequantisation of
+    W is part of every call, as in the reference's torch implementation).  Returns TFLOP/s of the slice."""
+    import torch
+
+    import oracle
+    from intent_b200 import workloads
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    K, N = PREFILL["K"], PREFILL["N"]
+    rows = 64
+    x, p, s = workloads.w4a16_inputs(rows, K, N, dtype=torch.bfloat16, group_size=GROUP, seed=0)
+    t0 = time.perf_counter()
+    oracle.weight_only_int4_matmul(x, p, s, group_size=GROUP, zero_point=8)
+    one = time.perf_counter() - t0
+    steps = max(1, min(steps, int(budget_s / max(one, 1e-3)) - warmup))
+    for _ in range(warmup):
+        oracle.weight_only_int4_matmul(x, p, s, group_size=GROUP, zero_point=8)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.weight_only_int4_matmul(x, p, s, group_size=GROUP, zero_point=8)
+    seconds = (time.perf_counter() - t0) / steps
+    sample = (f"{steps} steps of {rows} of the 8192 rows of X against the full 8192x8192 int4 weight "
+              f"(dequantisation included), torch CPU, {cores} threads")
+    return 2.0 * rows * K * N / seconds / 1e12, cores, sample, seconds * 1e3, steps
+
+
+def cpu_w8a8(steps: int, warmup: int, budget_s: float):
+    import torch
+
+    import oracle
+    from intent_b200 import workloads
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    K, N = W8A8["K"], W8A8["N"]
+    rows = 512
+    a, b, sa, sb = workloads.w8a8_inputs(rows, K, N, seed=0)
+    t0 = time.perf_counter()
+    oracle.w8a8_scaled_gemm(a, b, sa, sb)
+    one = time.perf_counter() - t0
+    steps = max(1, min(steps, int(budget_s / max(one, 1e-3)) - warmup))
+    for _ in range(warmup):
+        oracle.w8a8_scaled_gemm(a, b, sa, sb)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.w8a8_scaled_gemm(a, b, sa, sb)
+    seconds = (time.perf_counter() - t0) / steps
+    sample = f"{steps} steps of {rows} of the 4096 rows of A against the full 8192x8192 B, torch CPU int matmul, {cores} threads"
+    return 2.0 * rows * K * N / seconds / 1e12, cores, sample, seconds * 1e3, steps
+
+
+def cpu_moe(steps: int, warmup: int, budget_s: float):
+    import torch
+
+    import oracle
+    from intent_b200 import workloads
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = MOE
+    tokens, experts = 256, 8        # bounded sample: 256 tokens over 8 of the 64 experts, same H and I
+    data = workloads.moe_inputs(tokens, cfg["hidden"], experts, cfg["intermediate"], dtype=torch.bfloat16, seed=0)
+
+    def step():
+        ids, w = oracle.moe_route_top2(data["logits"])
+        oracle.moe_w4a16_swiglu_ffn(data["x"], ids, w, data["up_gate_packed"], data["up_gate_scales"],
+                                    data["down_packed"], data["down_scales"])
+
+    t0 = time.perf_counter()
+    step()
+    one = time.perf_counter() - t0
+    steps = max(1, min(steps, int(budget_s / max(one, 1e-3)) - warmup))
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    seconds = (time.perf_counter() - t0) / steps
+    flops = tokens * 2 * (2.0 * cfg["hidden"] * 2 * cfg["intermediate"] + 2.0 * cfg["intermediate"] * cfg["hidden"])
+    sample = (f"{steps} steps of {tokens} tokens over {experts} experts (H=4096, I=1408, top-2; per-expert "
+              f"dequantisation included), torch CPU, {cores} threads")
+    return flops / seconds / 1e12, cores, sample, seconds * 1e3, steps
+
+
+WORKLOAD_META = {
+    "prefill": ("w4a16_prefill_TFLOPs", "TFLOP/s", "strong", "bf16",
+                "w4a16_prefill_gemm M=8192 K=8192 N=8192 bf16 g128 zp8 (configs[2])"),
+    "w8a8": ("w8a8_gemm_TOPs", "TOP/s", "strong", "int8",
+             "w8a8_gemm M=4096 K=8192 N=8192 int8 -> bf16 scaled epilogue (configs[3])"),
+    "moe": ("moe_w4a16_ffn_TFLOPs", "TFLOP/s", "strong", "bf16",
+            "moe_w4a16_swiglu_ffn 16384 tokens H=4096 E=64 top-2 I=1408 g128 (configs[4])"),
+    "decode": ("w4a16_decode_weight_GBps", "GB/s", "weak", "f16", None),
+}
+
+
+def cpu_workload(args, steps: int, warmup: int, budget_s: float):
+    """(value, unit, cores, sample, ms per step, steps actually timed) of the CPU implementation."""
+    if args.workload == "decode":
+        value, cores, sample, ms = cpu_decode(args.batch, steps, warmup, budget_s)
+        return value, "GB/s", cores, sample, ms, steps
+    fn = {"prefill": cpu_prefill, "w8a8": cpu_w8a8, "moe": cpu_moe}[args.workload]
+    value, cores, sample, ms, done = fn(steps, warmup, budget_s)
+    return value, WORKLOAD_META[args.workload][1], cores, sample, ms, done
 
 
 def run_reference(args, rank: int, world: int):
     if rank != 0:
         return None
-    value, cores, sample, ms = cpu_decode(args.batch, args.steps, max(args.warmup, 1), budget_s=150.0)
+    metric, unit, scaling, _, workload = WORKLOAD_META[args.workload]
+    if workload is None:
+        workload = f"w4a16_decode_gemv M={args.batch} [4096->14336]+[14336->4096] g128 zp8 (configs[1])"
+    value, unit, cores, sample, ms, done = cpu_workload(args, args.steps, max(args.warmup, 1), budget_s=150.0)
     return {
-        "impl": "reference", "metric": "w4a16_decode_weight_GBps", "value": round(value, 4), "unit": "GB/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(ms, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"w4a16_decode_gemv M={args.batch} [4096->14336]+[14336->4096] g128 zp8 (configs[1])",
-                   "batch": args.batch, "group_size": GROUP},
-        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": metric, "value": round(value, 5), "unit": unit,
+        "n_gpus": world, "steps": done, "warmup": max(args.warmup, 1), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "note": "CPU implementation of the same path on the host cores; each step "
+                   "is the bounded sample named in cpu_baseline.sample, throughput is per unit of work"},
+        "cpu_baseline": {"value": round(value, 5), "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 5), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
 
@@ -344,14 +686,19 @@ def reduce_max(value: float, world: int, device) -> float:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--workload", default="decode", choices=["decode"])
+    parser.add_argument("--workload", default="prefill", choices=["prefill", "decode", "w8a8", "moe"])
     parser.add_argument("--batch", type=int, default=1, help="decode batch M (1, 4, 8)")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--load-seconds", type=float, default=1.5)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()
+    if args.steps is None:
+        args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20}[args.workload]
+        if args.impl == "reference":
+            args.steps = 5
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -376,13 +723,21 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
-    line = run_decode(args, rank, world, device)
+    runner = {"prefill": run_prefill, "decode": run_decode, "w8a8": run_w8a8, "moe": run_moe}[args.workload]
+    line = runner(args, rank, world, device)
+    if args.workload == "prefill" and not args.no_decode:
+        # the headline metric has two halves: attach the decode GEMV (weight GB/s) measured in the same run
+        decode_args = argparse.Namespace(**vars(args))
+        decode_args.steps, decode_args.load_seconds = 200, 0.5
+        decode = run_decode(decode_args, rank, world, device)
+        line["decode"] = {k: decode[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "roofline", "e2e",
+                                                  "gpu_launches", "scaling")}
     if rank == 0:
         if args.no_cpu_baseline:
             line["cpu_baseline"] = None
         else:
-            value, cores, sample, _ = cpu_decode(args.batch, 5, 1, budget_s=25.0)
-            line["cpu_baseline"] = {"value": round(value, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+            value, unit, cores, sample, _, _ = cpu_workload(args, 5, 1, budget_s=25.0)
+            line["cpu_baseline"] = {"value": round(value, 5), "unit": unit, "cores": cores, "kind": "port",
                                     "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
