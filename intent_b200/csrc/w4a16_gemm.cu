@@ -1,4 +1,4 @@
-// W4A16 prefill GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+// W4A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
 //   Y[m, n] = T( sum_k f32(X[m, k]) * f32( T( (q[k, n] - 8) * S[k / G, n] ) ) )
 //
@@ -6,29 +6,34 @@
 // examples/kernels/contraction/weight_only_int4.py:18-51 (the dequantised weight is
 // rounded to the activation type before the f32-accumulated product, as at :42-47).
 //
-// One persistent CTA per SM walks 128 x 256 output tiles; 14 warps in four roles:
-//   warp 0        TMA producer: per 64-wide k block one 128B-swizzled box of X
-//                 (128 rows x 64 k), one box of packed weights (8 packed rows x 256
-//                 columns, raw int32) and one box of scales, 4 stages deep.
-//   warps 6..13   dequantisers: thread n owns weight column n of the tile; per k block
-//                 it expands its 8 packed words to 64 values of T with the magic-number
-//                 trick (prmt + lop3, exact subtract, one rounding multiply by the
-//                 scale) and writes them as the 128-byte row n of the K-major,
-//                 128B-swizzled B operand tile (3 stages).
-//   warp 1        MMA issuer: one thread issues four tcgen05.mma (M128 N256 K16,
-//                 kind::f16, f32 accumulation in TMEM) per k block and commits to the
-//                 mbarriers that free the stages.
-//   warps 2..5    epilogue: tcgen05.ld the accumulator (each warp its 32-lane TMEM
-//                 quadrant), convert to T, store.  Two accumulators (2 x 256 TMEM
-//                 columns) let the epilogue of a tile overlap the next tile's MMAs.
-// Every wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT and the
-// CTA drains and frees its TMEM.
+// One persistent CTA per SM walks output tiles of (MT * 128) rows x 256 columns; 14 warps in
+// four roles:
+//   warp 0        TMA producer: per 64-wide k block MT 128B-swizzled boxes of X (128 rows x 64 k).
+//   warps 6..13   dequantisers: thread n owns weight column n of the tile.  It reads its packed
+//                 words straight from global memory (a warp reads 128 contiguous bytes per packed
+//                 row; three k blocks are kept in flight in registers), expands the 8 words of a
+//                 k block to 64 values of T with the magic-number trick (prmt + lop3, exact
+//                 subtract, one rounding multiply by the scale) and writes them as the 128-byte
+//                 row n of the K-major, 128B-swizzled B operand tile.  Shared memory therefore
+//                 carries each weight once (the operand tile), not twice.
+//   warp 1        MMA issuer: one thread issues, per k block, four tcgen05.mma (M128 N256 K16,
+//                 kind::f16, f32 accumulation in TMEM) for each of the MT row blocks - the row
+//                 blocks share the dequantised B tile - and commits to the mbarriers that free
+//                 the stages.
+//   warps 2..5    epilogue: tcgen05.ld the accumulators (each warp its 32-lane TMEM quadrant),
+//                 convert, store.  With MT = 1 two accumulators alternate so the epilogue of a
+//                 tile overlaps the next tile's MMAs; with MT = 2 the two row blocks fill TMEM.
+// Shared-memory bandwidth is what bounds this kernel (operand reads by the tensor core, operand
+// tile writes, TMA writes); MT = 2 halves the B traffic per flop.  Tiles are walked in bands of
+// rows so that the band of X and all of W stay in L2.
+// Every wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT and the CTA drains
+// and frees its TMEM.
 //
 // The same kernel serves the MoE grouped contractions (reference programs
 // examples/kernels/ragged/grouped_gemm.py:11-70 and examples/kernels/ragged/moe.py:12-53 with
-// int4 expert weights): rows are sorted by expert and padded to 128 per expert, so an M tile
-// belongs to one expert, read from the block -> expert table of the route alignment; the
-// number of M tiles is read from device memory (no host round trip).
+// int4 expert weights): rows are sorted by expert and padded to 128 per expert, so a 128-row
+// block belongs to one expert, read from the block -> expert table of the route alignment; the
+// number of row blocks is read from device memory (no host round trip).
 //   MODE 1  up|gate projection: the N tile is 128 gate columns + the matching 128 up columns,
 //           the epilogue writes T( silu(gate) * up ).
 //   MODE 2  down projection with f32 output rows (combined per token by a later kernel).
@@ -45,24 +50,30 @@ __device__ int g_w4a16_gemm_status = 0;
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int LOAD_STAGES = 4, B_STAGES = 3;
-constexpr int A_BYTES = BM * BK * 2;         // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;         // 32 KiB
-constexpr int RAW_BYTES = (BK / 8) * BN * 4; // 8 KiB
-constexpr int SCALE_BYTES = 1024;            // up to 2 rows x 256 columns x 2 bytes
+constexpr int A_BYTES = BM * BK * 2;  // one 128-row box of X, 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // dequantised operand tile, 32 KiB
 constexpr int DEQUANT_WARPS = 8;
 constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
-constexpr int SMEM_BYTES = 1024 + LOAD_STAGES * (A_BYTES + RAW_BYTES + SCALE_BYTES) + B_STAGES * B_BYTES + 256;
+constexpr int BAND_TILES = 8;         // row tiles per band of the tile walk
+
+template <int MT>
+struct Stages {
+  static constexpr int A = MT == 1 ? 5 : 3;   // stages of X
+  static constexpr int B = 3;                 // stages of the dequantised tile
+  static constexpr int SMEM = 1024 + A * MT * A_BYTES + B * B_BYTES + 256;
+};
 
 struct GemmParams {
   void* y;
-  int M, N, K;
-  int k_blocks;          // ceil(K / 64)
-  int m_tiles, n_tiles;
+  const uint32_t* packed;    // [E, K/8, WN]
+  const uint16_t* scales;    // [E, K/G, WN]
+  int M, K;
+  int WN;                    // columns of the weight matrix
+  int k_blocks;              // ceil(K / 64)
+  int m_tiles, n_tiles;      // tiles of (MT*128) rows, tiles of 256 accumulator columns
   int group_size;
-  int scale_rows;        // scale rows per k block: max(1, 64 / G)
   int twos_complement;
-  int second_box_offset;     // column distance of the second 128-column weight box (128, or I for up|gate)
+  int second_half_offset;    // weight-column distance of accumulator columns 128..255 (128, or I for up|gate)
   int out_cols;              // columns of the output matrix
   const int* total_rows;     // grouped modes: device pointer to the padded row count (multiple of 128)
   const int* tile_expert;    // grouped modes: expert of each 128-row block
@@ -70,39 +81,47 @@ struct GemmParams {
 
 constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
 
-template <typename T, int MODE>
+// Tile walk: bands of BAND_TILES row tiles; inside a band the row tile varies fastest.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& m_tile, int& n_tile) {
+  const int band_size = BAND_TILES * n_tiles;
+  const int band = tile / band_size;
+  const int in_band = tile - band * band_size;
+  const int rows_in_band = min(BAND_TILES, m_tiles - band * BAND_TILES);
+  n_tile = in_band / rows_in_band;
+  m_tile = band * BAND_TILES + (in_band - n_tile * rows_in_band);
+}
+
+template <typename T, int MODE, int MT>
 __global__ void __launch_bounds__(THREADS, 1)
-w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                  const __grid_constant__ CUtensorMap map_s, const GemmParams p) {
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  constexpr int A_STAGES = Stages<MT>::A, B_STAGES = Stages<MT>::B;
+  constexpr int ACC_BUFFERS = 2 / MT;       // accumulator sets that alternate between tiles
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t smem_a = base;
-  const uint32_t smem_b = smem_a + LOAD_STAGES * A_BYTES;
-  const uint32_t smem_raw_w = smem_b + B_STAGES * B_BYTES;
-  const uint32_t smem_sc = smem_raw_w + LOAD_STAGES * RAW_BYTES;
-  const uint32_t bars = smem_sc + LOAD_STAGES * SCALE_BYTES;
-  // barrier layout (8 bytes each)
-  const uint32_t full_load = bars;                         // [LOAD_STAGES] TMA bytes landed
-  const uint32_t empty_load = full_load + 8 * LOAD_STAGES; // [LOAD_STAGES] MMA done with A + dequantisers done with raw
-  const uint32_t full_b = empty_load + 8 * LOAD_STAGES;    // [B_STAGES] dequantised tile written
-  const uint32_t empty_b = full_b + 8 * B_STAGES;          // [B_STAGES] MMA done with it
-  const uint32_t tmem_full = empty_b + 8 * B_STAGES;       // [2] accumulator complete
-  const uint32_t tmem_empty = tmem_full + 16;              // [2] accumulator drained
-  const uint32_t tmem_slot = tmem_empty + 16;              // TMEM base address written by tcgen05.alloc
-  volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + (tmem_slot - base));
+  const uint32_t smem_b = smem_a + A_STAGES * MT * A_BYTES;
+  const uint32_t bars = smem_b + B_STAGES * B_BYTES;
+  const uint32_t full_a = bars;                        // [A_STAGES] TMA bytes landed
+  const uint32_t empty_a = full_a + 8 * A_STAGES;      // [A_STAGES] MMA done with the stage
+  const uint32_t full_b = empty_a + 8 * A_STAGES;      // [B_STAGES] dequantised tile written
+  const uint32_t empty_b = full_b + 8 * B_STAGES;      // [B_STAGES] MMA done with it
+  const uint32_t tmem_full = empty_b + 8 * B_STAGES;   // [2] accumulators complete
+  const uint32_t tmem_empty = tmem_full + 16;          // [2] accumulators drained
+  const uint32_t tmem_slot = tmem_empty + 16;          // TMEM base address written by tcgen05.alloc
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + (tmem_slot - base));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  // grouped modes: row blocks actually in use, read from device memory
   const int m_tiles = MODE == MODE_DENSE ? p.m_tiles : min(p.m_tiles, (*p.total_rows + BM - 1) / BM);
   const int tiles = m_tiles * p.n_tiles;
 
   if (tid == 0) {
-    for (int s = 0; s < LOAD_STAGES; ++s) {
-      mbar_init(full_load + 8 * s, 1);
-      mbar_init(empty_load + 8 * s, 1 + DEQUANT_WARPS);
+    for (int s = 0; s < A_STAGES; ++s) {
+      mbar_init(full_a + 8 * s, 1);
+      mbar_init(empty_a + 8 * s, 1);
     }
     for (int s = 0; s < B_STAGES; ++s) {
       mbar_init(full_b + 8 * s, DEQUANT_WARPS);
@@ -126,22 +145,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[m_tile];
-        // weight columns of the two 128-wide boxes of this N tile
-        const int col0 = MODE == MODE_UPGATE_SILU ? n_tile * 128 : n_tile * BN;
-        const int col1 = col0 + p.second_box_offset;
+        int m_tile, n_tile;
+        tile_coords(tile, m_tiles, p.n_tiles, m_tile, n_tile);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % LOAD_STAGES, phase = (it / LOAD_STAGES) & 1;
-          if (!mbar_wait(empty_load + 8 * s, phase ^ 1)) { ok = false; break; }
-          const uint32_t bar = full_load + 8 * s;
-          const int scale_row = (kb * BK) / p.group_size;
-          mbar_expect_tx(bar, A_BYTES + RAW_BYTES + uint32_t(p.scale_rows) * BN * 2);
-          tma_load_2d(smem_a + s * A_BYTES, &map_x, kb * BK, m_tile * BM, bar);
-          tma_load_3d(smem_raw_w + s * RAW_BYTES, &map_w, col0, kb * (BK / 8), expert, bar);
-          tma_load_3d(smem_raw_w + s * RAW_BYTES + RAW_BYTES / 2, &map_w, col1, kb * (BK / 8), expert, bar);
-          tma_load_3d(smem_sc + s * SCALE_BYTES, &map_s, col0, scale_row, expert, bar);
-          tma_load_3d(smem_sc + s * SCALE_BYTES + p.scale_rows * 256, &map_s, col1, scale_row, expert, bar);
+          const uint32_t s = it % A_STAGES;
+          if (!mbar_wait(empty_a + 8 * s, ((it / A_STAGES) & 1) ^ 1)) { ok = false; break; }
+          const uint32_t bar = full_a + 8 * s;
+          mbar_expect_tx(bar, MT * A_BYTES);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d(smem_a + (s * MT + mt) * A_BYTES, &map_x, kb * BK, (m_tile * MT + mt) * BM, bar);
         }
       }
       if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -154,21 +167,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-        const uint32_t acc = local & 1;
-        if (!mbar_wait(tmem_empty + 8 * acc, ((local >> 1) & 1) ^ 1)) { ok = false; break; }
+        const uint32_t acc = local % ACC_BUFFERS;
+        if (!mbar_wait(tmem_empty + 8 * acc, ((local / ACC_BUFFERS) & 1) ^ 1)) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + acc * (MT * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % LOAD_STAGES, t = it % B_STAGES;
-          if (!mbar_wait(full_load + 8 * s, (it / LOAD_STAGES) & 1) ||
+          const uint32_t s = it % A_STAGES, t = it % B_STAGES;
+          if (!mbar_wait(full_a + 8 * s, (it / A_STAGES) & 1) ||
               !mbar_wait(full_b + 8 * t, (it / B_STAGES) & 1)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint64_t desc_a = umma_desc_k_major_sw128(smem_a + s * A_BYTES);
           const uint64_t desc_b = umma_desc_k_major_sw128(smem_b + t * B_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements of 2 bytes = 32 bytes = 2 descriptor units
-            umma_f16(tmem_d, desc_a + uint64_t(2 * kk), desc_b + uint64_t(2 * kk), idesc, (kb | kk) != 0);
-          umma_commit(empty_load + 8 * s);
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint64_t desc_a = umma_desc_k_major_sw128(smem_a + (s * MT + mt) * A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements of 2 bytes = 32 bytes = 2 descriptor units
+              umma_f16(tmem_d + mt * BN, desc_a + uint64_t(2 * kk), desc_b + uint64_t(2 * kk), idesc, (kb | kk) != 0);
+          }
+          umma_commit(empty_a + 8 * s);
           umma_commit(empty_b + 8 * t);
         }
         if (ok) umma_commit(tmem_full + 8 * acc);
@@ -181,73 +197,79 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
     uint32_t local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-      const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-      const uint32_t acc = local & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full + 8 * acc, (local >> 1) & 1))) {
+      int m_tile, n_tile;
+      tile_coords(tile, m_tiles, p.n_tiles, m_tile, n_tile);
+      const uint32_t acc = local % ACC_BUFFERS;
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full + 8 * acc, (local / ACC_BUFFERS) & 1))) {
         if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
         break;
       }
       tcgen05_fence_after();
-      const int row = m_tile * BM + quadrant * 32 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quadrant * 32) << 16);
-      if (MODE == MODE_UPGATE_SILU) {
-        // accumulator columns 0..127 = gate, 128..255 = the matching up columns
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t gate[32], up[32];
-          tmem_load_32x32(taddr + c * 32, gate);
-          tmem_load_32x32(taddr + 128 + c * 32, up);
-          tmem_load_wait();
-          const int col = n_tile * 128 + c * 32;
-          if (row < p.M) {
-            uint16_t* dst = y + size_t(row) * p.out_cols + col;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float h[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const float gv = __uint_as_float(gate[8 * q + 2 * j + e]);
-                  const float uv = __uint_as_float(up[8 * q + 2 * j + e]);
-                  h[e] = gv * (1.0f / (1.0f + __expf(-gv))) * uv;  // silu(gate) * up in f32, one rounding
-                }
-                o[j] = uint32_t(Elem<T>::from_float(h[0])) | (uint32_t(Elem<T>::from_float(h[1])) << 16);
-              }
-              if (col + q * 8 < p.out_cols) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      } else {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = (m_tile * MT + mt) * BM + quadrant * 32 + lane;
+        const uint32_t taddr = tmem_base + acc * (MT * BN) + mt * BN + (uint32_t(quadrant * 32) << 16);
+        if (MODE == MODE_UPGATE_SILU) {
+          // accumulator columns 0..127 = gate, 128..255 = the matching up columns
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_load_32x32(taddr + c * 32, v);
-          tmem_load_wait();
-          const int col = n_tile * BN + c * 32;
-          if (row < p.M) {
-            if (MODE == MODE_GROUPED_F32) {
-              float* dst = reinterpret_cast<float*>(p.y) + size_t(row) * p.out_cols + col;
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                if (col + q * 4 < p.out_cols)
-                  *reinterpret_cast<uint4*>(dst + q * 4) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t gate[32], up[32];
+            tmem_load_32x32(taddr + c * 32, gate);
+            tmem_load_32x32(taddr + 128 + c * 32, up);
+            tmem_load_wait();
+            const int col = n_tile * 128 + c * 32;
+            if (row < p.M) {
               uint16_t* dst = y + size_t(row) * p.out_cols + col;
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                if (col + q * 8 < p.out_cols) {  // the column count is a multiple of 8
-                  uint4 o;
-                  o.x = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 0]))) |
-                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 1]))) << 16);
-                  o.y = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 2]))) |
-                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 3]))) << 16);
-                  o.z = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 4]))) |
-                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 5]))) << 16);
-                  o.w = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 6]))) |
-                        (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 7]))) << 16);
-                  *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float h[2];
+#pragma unroll
+                  for (int e = 0; e < 2; ++e) {
+                    const float gv = __uint_as_float(gate[8 * q + 2 * j + e]);
+                    const float uv = __uint_as_float(up[8 * q + 2 * j + e]);
+                    h[e] = gv * (1.0f / (1.0f + __expf(-gv))) * uv;  // silu(gate) * up in f32, one rounding
+                  }
+                  o[j] = uint32_t(Elem<T>::from_float(h[0])) | (uint32_t(Elem<T>::from_float(h[1])) << 16);
+                }
+                if (col + q * 8 < p.out_cols)
+                  *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32];
+            tmem_load_32x32(taddr + c * 32, v);
+            tmem_load_wait();
+            const int col = n_tile * BN + c * 32;
+            if (row < p.M) {
+              if (MODE == MODE_GROUPED_F32) {
+                float* dst = reinterpret_cast<float*>(p.y) + size_t(row) * p.out_cols + col;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  if (col + q * 4 < p.out_cols)
+                    *reinterpret_cast<uint4*>(dst + q * 4) =
+                        make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              } else {
+                uint16_t* dst = y + size_t(row) * p.out_cols + col;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if (col + q * 8 < p.out_cols) {  // the column count is a multiple of 8
+                    uint4 o;
+                    o.x = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 0]))) |
+                          (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 1]))) << 16);
+                    o.y = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 2]))) |
+                          (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 3]))) << 16);
+                    o.z = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 4]))) |
+                          (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 5]))) << 16);
+                    o.w = uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 6]))) |
+                          (uint32_t(Elem<T>::from_float(__uint_as_float(v[8 * q + 7]))) << 16);
+                    *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                  }
                 }
               }
             }
@@ -260,58 +282,98 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else {
     // ------------------------------ dequantisers --------------------------------
-    const int n = tid - 6 * 32;  // weight column of the tile owned by this thread, 0..255
+    const int n = tid - 6 * 32;  // accumulator column of the tile owned by this thread, 0..255
     const uint32_t magic = Elem<T>::kMagic2 ^ (p.twos_complement ? 0x00080008u : 0u);
     const uint32_t row_off = uint32_t(n) * 128u;
     const uint32_t swz = uint32_t(n & 7);
-    uint32_t it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-        const uint32_t s = it % LOAD_STAGES, t = it % B_STAGES;
-        ok = mbar_wait(full_load + 8 * s, (it / LOAD_STAGES) & 1) &&
-             mbar_wait(empty_b + 8 * t, ((it / B_STAGES) & 1) ^ 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        // the tile's 256 columns arrive as two boxes of 128 columns
-        const uint32_t raw = smem_raw_w + s * RAW_BYTES + uint32_t(n >> 7) * (RAW_BYTES / 2) + uint32_t(n & 127) * 4u;
-        const uint32_t sc = smem_sc + s * SCALE_BYTES + uint32_t(n >> 7) * uint32_t(p.scale_rows * 256) +
-                            uint32_t(n & 127) * 2u;
-        const uint32_t dst = smem_b + t * B_BYTES + row_off;
-        uint32_t s_lo, s_hi;  // scale of k 0..31 and of k 32..63 of this block, duplicated into both halves
-        {
-          uint16_t a, b;
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(a) : "r"(sc));
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b) : "r"(sc + (p.scale_rows > 1 ? 256 : 0)));
-          s_lo = uint32_t(a) | (uint32_t(a) << 16);
-          s_hi = uint32_t(b) | (uint32_t(b) << 16);
-        }
-#pragma unroll
-        for (int r = 0; r < BK / 8; ++r) {
-          uint32_t w;
-          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(raw + r * 512));
-          const uint32_t w4 = w >> 4;
-          const uint32_t scale2 = r < 4 ? s_lo : s_hi;
-          uint4 o;
-          o.x = lop3_and_xor_u32(prmt(w, w4, 0x0400), 0x000F000Fu, magic);  // (k0, k1)
-          o.y = lop3_and_xor_u32(prmt(w, w4, 0x0501), 0x000F000Fu, magic);  // (k2, k3)
-          o.z = lop3_and_xor_u32(prmt(w, w4, 0x0602), 0x000F000Fu, magic);  // (k4, k5)
-          o.w = lop3_and_xor_u32(prmt(w, w4, 0x0703), 0x000F000Fu, magic);  // (k6, k7)
-          o.x = Elem<T>::mul2(Elem<T>::sub2(o.x, Elem<T>::kBias2), scale2);
-          o.y = Elem<T>::mul2(Elem<T>::sub2(o.y, Elem<T>::kBias2), scale2);
-          o.z = Elem<T>::mul2(Elem<T>::sub2(o.z, Elem<T>::kBias2), scale2);
-          o.w = Elem<T>::mul2(Elem<T>::sub2(o.w, Elem<T>::kBias2), scale2);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + ((uint32_t(r) ^ swz) << 4)), "r"(o.x),
-                       "r"(o.y), "r"(o.z), "r"(o.w)
-                       : "memory");
-        }
-        fence_proxy_async();  // the tensor core reads this tile through the async proxy
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(full_b + 8 * t);
-          mbar_arrive(empty_load + 8 * s);
-        }
+    const int packed_rows = p.K >> 3, scale_rows = p.K / p.group_size;
+    const int my_tiles = tiles > int(blockIdx.x) ? (tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const int total = my_tiles * p.k_blocks;
+
+    struct Block {
+      uint32_t w[BK / 8];
+      uint32_t s_lo, s_hi;  // scale of k 0..31 and of k 32..63 of the block, duplicated into both halves
+    };
+    // Fetch state: walks this CTA's (tile, k block) sequence in order, three blocks ahead of the
+    // consumer; everything that depends only on the tile is recomputed when the tile changes.
+    const int group_shift = 31 - __clz(p.group_size);  // the group size is a power of two
+    int f_tile = int(blockIdx.x), f_kb = 0, f_left = total;
+    bool f_col_ok = false;
+    const uint32_t* f_w = p.packed;
+    const uint16_t* f_s = p.scales;
+    auto fetch = [&](Block& b) {
+      if (f_left <= 0) return;
+      --f_left;
+      if (f_kb == 0) {
+        int m_tile, n_tile;
+        tile_coords(f_tile, m_tiles, p.n_tiles, m_tile, n_tile);
+        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[m_tile];
+        const int col = (MODE == MODE_UPGATE_SILU ? n_tile * 128 : n_tile * BN) +
+                        (n < 128 ? n : p.second_half_offset + (n - 128));
+        f_col_ok = col < p.WN;
+        f_w = p.packed + size_t(expert) * packed_rows * p.WN + (f_col_ok ? col : 0);
+        f_s = p.scales + size_t(expert) * scale_rows * p.WN + (f_col_ok ? col : 0);
       }
+      const int rows_left = packed_rows - f_kb * (BK / 8);
+      if (f_col_ok && rows_left >= BK / 8) {
+        const uint32_t* q = f_w;
+#pragma unroll
+        for (int r = 0; r < BK / 8; ++r, q += p.WN) b.w[r] = __ldg(q);
+      } else {
+#pragma unroll
+        for (int r = 0; r < BK / 8; ++r) b.w[r] = (f_col_ok && r < rows_left) ? __ldg(f_w + size_t(r) * p.WN) : 0u;
+      }
+      const int g0 = (f_kb * BK) >> group_shift;
+      const int g1 = p.group_size < BK ? g0 + 1 : g0;
+      const uint32_t a = (f_col_ok && g0 < scale_rows) ? __ldg(f_s + size_t(g0) * p.WN) : 0u;
+      const uint32_t c = g1 == g0 ? a : ((f_col_ok && g1 < scale_rows) ? __ldg(f_s + size_t(g1) * p.WN) : 0u);
+      b.s_lo = a | (a << 16);
+      b.s_hi = c | (c << 16);
+      f_w += size_t(BK / 8) * p.WN;
+      if (++f_kb == p.k_blocks) {
+        f_kb = 0;
+        f_tile += int(gridDim.x);
+      }
+    };
+    bool ok = true;
+    auto consume = [&](int i, const Block& b) {
+      if (i >= total || !ok) return;
+      const uint32_t t = uint32_t(i) % B_STAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(empty_b + 8 * t, ((uint32_t(i) / B_STAGES) & 1) ^ 1));
+      if (!ok) return;
+      const uint32_t dst = smem_b + t * B_BYTES + row_off;
+#pragma unroll
+      for (int r = 0; r < BK / 8; ++r) {
+        const uint32_t w = b.w[r], w4 = w >> 4;
+        const uint32_t scale2 = r < 4 ? b.s_lo : b.s_hi;
+        uint4 o;
+        o.x = lop3_and_xor_u32(prmt(w, w4, 0x0400), 0x000F000Fu, magic);  // (k0, k1)
+        o.y = lop3_and_xor_u32(prmt(w, w4, 0x0501), 0x000F000Fu, magic);  // (k2, k3)
+        o.z = lop3_and_xor_u32(prmt(w, w4, 0x0602), 0x000F000Fu, magic);  // (k4, k5)
+        o.w = lop3_and_xor_u32(prmt(w, w4, 0x0703), 0x000F000Fu, magic);  // (k6, k7)
+        o.x = Elem<T>::mul2(Elem<T>::sub2(o.x, Elem<T>::kBias2), scale2);
+        o.y = Elem<T>::mul2(Elem<T>::sub2(o.y, Elem<T>::kBias2), scale2);
+        o.z = Elem<T>::mul2(Elem<T>::sub2(o.z, Elem<T>::kBias2), scale2);
+        o.w = Elem<T>::mul2(Elem<T>::sub2(o.w, Elem<T>::kBias2), scale2);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + ((uint32_t(r) ^ swz) << 4)), "r"(o.x),
+                     "r"(o.y), "r"(o.z), "r"(o.w)
+                     : "memory");
+      }
+      fence_proxy_async();  // the tensor core reads this tile through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_b + 8 * t);
+    };
+    Block b0, b1, b2;
+    fetch(b0);
+    fetch(b1);
+    fetch(b2);
+    for (int i = 0; i < total && ok; i += 3) {
+      consume(i, b0);
+      fetch(b0);
+      consume(i + 1, b1);
+      fetch(b1);
+      consume(i + 2, b2);
+      fetch(b2);
     }
     if (!ok && lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
   }
@@ -324,7 +386,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   }
 }
 
-
 int device_sms() {
   static int sms = [] {
     int device = 0, value = 0;
@@ -336,47 +397,42 @@ int device_sms() {
 }
 
 // x: [rows, K] activations; w: [E, K/8, WN] packed; s: [E, K/G, WN] scales; out: [rows, out_cols].
-template <typename T, int MODE>
-int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t experts, int64_t WN,
-                void* out, int64_t out_cols, int group_size, int zero_point, const int* total_rows,
-                const int* tile_expert, cudaStream_t stream) {
+template <typename T, int MODE, int MT>
+int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t WN, void* out,
+                int64_t out_cols, int group_size, int zero_point, const int* total_rows, const int* tile_expert,
+                cudaStream_t stream) {
   const int sms = device_sms();
   if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
   const CUtensorMapDataType type =
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   GemmParams p{};
   p.y = out;
+  p.packed = static_cast<const uint32_t*>(w);
+  p.scales = static_cast<const uint16_t*>(s);
   p.M = int(rows);
-  p.N = int(WN);
   p.K = int(K);
+  p.WN = int(WN);
   p.k_blocks = int((K + BK - 1) / BK);
-  p.m_tiles = int((rows + BM - 1) / BM);
+  p.m_tiles = int((rows + MT * BM - 1) / (MT * BM));
   p.n_tiles = MODE == MODE_UPGATE_SILU ? int(out_cols / 128) : int((out_cols + BN - 1) / BN);
   p.group_size = group_size;
-  p.scale_rows = group_size >= BK ? 1 : BK / group_size;
   p.twos_complement = zero_point == -1 ? 1 : 0;
-  p.second_box_offset = MODE == MODE_UPGATE_SILU ? int(out_cols) : 128;
+  p.second_half_offset = MODE == MODE_UPGATE_SILU ? int(out_cols) : 128;
   p.out_cols = int(out_cols);
   p.total_rows = total_rows;
   p.tile_expert = tile_expert;
 
-  CUtensorMap map_x, map_w, map_s;
+  CUtensorMap map_x;
   if (!make_tensor_map_2d(&map_x, type, x, uint64_t(rows), uint64_t(K), uint64_t(K) * 2, BM, BK,
-                          CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_tensor_map_3d(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, w, uint64_t(experts), uint64_t(K / 8), uint64_t(WN),
-                          uint64_t(WN) * 4, uint64_t(K / 8) * uint64_t(WN) * 4, BK / 8, 128,
-                          CU_TENSOR_MAP_SWIZZLE_NONE) ||
-      !make_tensor_map_3d(&map_s, type, s, uint64_t(experts), uint64_t(K / group_size), uint64_t(WN),
-                          uint64_t(WN) * 2, uint64_t(K / group_size) * uint64_t(WN) * 2, uint32_t(p.scale_rows), 128,
-                          CU_TENSOR_MAP_SWIZZLE_NONE))
+                          CU_TENSOR_MAP_SWIZZLE_128B))
     return INTENT_B200_ERR_UNSUPPORTED;
 
-  auto kernel = w4a16_gemm_kernel<T, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  auto kernel = w4a16_gemm_kernel<T, MODE, MT>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Stages<MT>::SMEM);
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_x, map_w, map_s, p);
+  kernel<<<grid, THREADS, Stages<MT>::SMEM, stream>>>(map_x, p);
   note_launch();
   return launch_status();
 }
@@ -393,8 +449,11 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
   if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(y)) return INTENT_B200_ERR_LAYOUT;
   if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
   if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
-  return launch_gemm<T, MODE_DENSE>(x.p, M, K, w.p, s.p, 1, N, y.p, N, group_size, zero_point, nullptr, nullptr,
-                                    stream);
+  if (M > BM)   // two row blocks per tile share every dequantised weight tile
+    return launch_gemm<T, MODE_DENSE, 2>(x.p, M, K, w.p, s.p, N, y.p, N, group_size, zero_point, nullptr, nullptr,
+                                         stream);
+  return launch_gemm<T, MODE_DENSE, 1>(x.p, M, K, w.p, s.p, N, y.p, N, group_size, zero_point, nullptr, nullptr,
+                                       stream);
 }
 
 // Grouped contractions over expert-sorted, 128-padded rows.
@@ -417,8 +476,8 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
   if (K == 0 || WN % 8 != 0 || (MODE == MODE_UPGATE_SILU && (WN % 256 != 0)) ||
       P > (1 << 24) || K > (1 << 24) || WN > (1 << 24))
     return INTENT_B200_ERR_UNSUPPORTED;
-  return launch_gemm<T, MODE>(x.p, P, K, w.p, s.p, E, WN, out.p, out_cols, group_size, zero_point,
-                              static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
+  return launch_gemm<T, MODE, 1>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
+                                 static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
 }
 
 }  // namespace
