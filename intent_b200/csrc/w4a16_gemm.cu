@@ -52,7 +52,9 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // one 128-row box of X, 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // dequantised operand tile, 32 KiB
-constexpr int DEQUANT_WARPS = 8;
+constexpr int DEQUANT_WARPS = 16;          // two threads per weight column, each expands half a k block
+constexpr int DQ_PARTS = DEQUANT_WARPS / 8;  // threads per column
+constexpr int DQ_ROWS = (BK / 8) / DQ_PARTS; // packed words per thread and k block
 constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
 constexpr int BAND_TILES = 8;         // row tiles per band of the tile walk
 
@@ -282,7 +284,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
     }
   } else {
     // ------------------------------ dequantisers --------------------------------
-    const int n = tid - 6 * 32;  // accumulator column of the tile owned by this thread, 0..255
+    const int n = (tid - 6 * 32) & 255;   // accumulator column of the tile owned by this thread, 0..255
+    const int part = (tid - 6 * 32) >> 8; // which DQ_ROWS packed rows of every k block it expands
     const uint32_t magic = Elem<T>::kMagic2 ^ (p.twos_complement ? 0x00080008u : 0u);
     const uint32_t row_off = uint32_t(n) * 128u;
     const uint32_t swz = uint32_t(n & 7);
@@ -291,7 +294,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
     const int total = my_tiles * p.k_blocks;
 
     struct Block {
-      uint32_t w[BK / 8];
+      uint32_t w[DQ_ROWS];
       uint32_t s_lo, s_hi;  // scale of k 0..31 and of k 32..63 of the block, duplicated into both halves
     };
     // Fetch state: walks this CTA's (tile, k block) sequence in order, three blocks ahead of the
@@ -314,14 +317,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
         f_w = p.packed + size_t(expert) * packed_rows * p.WN + (f_col_ok ? col : 0);
         f_s = p.scales + size_t(expert) * scale_rows * p.WN + (f_col_ok ? col : 0);
       }
-      const int rows_left = packed_rows - f_kb * (BK / 8);
-      if (f_col_ok && rows_left >= BK / 8) {
-        const uint32_t* q = f_w;
+      const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
+      if (f_col_ok && rows_left >= DQ_ROWS) {
+        const uint32_t* q = f_w + size_t(part * DQ_ROWS) * p.WN;
 #pragma unroll
-        for (int r = 0; r < BK / 8; ++r, q += p.WN) b.w[r] = __ldg(q);
+        for (int r = 0; r < DQ_ROWS; ++r, q += p.WN) b.w[r] = __ldg(q);
       } else {
 #pragma unroll
-        for (int r = 0; r < BK / 8; ++r) b.w[r] = (f_col_ok && r < rows_left) ? __ldg(f_w + size_t(r) * p.WN) : 0u;
+        for (int r = 0; r < DQ_ROWS; ++r)
+          b.w[r] = (f_col_ok && r < rows_left) ? __ldg(f_w + size_t(part * DQ_ROWS + r) * p.WN) : 0u;
       }
       const int g0 = (f_kb * BK) >> group_shift;
       const int g1 = p.group_size < BK ? g0 + 1 : g0;
@@ -343,8 +347,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       if (!ok) return;
       const uint32_t dst = smem_b + t * B_BYTES + row_off;
 #pragma unroll
-      for (int r = 0; r < BK / 8; ++r) {
-        const uint32_t w = b.w[r], w4 = w >> 4;
+      for (int j = 0; j < DQ_ROWS; ++j) {
+        const int r = part * DQ_ROWS + j;   // packed row (16-byte chunk) of the k block
+        const uint32_t w = b.w[j], w4 = w >> 4;
         const uint32_t scale2 = r < 4 ? b.s_lo : b.s_hi;
         uint4 o;
         o.x = lop3_and_xor_u32(prmt(w, w4, 0x0400), 0x000F000Fu, magic);  // (k0, k1)
