@@ -280,13 +280,17 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           *reinterpret_cast<float4*>(mine + m * kUnitCols + 4 * g) =
               make_float4(facc[mb][0 + hh], facc[mb][2 + hh], facc[mb][4 + hh], facc[mb][6 + hh]);
       }
-    __threadfence();
+    // One acq_rel ticket per unit: the warp barrier orders every lane's stores before lane 0's
+    // release, and the acquire side of the same atomic covers the reads of the last arriver.
     __syncwarp();
     int last = 0;
-    if (lane == 0) last = atomicAdd(&p.counters[tile], 1) == p.chunks - 1;
+    if (lane == 0) {
+      int old;
+      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile) : "memory");
+      last = old == p.chunks - 1;
+    }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
-      __threadfence();
       // lane = 8*q + v: quarter q adds chunks q, q+4, ... for columns 4v..4v+3 (independent loads,
       // all in flight together), then the four quarters are added in a fixed order
       const float* all = p.scratch + size_t(tile) * p.chunks * part;

@@ -85,3 +85,11 @@ def check(status: int, entry_name: str, observation=None) -> None:
         raise CompilationStageError("provider_invocation",
                                     f"{entry_name} returned status {status}: {status_string(status)}",
                                     observation=observation, status=status)
+
+
+def set_gemv_launch_overlap(enabled: bool) -> None:
+    """Process-wide switch of the bandwidth kernel's programmatic dependent launch: a launch may
+    request its packed weights while the previous kernel on the stream is still running.  Only
+    valid when the weights are not written by the kernel launched immediately before (static model
+    weights in a decode loop)."""
+    check(library().intent_b200_w4a16_gemv_overlap(1 if enabled else 0), "intent_b200_w4a16_gemv_overlap")
