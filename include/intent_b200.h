@@ -94,6 +94,9 @@ INTENT_B200_API int64_t intent_b200_w4a16_gemv_workspace_bytes(int64_t M, int64_
 /* Status word of the tensor-core W4A16 kernel: 0, or INTENT_B200_ERR_TIMEOUT if a bounded
  * device-side wait expired in an earlier launch.  Synchronises the device and clears the word. */
 INTENT_B200_API int intent_b200_w4a16_gemm_device_status(void);
+/* Dense W4A16 with M >= 512 runs on CTA pairs (tcgen05 cta_group::2); 0 forces the single-CTA kernel.
+ * For measurement and tests; process-global. */
+INTENT_B200_API int intent_b200_w4a16_gemm_pairs(int32_t enable);
 /* Launch-latency overlap of the bandwidth kernel (programmatic dependent
  * launch).  When enabled, a launch may start and request its packed weights
  * while the kernel before it on the stream is still running; it waits for that

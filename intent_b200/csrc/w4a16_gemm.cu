@@ -47,6 +47,10 @@ namespace ib200 {
 
 __device__ int g_w4a16_gemm_status = 0;
 
+template <typename T>
+int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
+                    int group_size, int zero_point, cudaStream_t stream);
+
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
@@ -454,6 +458,10 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
   if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(y)) return INTENT_B200_ERR_LAYOUT;
   if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
   if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
+  {  // large M: CTA pairs, each CTA dequantises half of every weight tile
+    const int status = w4a16_gemm_pair<T>(x.p, M, K, w.p, s.p, N, y.p, group_size, zero_point, stream);
+    if (status != INTENT_B200_ERR_UNSUPPORTED) return status;
+  }
   if (M > BM)   // two row blocks per tile share every dequantised weight tile
     return launch_gemm<T, MODE_DENSE, 2>(x.p, M, K, w.p, s.p, N, y.p, N, group_size, zero_point, nullptr, nullptr,
                                          stream);

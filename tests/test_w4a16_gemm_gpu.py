@@ -78,3 +78,25 @@ def test_gemm_full_size_prefill_rows(cuda_device):
     assert max_abs_rel(out[rows.to(cuda_device)].cpu(), ref) <= 2e-2
     # every tile was written: no element is left at the fill value
     assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 512, 256), (1100, 1024, 776), (2048, 2048, 2048)])
+def test_cta_pair_kernel_equals_single_cta_kernel(cuda_device, M, K, N):
+    """M >= 512 runs on CTA pairs (cta_group::2); the k loop and the rounding are the same as in the
+    single-CTA kernel, so the two must agree bit for bit, and with the oracle within tolerance."""
+    lib = native.library()
+    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=128, seed=9)
+    artifact = _compile("bf16", 128, 8)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    try:
+        lib.intent_b200_w4a16_gemm_pairs(1)
+        paired = artifact.run(xd, pd, sd)
+        lib.intent_b200_w4a16_gemm_pairs(0)
+        single = artifact.run(xd, pd, sd)
+        torch.cuda.synchronize()
+    finally:
+        lib.intent_b200_w4a16_gemm_pairs(1)
+    assert _device_status() == 0
+    assert torch.equal(paired, single)
+    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
+    assert max_abs_rel(paired.cpu(), ref) <= 2e-2
