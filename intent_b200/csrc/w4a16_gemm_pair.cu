@@ -36,7 +36,7 @@ constexpr int PAIR_ROWS = 2 * MT * BM;      // 512
 constexpr int A_BYTES = BM * BK * 2;        // one 128-row box of X
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the operand tile, 16 KiB
 constexpr int A_STAGES = 3, B_STAGES = 4;
-constexpr int DEQUANT_WARPS = 8;
+constexpr int DEQUANT_WARPS = 16;
 constexpr int DQ_PARTS = DEQUANT_WARPS * 32 / (BN / 2);  // threads per weight column (2)
 constexpr int DQ_ROWS = (BK / 8) / DQ_PARTS;             // packed words per thread and k block (4)
 constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
