@@ -375,7 +375,7 @@ def run_prefill(args, rank: int, world: int, device):
                      "traffic": NCU_TRAFFIC_BYTES.get("prefill"), "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                      "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4),
                      "frac_of_nominal_2250": round(achieved / 2250.0, 4),
-                     "algorithmic_flops_per_launch": per_launch_flops, "kernel": "w4a16_gemm_kernel",
+                     "algorithmic_flops_per_launch": per_launch_flops, "kernel": "w4a16_gemm_pair_kernel",
                      "ms_per_launch": round(ms, 5)},
         "e2e": {"value": round(flops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * n_local * 2,
