@@ -79,10 +79,21 @@ def return_rows(rows, plan: ExchangePlan, group=None):
 class ExpertParallelMoE:
     """Expert-parallel SiLU-gated int4 MoE FFN.  ``experts`` is the global expert count,
     ``tokens`` the number of tokens routed by THIS rank per call; every rank holds the weights of
-    its own ``experts // world`` experts."""
+    its own ``experts // world`` experts.
+
+    Two exchange modes:
+
+    * exact (default): rows travel with their true per-rank counts.  The counts have to reach the
+      host as split sizes of the collective, which costs one device -> host read per step.
+    * ``capacity_factor=f``: every rank sends a fixed ``cap = ceil(f * routes / world)`` rows to every
+      rank (unused slots are zero rows), so nothing is read back and the whole step is
+      asynchronous.  If a rank ever gets more than ``cap`` routes for one destination the step's
+      result is incomplete; that is recorded on the device and :meth:`check_overflow` raises.
+    """
 
     def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
-                 act_dtype="bf16", capacity_rows=None, target=None, group=None):
+                 act_dtype="bf16", capacity_rows=None, capacity_factor=None, target=None, group=None):
+        import torch
         import torch.distributed as dist
 
         from . import programs
@@ -97,13 +108,18 @@ class ExpertParallelMoE:
         self.local_experts = experts // self.world
         self.tokens, self.hidden, self.top_k = tokens, hidden, top_k
         self.routes = tokens * top_k
-        # rows this rank may receive; the worst case is every route of every rank
-        self.capacity = capacity_rows or self.routes * self.world
+        self.capacity_factor = capacity_factor
+        if capacity_factor is None:
+            self.slot_rows = 1                           # spans are exactly as long as their counts
+            self.capacity = capacity_rows or self.routes * self.world
+        else:
+            self.slot_rows = -(-int(capacity_factor * self.routes) // self.world)
+            self.capacity = self.slot_rows * self.world   # rows sent and received per step, fixed
         self.router = _compile(programs.moe_route_top2, target=target)
         # sorting routes by destination rank is the same stable partition as the expert alignment
-        self.by_rank = MoEAlignment.build(tokens=tokens, top_k=top_k, experts=self.world, block_size=1,
-                                          target=target)
-        rank_constexprs = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": self.world, "BLOCK_SIZE": 1}
+        self.by_rank = MoEAlignment.build(tokens=tokens, top_k=top_k, experts=self.world,
+                                          block_size=self.slot_rows, target=target)
+        rank_constexprs = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": self.world, "BLOCK_SIZE": self.slot_rows}
         self.send_positions = _compile(programs.moe_route_positions, target=target, constexprs=rank_constexprs)
         self.gather = _compile(programs.moe_gather_rows, target=target,
                                constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k})
@@ -111,31 +127,55 @@ class ExpertParallelMoE:
                                  experts=self.local_experts, top_k=1, group_size=group_size,
                                  zero_point=zero_point, act_dtype=act_dtype, target=target)
         self.combine = _compile(programs.moe_combine, target=target)
+        self._overflow = None
+        self._torch = torch
+
+    def check_overflow(self) -> None:
+        """Capacity mode: raise if any step since the last check had more routes for one rank than
+        fit its slot (reads one device word)."""
+        if self._overflow is not None and bool(self._overflow.item()):
+            self._overflow.zero_()
+            raise RuntimeError("expert-parallel exchange overflowed its capacity; raise capacity_factor")
+
+    def _send_experts(self, ids, sorted_routes, rows):
+        """Local expert id of every sent row; rows that are padding get an id no expert matches."""
+        torch = self._torch
+        index = sorted_routes[:rows].long()
+        valid = index < self.routes
+        chosen = ids.flatten()[index.clamp(max=self.routes - 1)] % self.local_experts
+        return torch.where(valid, chosen, torch.full_like(chosen, self.local_experts)).to(torch.int32)
 
     def forward(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):
         """logits [T, E] f32 and x [T, H] of this rank's tokens; weights of this rank's experts.
         Returns y [T, H] f32."""
-        import torch
-
+        torch = self._torch
         ids, weights = self.router.run(logits)
         destination = torch.div(ids, self.local_experts, rounding_mode="floor").to(torch.int32)
-        sorted_routes, _, total = self.by_rank.run(destination)            # routes grouped by destination rank
-        counts = torch.bincount(destination.flatten(), minlength=self.world)
-        plan = exchange_counts(counts, self.group)
-        send_rows = self.gather.run(x, sorted_routes, total)[: self.routes]
-        send_experts = (ids.flatten()[sorted_routes[: self.routes].long()] % self.local_experts).to(torch.int32)
+        call = self.by_rank.prepare(destination)
+        call.launch()                                                     # routes grouped by destination rank
+        sorted_routes, _, total = call.result()
+        if self.capacity_factor is None:
+            plan = exchange_counts(call.counts, self.group)               # the one host read of the step
+            n_send, n = self.routes, plan.received_rows
+            if n > self.capacity:
+                raise RuntimeError(f"received {n} rows, capacity is {self.capacity}")
+        else:
+            plan = ExchangePlan([self.slot_rows] * self.world, [self.slot_rows] * self.world)
+            n_send = n = self.capacity
+            over = (total != self.capacity).to(torch.int32)
+            self._overflow = over if self._overflow is None else torch.maximum(self._overflow, over)
+        send_rows = self.gather.run(x, sorted_routes, total)[:n_send]
+        send_experts = self._send_experts(ids, sorted_routes, n_send)
         received = dispatch_rows(send_rows, plan, self.group)
         received_experts = dispatch_rows(send_experts.unsqueeze(1), plan, self.group)
-        n = plan.received_rows
-        if n > self.capacity:
-            raise RuntimeError(f"received {n} rows, capacity is {self.capacity}")
         results = torch.zeros((n, self.hidden), dtype=torch.float32, device=x.device)
         if n:
             rows, positions = self.local.experts_forward(received, received_experts.contiguous(), up_gate_packed,
-                                                         up_gate_scales, down_packed, down_scales)
+                                                         up_gate_scales, down_packed, down_scales,
+                                                         clear_positions=self.capacity_factor is not None)
             ones = torch.ones((n, 1), dtype=torch.float32, device=x.device)
             self.combine.run(rows, positions[:n], ones, results)            # back to arrival order
-        returned = return_rows(results, plan, self.group)                   # [routes, H] in send order
+        returned = return_rows(results, plan, self.group)                   # [rows sent, H] in send order
         send_position = self.send_positions.run(sorted_routes, total)       # route -> slot in send order
         y = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
         self.combine.run(returned, send_position, weights, y)

@@ -142,11 +142,19 @@ class MoEW4A16FFN:
         """logits [T, E_total] f32 -> (ids [T,2] i32, weights [T,2] f32)."""
         return self.router.run(logits)
 
-    def experts_forward(self, x, topk_ids, up_gate_packed, up_gate_scales, down_packed, down_scales):
+    def experts_forward(self, x, topk_ids, up_gate_packed, up_gate_scales, down_packed, down_scales,
+                        clear_positions=False):
         """Rows of the down projection in the expert-sorted layout plus the inverse map:
-        returns (rows f32 [P, H], route_positions i32 [T*top_k])."""
+        returns (rows f32 [P, H], route_positions i32 [T*top_k]).  ``clear_positions``: routes whose
+        expert id matches no local expert (padding of a fixed-capacity exchange) get position 0."""
         sorted_routes, expert_blocks, total = self.alignment.run(topk_ids)
-        positions = self.positions.run(sorted_routes, total)
+        if clear_positions:
+            import torch
+
+            positions = torch.zeros((self.tokens * self.top_k,), dtype=torch.int32, device=x.device)
+            self.positions(sorted_routes, total, positions)
+        else:
+            positions = self.positions.run(sorted_routes, total)
         rows = self.gather.run(x, sorted_routes, total)
         hidden = self.up_gate.run(rows, expert_blocks, total, up_gate_packed, up_gate_scales)
         out = self.down.run(hidden, expert_blocks, total, down_packed, down_scales)

@@ -47,6 +47,25 @@ def _ep_worker(rank, world, port, results):
                dev["down_packed"][ex].contiguous(), dev["down_scales"][ex].contiguous())
         torch.cuda.synchronize()
         moe_ok = bool(torch.equal(y, expected[rows]))
+        # fixed-capacity exchange: asynchronous, same bits while nothing overflows
+        capped = ExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
+                                   capacity_factor=1.5, target=target)
+        y_capped = capped(dev["logits"][rows].contiguous(), dev["x"][rows].contiguous(),
+                          dev["up_gate_packed"][ex].contiguous(), dev["up_gate_scales"][ex].contiguous(),
+                          dev["down_packed"][ex].contiguous(), dev["down_scales"][ex].contiguous())
+        capped.check_overflow()
+        moe_ok = moe_ok and bool(torch.equal(y_capped, expected[rows]))
+        # a capacity that is too small is reported, not silently wrong
+        tiny = ExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
+                                 capacity_factor=0.5, target=target)
+        tiny(dev["logits"][rows].contiguous(), dev["x"][rows].contiguous(),
+             dev["up_gate_packed"][ex].contiguous(), dev["up_gate_scales"][ex].contiguous(),
+             dev["down_packed"][ex].contiguous(), dev["down_scales"][ex].contiguous())
+        try:
+            tiny.check_overflow()
+            moe_ok = False
+        except RuntimeError:
+            pass
 
         # column-sharded dense prefill
         x, p, s = ib.workloads.w4a16_inputs(256, 1024, 1024, dtype=torch.bfloat16, seed=3)
