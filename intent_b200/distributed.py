@@ -182,3 +182,58 @@ class ExpertParallelMoE:
         return y
 
     __call__ = forward
+
+    def prepare(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):
+        """Capacity mode only: bind the whole step to fixed buffers (all shapes are static), so that
+        ``launch()`` is a short sequence of pre-bound kernel launches and collectives on those
+        buffers.  Returns an object whose ``launch()`` yields y [T, H] f32 (same bits as forward)."""
+        if self.capacity_factor is None:
+            raise NotImplementedError("prepare() needs the fixed-capacity exchange (capacity_factor=...)")
+        return PreparedExpertParallel(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales)
+
+
+class PreparedExpertParallel:
+    def __init__(self, ep: ExpertParallelMoE, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):
+        import torch
+
+        self.ep = ep
+        n, device = ep.capacity, x.device
+        self.router = ep.router.prepare(logits)
+        self.ids, self.weights = self.router.result()
+        self.destination = torch.empty_like(self.ids)
+        self.by_rank = ep.by_rank.prepare(self.destination)
+        self.sorted_routes, _, self.total = self.by_rank.result()
+        self.gather = ep.gather.prepare(x, self.sorted_routes, self.total)
+        self.send_rows = self.gather.result()[:n]
+        self.received = torch.empty((n, ep.hidden), dtype=x.dtype, device=device)
+        self.received_experts = torch.empty((n, 1), dtype=torch.int32, device=device)
+        self.results = torch.zeros((n, ep.hidden), dtype=torch.float32, device=device)
+        self.local = ep.local.prepare(self.received, self.received_experts,
+                                      torch.ones((n, 1), dtype=torch.float32, device=device), up_gate_packed,
+                                      up_gate_scales, down_packed, down_scales, self.results, clear_positions=True)
+        self.returned = torch.empty((n, ep.hidden), dtype=torch.float32, device=device)
+        self.send_position = ep.send_positions.prepare(self.sorted_routes, self.total)
+        self.y = torch.zeros((x.shape[0], ep.hidden), dtype=torch.float32, device=device)
+        self.combine = ep.combine.prepare(self.returned, self.send_position.result(), self.weights, self.y)
+        self.splits = [ep.slot_rows] * ep.world
+
+    def launch(self):
+        import torch
+        import torch.distributed as dist
+
+        ep = self.ep
+        self.router.launch()
+        torch.div(self.ids, ep.local_experts, rounding_mode="floor", out=self.destination)
+        self.by_rank.launch()
+        over = (self.total != ep.capacity).to(torch.int32)
+        ep._overflow = over if ep._overflow is None else torch.maximum(ep._overflow, over)
+        self.gather.launch()
+        send_experts = ep._send_experts(self.ids, self.sorted_routes, ep.capacity).unsqueeze(1)
+        dist.all_to_all_single(self.received, self.send_rows, self.splits, self.splits, group=ep.group)
+        dist.all_to_all_single(self.received_experts, send_experts, self.splits, self.splits, group=ep.group)
+        self.local.launch()                      # zeroes `results`, then un-permutes the expert rows into it
+        dist.all_to_all_single(self.returned, self.results, self.splits, self.splits, group=ep.group)
+        self.send_position.launch()
+        self.y.zero_()
+        self.combine.launch()
+        return self.y

@@ -172,3 +172,49 @@ class MoEW4A16FFN:
         return y
 
     __call__ = forward
+
+    def prepare(self, x, topk_ids, topk_weights, up_gate_packed, up_gate_scales, down_packed, down_scales, y,
+                clear_positions=False):
+        """Bind the whole chain to fixed buffers once; ``launch()`` then replays it without any
+        per-call validation or allocation (same results as :meth:`forward`).  ``y`` is zeroed by
+        every launch unless ``launch(accumulate=True)``."""
+        import torch
+
+        align = self.alignment.prepare(topk_ids)
+        sorted_routes, expert_blocks, total = align.result()
+        positions = torch.zeros((topk_ids.shape[0] * self.top_k,), dtype=torch.int32, device=x.device)
+        full_positions = torch.zeros((self.tokens * self.top_k,), dtype=torch.int32, device=x.device)
+        position_call = self.positions.prepare(sorted_routes, total, outputs=(full_positions,))
+        positions = full_positions[: topk_ids.shape[0] * self.top_k]
+        gather_call = self.gather.prepare(x, sorted_routes, total)
+        up_call = self.up_gate.prepare(gather_call.result(), expert_blocks, total, up_gate_packed, up_gate_scales)
+        down_call = self.down.prepare(up_call.result(), expert_blocks, total, down_packed, down_scales)
+        combine_call = self.combine.prepare(down_call.result(), positions, topk_weights, y)
+        return PreparedFFN(align, position_call, gather_call, up_call, down_call, combine_call, full_positions, y,
+                           clear_positions)
+
+
+@dataclass
+class PreparedFFN:
+    align: object
+    position_call: object
+    gather_call: object
+    up_call: object
+    down_call: object
+    combine_call: object
+    positions: object
+    y: object
+    clear_positions: bool
+
+    def launch(self, accumulate: bool = False):
+        self.align.launch()
+        if self.clear_positions:
+            self.positions.zero_()
+        self.position_call.launch()
+        self.gather_call.launch()
+        self.up_call.launch()
+        self.down_call.launch()
+        if not accumulate:
+            self.y.zero_()
+        self.combine_call.launch()
+        return self.y

@@ -55,6 +55,14 @@ def _ep_worker(rank, world, port, results):
                           dev["down_packed"][ex].contiguous(), dev["down_scales"][ex].contiguous())
         capped.check_overflow()
         moe_ok = moe_ok and bool(torch.equal(y_capped, expected[rows]))
+        # the same step bound once to fixed buffers and replayed twice
+        prepared = capped.prepare(dev["logits"][rows].contiguous(), dev["x"][rows].contiguous(),
+                                  dev["up_gate_packed"][ex].contiguous(), dev["up_gate_scales"][ex].contiguous(),
+                                  dev["down_packed"][ex].contiguous(), dev["down_scales"][ex].contiguous())
+        prepared.launch()
+        y_prepared = prepared.launch()
+        capped.check_overflow()
+        moe_ok = moe_ok and bool(torch.equal(y_prepared, expected[rows]))
         # a capacity that is too small is reported, not silently wrong
         tiny = ExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
                                  capacity_factor=0.5, target=target)
