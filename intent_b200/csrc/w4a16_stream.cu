@@ -62,6 +62,7 @@ struct StreamParams {
   int units;       // tiles * chunks
   int slots;       // shared-memory slots per CTA
   int slot_bytes;  // weight unit (+ activation box), multiple of 1024
+  int own_tiles;   // column tiles every CTA owns whole (reduced in shared memory); the rest is split over K
   int twos_complement;
   int overlap;
   int* status;
@@ -95,25 +96,52 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   float* corr = reinterpret_cast<float*>(base_ptr + corr_offset);
   uint4* xs = reinterpret_cast<uint4*>(base_ptr + corr_offset + size_t(p.groups) * CP * 4);  // [chunks*32][M]
   const uint32_t xs_addr = base + uint32_t(corr_offset) + uint32_t(p.groups) * CP * 4;
+  // partial sums and ticket counters of the column tiles this CTA owns whole
+  const size_t own_offset = corr_offset + size_t(p.groups) * CP * 4 + (XSTAGED ? size_t(p.chunks) * kUnitRows * p.M * 16 : 0);
+  int* own_count = reinterpret_cast<int*>(base_ptr + own_offset);
+  float* own_part = reinterpret_cast<float*>(base_ptr + own_offset + 256);
 
   // ---- this CTA's unit range -----------------------------------------------------
+  // Units of this CTA: first its share of the K-split ("left-over") column tiles, whose partial sums
+  // meet in global scratch - their store/ticket round trips then overlap the rest of the stream - and
+  // then every K chunk of the column tiles it owns whole, which are reduced in shared memory.
   const long long grid = gridDim.x;
-  const int u0 = int((long long)blockIdx.x * p.units / grid);
-  const int u1 = int((long long)(blockIdx.x + 1) * p.units / grid);
-  const int n_units = u1 - u0;
+  const int left_base = p.own_tiles * int(grid) * p.chunks;   // first unit of the K-split tiles
+  const int left_total = p.units - left_base;
+  const int l0 = int((long long)blockIdx.x * left_total / grid);
+  const int l1 = int((long long)(blockIdx.x + 1) * left_total / grid);
+  const int n_left = l1 - l0;
+  const int n_units = n_left + p.own_tiles * p.chunks;
+  auto unit_of = [&](int j, int& tile, int& chunk) {   // returns true for a unit of an owned tile
+    if (j < n_left) {
+      const int u = left_base + l0 + j;
+      tile = u / p.chunks;
+      chunk = u - tile * p.chunks;
+      return false;
+    }
+    const int jj = j - n_left;
+    const int local = jj / p.chunks;
+    tile = int(blockIdx.x) * p.own_tiles + local;
+    chunk = jj - local * p.chunks;
+    return true;
+  };
   const uint32_t x_bytes = XSTAGED ? 0u : uint32_t(p.M) * 512u;
 
   auto slot_addr = [&](int j) { return base + uint32_t(j % p.slots) * p.slot_bytes; };
   auto bar_addr = [&](int j) { return bars + uint32_t(j % p.slots) * 8u; };
   auto issue_weights = [&](int j) {
-    const int u = u0 + j;
-    const int tile = u / p.chunks, chunk = u - tile * p.chunks;
+    int tile, chunk;
+    unit_of(j, tile, chunk);
     mbar_expect_tx(bar_addr(j), kUnitWeightBytes + GPC * 64 + x_bytes);
     tma_load_2d(slot_addr(j), &map_w, tile * kUnitCols, chunk * kUnitRows, bar_addr(j));
     tma_load_2d(slot_addr(j) + kUnitWeightBytes, &map_s, tile * kUnitCols, chunk * GPC, bar_addr(j));
   };
   auto issue_activations = [&](int j) {
-    if (!XSTAGED) tma_load_2d(slot_addr(j) + kUnitActOffset, &map_x, ((u0 + j) % p.chunks) * 256, 0, bar_addr(j));
+    if (!XSTAGED) {
+      int tile, chunk;
+      unit_of(j, tile, chunk);
+      tma_load_2d(slot_addr(j) + kUnitActOffset, &map_x, chunk * 256, 0, bar_addr(j));
+    }
   };
 
   // ---- start the weight stream before anything else ----------------------------
@@ -135,7 +163,8 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // in RPG adjacent lanes and are added by a fixed-order butterfly.
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
     const int k8 = p.K >> 3;
-    const int touched = XSTAGED ? p.chunks : min(p.chunks, n_units);
+    const bool all_chunks = XSTAGED || p.own_tiles > 0;
+    const int touched = all_chunks ? p.chunks : min(p.chunks, n_left);
     const int rows = touched * kUnitRows;
     const int total = rows * p.M;
     for (int start = 0; start < total; start += THREADS) {
@@ -146,7 +175,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (active) {
         m = i / rows;
         const int lr = i - m * rows;
-        const int chunk = XSTAGED ? lr / kUnitRows : (u0 + lr / kUnitRows) % p.chunks;
+        const int chunk = all_chunks ? lr / kUnitRows : (left_base + l0 + lr / kUnitRows) % p.chunks;
         row = chunk * kUnitRows + (lr % kUnitRows);
         active = row < k8;
         uint4 o = make_uint4(0, 0, 0, 0);  // rows past K/8 (last chunk) are staged as zeros
@@ -166,6 +195,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (active && (row % RPG) == 0) corr[(row / RPG) * CP + m] = -partial;
     }
   }
+  for (int i = tid; i < p.own_tiles; i += THREADS) own_count[i] = 0;
   __syncthreads();
 
   uint32_t magic_a, magic_b;
@@ -184,8 +214,8 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 
   for (int j = warp; j < n_units; j += WARPS) {
-    const int u = u0 + j;
-    const int tile = u / p.chunks, chunk = u - tile * p.chunks;
+    int tile, chunk;
+    const bool owned = unit_of(j, tile, chunk);
     if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(j), (j / p.slots) & 1))) {
       if (lane == 0) atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);  // this unit's loads never completed
       break;
@@ -270,7 +300,9 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     // ---- the unit's partial goes to scratch; the last ticket of the tile finishes it ----
     // accumulator element (mb, i): row m = 8*mb + 2t + (i & 1), column 4g + (i >> 1)
-    float* mine = p.scratch + (size_t(tile) * p.chunks + chunk) * part;
+    const int tile_local = tile - int(blockIdx.x) * p.own_tiles;
+    float* mine = owned ? own_part + (size_t(tile_local) * p.chunks + chunk) * part
+                        : p.scratch + (size_t(tile) * p.chunks + chunk) * part;
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
@@ -280,25 +312,34 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           *reinterpret_cast<float4*>(mine + m * kUnitCols + 4 * g) =
               make_float4(facc[mb][0 + hh], facc[mb][2 + hh], facc[mb][4 + hh], facc[mb][6 + hh]);
       }
-    // One acq_rel ticket per unit: the warp barrier orders every lane's stores before lane 0's
-    // release, and the acquire side of the same atomic covers the reads of the last arriver.
+    // One ticket per unit.  Owned tiles: shared-memory partials and counter, block-scope fences.
+    // K-split tiles: global scratch, one acq_rel atomic (the warp barrier orders every lane's stores
+    // before lane 0's release; the acquire side covers the reads of the last arriver).
     __syncwarp();
     int last = 0;
     if (lane == 0) {
       int old;
-      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile) : "memory");
+      if (owned) {
+        __threadfence_block();
+        old = atomicAdd(own_count + tile_local, 1);
+      } else {
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile) : "memory");
+      }
       last = old == p.chunks - 1;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
+      if (owned) __threadfence_block();
       // lane = 8*q + v: quarter q adds chunks q, q+4, ... for columns 4v..4v+3 (independent loads,
       // all in flight together), then the four quarters are added in a fixed order
-      const float* all = p.scratch + size_t(tile) * p.chunks * part;
+      const float* all = owned ? own_part + size_t(tile_local) * p.chunks * part
+                               : p.scratch + size_t(tile) * p.chunks * part;
       const int q = lane >> 3, v = lane & 7;
       for (int m = 0; m < p.M; ++m) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c = q; c < p.chunks; c += 4) {
-          const float4 a = __ldcg(reinterpret_cast<const float4*>(all + size_t(c) * part + m * kUnitCols + 4 * v));
+          const float4* src = reinterpret_cast<const float4*>(all + size_t(c) * part + m * kUnitCols + 4 * v);
+          const float4 a = owned ? *src : __ldcg(src);
           sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
         }
 #pragma unroll
@@ -316,13 +357,13 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           *reinterpret_cast<uint2*>(y + size_t(m) * p.N + n) = out;
         }
       }
-      if (lane == 0) p.counters[tile] = 0;  // ready for the next launch
+      if (lane == 0 && !owned) p.counters[tile] = 0;  // ready for the next launch
     }
   }
 }
 
 struct Plan {
-  int grid, slots, slot_bytes, warps, tiles, chunks, units;
+  int grid, slots, slot_bytes, warps, tiles, chunks, units, own_tiles;
   bool staged;
   size_t smem_bytes, counters_offset, scratch_offset, workspace_bytes;
 };
@@ -335,11 +376,16 @@ bool make_plan(int M, int K, int N, int mb, int sms, int warps_override, Plan* p
   q.units = q.tiles * q.chunks;
   q.grid = q.units < sms ? q.units : sms;
   q.warps = warps_override ? warps_override : (mb == 1 ? 32 : 16);
-  const int per_cta_max = (q.units + q.grid - 1) / q.grid;
+  // column tiles owned whole by every CTA (their partial sums live in shared memory)
+  q.own_tiles = q.tiles / q.grid;
+  if (q.own_tiles > 64 || size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4 > 32 * 1024) q.own_tiles = 0;
+  const int left_units = q.units - q.own_tiles * q.grid * q.chunks;
+  const int per_cta_max = q.own_tiles * q.chunks + (left_units + q.grid - 1) / q.grid;
   const size_t x_bytes = size_t(M) * q.chunks * kUnitRows * 16;  // staged rows are padded to whole chunks
   q.staged = x_bytes <= 32 * 1024;
   q.slot_bytes = ((kUnitActOffset + (q.staged ? 0 : M * 512) + 1023) / 1024) * 1024;
-  const size_t fixed = 1024 + 16 + size_t((K + 31) / 32) * 8 * mb * 4 + (q.staged ? x_bytes : 0);
+  const size_t fixed = 1024 + 16 + size_t((K + 31) / 32) * 8 * mb * 4 + (q.staged ? x_bytes : 0) + 256 + 16 +
+                       size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4;
   long long capacity = (long long)(size_t(kSmemLimit) - fixed) / (q.slot_bytes + 8);
   if (capacity >= per_cta_max) {
     q.slots = per_cta_max;
@@ -452,6 +498,7 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, void
   p.units = plan.units;
   p.slots = plan.slots;
   p.slot_bytes = plan.slot_bytes;
+  p.own_tiles = plan.own_tiles;
   p.twos_complement = zero_point == -1 ? 1 : 0;
   p.overlap = g_overlap;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
