@@ -48,7 +48,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # DRAM traffic per launch of the dominant kernel from an ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {"decode": 30314496, "prefill": 486003712, "w8a8": 149691136}
+NCU_TRAFFIC_BYTES = {"decode": 30314496, "prefill": 529902848, "w8a8": 149691136}
 
 
 def measured_peaks():
