@@ -181,6 +181,50 @@ INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_V
                                             INTENT_B200_VIEW2(a3), void* stream);
 
 /* ------------------------------------------------------------------------
+ * Ragged grouped contractions with dense 16-bit weights (tcgen05 kind::f16, f32 accumulation).
+ * Group offsets are read on the device (clamped to the row count); K and N multiples of 8,
+ * at most 1024 groups.  Rows of an empty group and rows outside every group are not written.
+ * ------------------------------------------------------------------------ */
+/* ragged_grouped_gemm / ragged_grouped_gemm_bf16 (examples/kernels/ragged/grouped_gemm.py:11-39, 42-70):
+ *   a0 x [R,K] T, a1 group_offsets [G+1] i32, a2 weight [G,K,N] T -> a3 y [R,N] T
+ *   y[r,:] = T(x[r,:] . weight[g]) for offsets[g] <= r < offsets[g+1] */
+INTENT_B200_API int intent_b200_ragged_grouped_gemm_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                        INTENT_B200_VIEW3(a2), INTENT_B200_VIEW2(a3), void* stream);
+INTENT_B200_API int intent_b200_ragged_grouped_gemm_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                         INTENT_B200_VIEW3(a2), INTENT_B200_VIEW2(a3), void* stream);
+/* routed_expert_projection_bf16 (grouped_gemm.py:101-138; the f16 entry is the same program on f16):
+ *   a0 x [T,K] T, a1 expert_offsets [E+1] i32, a2 member_routes [R] i32, a3 weight [E,N,K] T
+ *   -> a4 output [T,TOP_K,N] T;  for route = member_routes[i], offsets[e] <= i < offsets[e+1]:
+ *   output[route / TOP_K, route % TOP_K, :] = T(x[route / TOP_K, :] . weight[e]^T)
+ *   workspace: at least R*K*2 bytes rounded up to 256 (the gathered rows), 16-byte aligned, not cleared. */
+INTENT_B200_API int intent_b200_routed_expert_projection_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                              INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3),
+                                                              INTENT_B200_VIEW3(a4), int32_t top_k, void* workspace,
+                                                              int64_t workspace_bytes, void* stream);
+INTENT_B200_API int intent_b200_routed_expert_projection_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                             INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3),
+                                                             INTENT_B200_VIEW3(a4), int32_t top_k, void* workspace,
+                                                             int64_t workspace_bytes, void* stream);
+/* moe_expert_ffn (examples/kernels/ragged/moe.py:12-53; the bf16 entry is the same program on bf16):
+ *   a0 x [T,D] T, a1 route_offsets [E+1] i32, a2 member_routes [R] i32, a3 route_token [NR] i32,
+ *   a4 route_weights [NR] f32, a5 w1 [E,D,F] T, a6 w2 [E,F,D] T, a7 y [T,D] f32 (InOut)
+ *   for route = member_routes[i] of expert e, token = route_token[route]:
+ *   y[token,:] += route_weights[route] * (T(relu(x[token,:] . w1[e])) . w2[e])
+ *   The additions are relaxed float reductions in no fixed order, as in the reference's GPU lowering
+ *   (lib/Target/Triton/Transforms/Access/Scatter.cpp:43-60).
+ *   workspace: R*D*2 rounded up to 256, plus R*F*2 rounded up to 256 bytes; not cleared. */
+INTENT_B200_API int intent_b200_moe_expert_ffn_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                   INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW3(a5),
+                                                   INTENT_B200_VIEW3(a6), INTENT_B200_VIEW2(a7), void* workspace,
+                                                   int64_t workspace_bytes, void* stream);
+INTENT_B200_API int intent_b200_moe_expert_ffn_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                    INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW3(a5),
+                                                    INTENT_B200_VIEW3(a6), INTENT_B200_VIEW2(a7), void* workspace,
+                                                    int64_t workspace_bytes, void* stream);
+/* Status word of the dense grouped kernels (a bounded device wait that expired); synchronises the device. */
+INTENT_B200_API int intent_b200_grouped_gemm16_device_status(void);
+
+/* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.
  * This entry has no counterpart in the reference.  It exists for callers that
  * cannot allocate device memory on behalf of the library: a host that runs

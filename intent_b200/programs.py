@@ -324,3 +324,98 @@ moe_combine = KernelDefinition("moe_combine", {}, _lower_combine,
 ALL.update({d.name: d for d in (moe_count_routes, moe_prefix_routes, moe_scatter_routes, moe_mark_expert_blocks,
                                 moe_route_positions, moe_route_top2, moe_gather_rows, moe_grouped_upgate_silu,
                                 moe_grouped_down, moe_combine)})
+
+
+# ---------------------------------------------------------------------------------
+# Ragged grouped contractions with dense 16-bit weights
+# ---------------------------------------------------------------------------------
+def _align256(count):
+    return (int(count) + 255) & ~255
+
+
+_DENSE_RULES = (
+    _rule(lambda d: d["K"] % 8 == 0 and d["N"] % 8 == 0,
+          "this backend requires K and N to be multiples of 8 for 16-bit operands"),
+)
+
+
+def _lower_ragged(c, device, element):
+    interface = PublicInterface((
+        ViewParameter(0, "x", element, ("R", "K"), IN),
+        ViewParameter(1, "group_offsets", dtypes.i32, ("G_PLUS_1",), IN, alignment=4),
+        ViewParameter(2, "weight", element, ("G", "K", "N"), IN),
+        ViewParameter(3, "y", element, ("R", "N"), OUT),
+    ), dimension_rules=_DENSE_RULES + (
+        _rule(lambda d: d["G_PLUS_1"] == d["G"] + 1, "group_offsets must have G + 1 entries"),
+        _rule(lambda d: d["G"] <= 1024, "at most 1024 groups"),
+    ))
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_ragged_grouped_gemm_{element.name}",
+                         device=device, empty=lambda d: d["R"] == 0 or d["N"] == 0 or d["G"] == 0)
+
+
+ragged_grouped_gemm = KernelDefinition(
+    "ragged_grouped_gemm", {}, lambda c, d: _lower_ragged(c, d, dtypes.f16),
+    "examples/kernels/ragged/grouped_gemm.py:11-39",
+    "rows offsets[g]:offsets[g+1] of X times W[g], f16, f32 accumulation")
+ragged_grouped_gemm_bf16 = KernelDefinition(
+    "ragged_grouped_gemm_bf16", {}, lambda c, d: _lower_ragged(c, d, dtypes.bf16),
+    "examples/kernels/ragged/grouped_gemm.py:42-70",
+    "rows offsets[g]:offsets[g+1] of X times W[g], bf16, f32 accumulation")
+
+
+def _lower_routed(c, device):
+    element = _act_dtype(c, "DTYPE")
+    top_k = int(c["TOP_K"])
+    if top_k <= 0:
+        raise CompilationStageError("frontend_kir", "TOP_K must be positive")
+    interface = PublicInterface((
+        ViewParameter(0, "x", element, ("T", "K"), IN),
+        ViewParameter(1, "expert_offsets", dtypes.i32, ("E_PLUS_1",), IN, alignment=4),
+        ViewParameter(2, "member_routes", dtypes.i32, ("R",), IN, alignment=4),
+        ViewParameter(3, "weight", element, ("E", "N", "K"), IN),
+        ViewParameter(4, "output", element, ("T", top_k, "N"), OUT),
+    ), dimension_rules=_DENSE_RULES + (
+        _rule(lambda d: d["E_PLUS_1"] == d["E"] + 1, "expert_offsets must have E + 1 entries"),
+        _rule(lambda d: d["E"] <= 1024, "at most 1024 experts"),
+    ))
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_routed_expert_projection_{element.name}",
+                         constants=(top_k,), device=device,
+                         workspace=lambda d: _align256(d["R"] * d["K"] * 2),
+                         empty=lambda d: d["R"] == 0 or d["N"] == 0 or d["E"] == 0 or d["T"] == 0)
+
+
+routed_expert_projection_bf16 = KernelDefinition(
+    "routed_expert_projection_bf16", {"TOP_K": 2, "DTYPE": "bf16"}, _lower_routed,
+    "examples/kernels/ragged/grouped_gemm.py:101-138",
+    "out[token, slot] = x[token] @ W[e].T for the routes member_routes lists per expert")
+
+
+def _lower_expert_ffn(c, device):
+    element = _act_dtype(c, "DTYPE")
+    interface = PublicInterface((
+        ViewParameter(0, "x", element, ("T", "D"), IN),
+        ViewParameter(1, "route_offsets", dtypes.i32, ("E_PLUS_1",), IN, alignment=4),
+        ViewParameter(2, "member_routes", dtypes.i32, ("R",), IN, alignment=4),
+        ViewParameter(3, "route_token", dtypes.i32, ("NR",), IN, alignment=4),
+        ViewParameter(4, "route_weights", dtypes.f32, ("NR",), IN, alignment=4),
+        ViewParameter(5, "w1", element, ("E", "D", "F"), IN),
+        ViewParameter(6, "w2", element, ("E", "F", "D"), IN),
+        ViewParameter(7, "y", dtypes.f32, ("T", "D"), INOUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["D"] % 8 == 0 and d["F"] % 8 == 0,
+              "this backend requires D and F to be multiples of 8 for 16-bit operands"),
+        _rule(lambda d: d["E_PLUS_1"] == d["E"] + 1, "route_offsets must have E + 1 entries"),
+        _rule(lambda d: d["E"] <= 1024, "at most 1024 experts"),
+    ))
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_expert_ffn_{element.name}", device=device,
+                         workspace=lambda d: _align256(d["R"] * d["D"] * 2) + _align256(d["R"] * d["F"] * 2),
+                         empty=lambda d: d["R"] == 0 or d["D"] == 0 or d["E"] == 0 or d["T"] == 0 or d["F"] == 0)
+
+
+moe_expert_ffn = KernelDefinition(
+    "moe_expert_ffn", {"DTYPE": "f16"}, _lower_expert_ffn,
+    "examples/kernels/ragged/moe.py:12-53",
+    "y[token] += w[route] * (relu(x[token] @ W1[e]) @ W2[e]) over the routes of every expert")
+
+ALL.update({d.name: d for d in (ragged_grouped_gemm, ragged_grouped_gemm_bf16, routed_expert_projection_bf16,
+                                moe_expert_ffn)})

@@ -37,16 +37,19 @@ def routed_expert_projection(x, offsets, member_routes, weight):
     return output.reshape(x.shape[0], top_k, weight.shape[1])
 
 
-def moe_expert_ffn(x, route_offsets, member_routes, route_token, route_weights, w1, w2, y):
+def moe_expert_ffn(x, route_offsets, member_routes, route_token, route_weights, w1, w2, y, *, round_hidden=False):
     """The reference's dense-weight MoE FFN (cpu_runtime.py:1279-1286): ReLU
     between the two products, weighted add into the f32 InOut ``y``.  The kernel
     body rounds the hidden activation to the input dtype between the products
     (moe.py:42); the torch reference does not - both are inside the reference's
-    own tolerance and this function follows the torch reference."""
+    own tolerance.  The default follows the torch reference; ``round_hidden``
+    follows the kernel body."""
     for expert in range(w1.shape[0]):
         routes = member_routes[int(route_offsets[expert]):int(route_offsets[expert + 1])].long()
         tokens = route_token[routes].long()
         hidden = torch.relu(x[tokens].float() @ w1[expert].float())
+        if round_hidden:
+            hidden = hidden.to(x.dtype).float()
         values = hidden @ w2[expert].float()
         y.index_add_(0, tokens, route_weights[routes, None] * values)
     return y

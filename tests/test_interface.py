@@ -133,3 +133,30 @@ def test_artifact_rejects_wrong_device(artifact):
     x, p, s = _inputs()
     with pytest.raises(ValueError, match="bound to"):
         artifact.run(x, p, s)          # CPU tensors handed to a CUDA artifact
+
+
+# ---- dense ragged programs: declaration mirrors the reference's parameter order ------------------
+def test_dense_grouped_declarations():
+    ragged = ib.compile(ib.programs.ragged_grouped_gemm_bf16, resolve_target=False)
+    assert [p.name for p in ragged.interface.parameters] == ["x", "group_offsets", "weight", "y"]
+    routed = ib.compile(ib.programs.routed_expert_projection_bf16, constexprs={"TOP_K": 4}, resolve_target=False)
+    assert [p.name for p in routed.interface.parameters] == ["x", "expert_offsets", "member_routes", "weight", "output"]
+    ffn = ib.compile(ib.programs.moe_expert_ffn, resolve_target=False)
+    assert [p.name for p in ffn.interface.parameters] == ["x", "route_offsets", "member_routes", "route_token",
+                                                          "route_weights", "w1", "w2", "y"]
+    assert [p.name for p in ffn.interface.mutable_inputs] == ["y"] and ffn.interface.outputs == ()
+
+    x = torch.zeros((10, 64), dtype=torch.bfloat16)
+    w = torch.zeros((3, 32, 64), dtype=torch.bfloat16)                  # [E, N, K]
+    offsets = torch.zeros((4,), dtype=torch.int32)
+    members = torch.zeros((40,), dtype=torch.int32)
+    bound = routed.interface.bind((x, offsets, members, w), device=CPU)
+    assert bound.result().shape == (10, 4, 32)
+    with pytest.raises(ValueError):
+        routed.interface.bind((x, offsets[:3].contiguous(), members, w), device=CPU)     # E + 1 offsets
+    with pytest.raises(ValueError):
+        routed.interface.bind((x, offsets, members, torch.zeros((3, 32, 60), dtype=torch.bfloat16)), device=CPU)  # K
+    with pytest.raises(TypeError):
+        routed.interface.bind((x.half(), offsets, members, w), device=CPU)
+    with pytest.raises(TypeError):
+        ffn.interface.bind((x.half(),), device=CPU)
