@@ -435,6 +435,73 @@ def run_w8a8(args, rank: int, world: int, device):
     }
 
 
+GROUPED = dict(groups=8, rows_per_group=1024, K=4096, N=14336)
+GROUPED_PUBLISHED_MS = 4.393   # the reference's own number for this case on an RTX 5090D (other hardware)
+
+
+def run_grouped(args, rank: int, world: int, device):
+    """The reference's published dense grouped GEMM case (experiments/gpu/registry.py:7):
+    8 groups x 1024 rows, K=4096, N=14336, f16, through the ragged_grouped_gemm program."""
+    import torch
+
+    import intent_b200 as ib
+    from intent_b200.distributed import column_shard
+
+    G, rows_per_group, K, N = (GROUPED[k] for k in ("groups", "rows_per_group", "K", "N"))
+    R = G * rows_per_group
+    gen = torch.Generator().manual_seed(0)
+    x = (torch.randn((R, K), generator=gen) * 0.5).half()
+    cols = column_shard(N, world, rank)
+    n_local = cols.stop - cols.start
+    wd = torch.empty((G, K, n_local), dtype=torch.float16, device=device)
+    for g in range(G):      # weights are drawn group by group so the host never holds all 940 MB at once
+        wd[g] = (torch.randn((K, N), generator=gen) / K ** 0.5).half()[:, cols].to(device)
+    offsets = (torch.arange(G + 1, dtype=torch.int32) * rows_per_group).to(device)
+    artifact = ib.compile(ib.programs.ragged_grouped_gemm, target=ib.B200Target(device.index))
+    xd = x.to(device)
+    call = artifact.prepare(xd, offsets, wd)
+    elapsed_ms, clocks, launches = timed_steps(call.launch, args.steps, args.warmup, world, device, rank,
+                                               args.load_seconds)
+    pinned_x = x.pin_memory()
+    pinned_y = torch.empty((R, n_local), dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        y = artifact.run(pinned_x.to(device, non_blocking=True), offsets, wd)
+        pinned_y.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(1, min(args.steps, 20))
+    e2e_s = timed_e2e(e2e_step, e2e_steps, args.warmup, world, device)
+    flops = 2.0 * R * K * N
+    ms = elapsed_ms / args.steps
+    peaks = measured_peaks()
+    achieved = flops / world / (ms * 1e-3) / 1e12
+    published_tflops = flops / (GROUPED_PUBLISHED_MS * 1e-3) / 1e12
+    return {
+        "metric": "ragged_grouped_gemm_TFLOPs", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(flops / (ms * 1e-3) / 1e12 / published_tflops, 3) if world == 1 else None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD_META["grouped"][4],
+                   "parallelism": f"columns of W split over {world} gpu(s), no collective",
+                   "l2": "W (940 MB) + X + Y exceed the 126 MB L2 every step",
+                   "published": f"{GROUPED_PUBLISHED_MS} ms = {published_tflops:.0f} TFLOP/s on an RTX 5090D "
+                                "(the reference's generated Triton kernel; other hardware)"},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
+                     "traffic": NCU_TRAFFIC_BYTES.get("grouped"),
+                     "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4),
+                     "algorithmic_flops_per_launch": flops / world, "kernel": "grouped_gemm16_kernel",
+                     "ms_per_launch": round(ms, 5)},
+        "e2e": {"value": round(flops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": R * K * 2, "d2h_bytes_per_step": R * n_local * 2,
+                "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+
 def run_moe(args, rank: int, world: int, device):
     import torch
 
@@ -647,6 +714,34 @@ def cpu_moe(steps: int, warmup: int, budget_s: float):
     return flops / seconds / 1e12, cores, sample, seconds * 1e3, steps
 
 
+def cpu_grouped(steps: int, warmup: int, budget_s: float):
+    import torch
+
+    import oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    G, K, N = GROUPED["groups"], GROUPED["K"], GROUPED["N"]
+    rows, groups = 128, 2      # bounded sample: 2 of the 8 groups, 128 of the 1024 rows each
+    gen = torch.Generator().manual_seed(0)
+    x = (torch.randn((rows * groups, K), generator=gen) * 0.5).half()
+    w = (torch.randn((groups, K, N), generator=gen) / K ** 0.5).half()
+    offsets = torch.arange(groups + 1, dtype=torch.int32) * rows
+    t0 = time.perf_counter()
+    oracle.ragged_grouped_gemm(x, offsets, w)
+    one = time.perf_counter() - t0
+    steps = max(1, min(steps, int(budget_s / max(one, 1e-3)) - warmup))
+    for _ in range(warmup):
+        oracle.ragged_grouped_gemm(x, offsets, w)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.ragged_grouped_gemm(x, offsets, w)
+    seconds = (time.perf_counter() - t0) / steps
+    sample = (f"{steps} steps of {groups} of the {G} groups, {rows} of the 1024 rows each, full K and N, "
+              f"torch CPU f32 matmul per group, {cores} threads")
+    return 2.0 * rows * groups * K * N / seconds / 1e12, cores, sample, seconds * 1e3, steps
+
+
 WORKLOAD_META = {
     "prefill": ("w4a16_prefill_TFLOPs", "TFLOP/s", "strong", "bf16",
                 "w4a16_prefill_gemm M=8192 K=8192 N=8192 bf16 g128 zp8 (configs[2])"),
@@ -655,6 +750,8 @@ WORKLOAD_META = {
     "moe": ("moe_w4a16_ffn_TFLOPs", "TFLOP/s", "strong", "bf16",
             "moe_w4a16_swiglu_ffn 16384 tokens H=4096 E=64 top-2 I=1408 g128 (configs[4])"),
     "decode": ("w4a16_decode_weight_GBps", "GB/s", "weak", "f16", None),
+    "grouped": ("ragged_grouped_gemm_TFLOPs", "TFLOP/s", "strong", "f16",
+                "ragged_grouped_gemm 8 groups x 1024 rows K=4096 N=14336 f16 (the reference's grouped_gemm case)"),
 }
 
 
@@ -663,7 +760,7 @@ def cpu_workload(args, steps: int, warmup: int, budget_s: float):
     if args.workload == "decode":
         value, cores, sample, ms = cpu_decode(args.batch, steps, warmup, budget_s)
         return value, "GB/s", cores, sample, ms, steps
-    fn = {"prefill": cpu_prefill, "w8a8": cpu_w8a8, "moe": cpu_moe}[args.workload]
+    fn = {"prefill": cpu_prefill, "w8a8": cpu_w8a8, "moe": cpu_moe, "grouped": cpu_grouped}[args.workload]
     value, cores, sample, ms, done = fn(steps, warmup, budget_s)
     return value, WORKLOAD_META[args.workload][1], cores, sample, ms, done
 
@@ -713,7 +810,7 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--workload", default="prefill", choices=["prefill", "decode", "w8a8", "moe"])
+    parser.add_argument("--workload", default="prefill", choices=["prefill", "decode", "w8a8", "moe", "grouped"])
     parser.add_argument("--batch", type=int, default=1, help="decode batch M (1, 4, 8)")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--load-seconds", type=float, default=1.5)
@@ -721,7 +818,7 @@ def main() -> int:
     parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()
     if args.steps is None:
-        args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20}[args.workload]
+        args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20, "grouped": 50}[args.workload]
         if args.impl == "reference":
             args.steps = 5
 
@@ -748,7 +845,8 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
-    runner = {"prefill": run_prefill, "decode": run_decode, "w8a8": run_w8a8, "moe": run_moe}[args.workload]
+    runner = {"prefill": run_prefill, "decode": run_decode, "w8a8": run_w8a8, "moe": run_moe,
+              "grouped": run_grouped}[args.workload]
     line = runner(args, rank, world, device)
     if args.workload == "prefill" and not args.no_decode:
         # the headline metric has two halves: attach the decode GEMV (weight GB/s) measured in the same run
