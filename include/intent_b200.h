@@ -225,6 +225,31 @@ INTENT_B200_API int intent_b200_moe_expert_ffn_bf16(INTENT_B200_VIEW2(a0), INTEN
 INTENT_B200_API int intent_b200_grouped_gemm16_device_status(void);
 
 /* ------------------------------------------------------------------------
+ * Packed-weight contractions next to weight_only_int4_matmul
+ * (examples/kernels/contraction/weight_only_int4.py:54-175).  The packed operand is decoded once
+ * into the workspace (K contiguous) and contracted by the dense tcgen05 kernels; the integer
+ * programs are exact with wrapping int32 arithmetic.  The workspace is not cleared.
+ * ------------------------------------------------------------------------ */
+/* w4a8_packed_matmul (weight_only_int4.py:54-91): a0 activation i8 [M,K], a1 packed_weight u8 [N,K/2]
+ * (low nibble = even k, two's-complement int4) -> a2 output i32 [N,M].  K % 32 == 0, M % 16 == 0.
+ * workspace >= N*K bytes rounded up to 256. */
+INTENT_B200_API int intent_b200_w4a8_packed_matmul(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                   INTENT_B200_VIEW2(a2), void* workspace, int64_t workspace_bytes,
+                                                   void* stream);
+/* bitnet_int2_matmul (weight_only_int4.py:94-123): a0 activation i8 [M,K], a1 packed_weight u8 [N,K/4]
+ * (value k of a 16-value word: byte k % 4, bit 2 * (k / 4), values 0..3) -> a2 output i32 [M,N].
+ * K % 16 == 0, N % 16 == 0.  workspace >= N*K bytes rounded up to 256. */
+INTENT_B200_API int intent_b200_bitnet_int2_matmul(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                   INTENT_B200_VIEW2(a2), void* workspace, int64_t workspace_bytes,
+                                                   void* stream);
+/* dequant_bf16_fp4_matmul (weight_only_int4.py:126-175): a0 activation bf16 [M,K], a1 packed_weight u8 [N,K/2]
+ * (four e2m1 codes per big-endian 16-bit word) -> a2 output bf16 [M,N], f32 accumulation.
+ * K % 8 == 0, N % 8 == 0.  workspace >= N*K*2 rounded up to 256, plus 256 bytes. */
+INTENT_B200_API int intent_b200_dequant_bf16_fp4_matmul(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                        INTENT_B200_VIEW2(a2), void* workspace,
+                                                        int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.
  * This entry has no counterpart in the reference.  It exists for callers that
  * cannot allocate device memory on behalf of the library: a host that runs

@@ -21,6 +21,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "dense.cuh"
 #include "tma.cuh"
 #include "umma.cuh"
 
@@ -455,6 +456,13 @@ int moe_expert_ffn(View2 x, View1 offsets, View1 members, View1 route_token, Vie
 }
 
 }  // namespace
+
+int bf16_gemm_nt(const void* a, int64_t M, int64_t K, const void* b, int64_t N, void* out, const int32_t* row_span,
+                 cudaStream_t stream) {
+  Problem q{a, M, K, N, 1, b, row_span, out, M, nullptr, nullptr, nullptr, 0};
+  return launch<__nv_bfloat16, true, kCast>(q, stream);
+}
+
 }  // namespace ib200
 
 #define IB200_RAGGED_ENTRY(name, T)                                                                            \

@@ -12,8 +12,11 @@
 // as MN-major, so no transposition pass exists anywhere.  One persistent CTA per SM walks
 // 128 x 256 tiles: warp 0 issues TMA (4 stages of 48 KiB), one thread of warp 1 issues four
 // M128 N256 K32 MMAs per stage, warps 2..5 drain the two TMEM accumulators.
+// With B_K_MAJOR the second operand is given as [N,K] (K contiguous, e.g. decoded packed weights)
+// and is loaded as one 256-row K-major box.
 // Every wait is bounded (see tma.cuh); a wait that gives up records a timeout status.
 #include "common.cuh"
+#include "dense.cuh"
 #include "tma.cuh"
 #include "umma.cuh"
 
@@ -41,7 +44,7 @@ struct I8Params {
 };
 
 // EPILOGUE 0: bf16(acc * sa[m] * sb[n]);  1: int32 acc + bias[n]
-template <int EPILOGUE>
+template <int EPILOGUE, bool B_K_MAJOR>
 __global__ void __launch_bounds__(THREADS, 1)
 i8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const I8Params p) {
@@ -92,8 +95,12 @@ i8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t bar = full + 8 * s;
           mbar_expect_tx(bar, A_BYTES + B_BYTES);
           tma_load_2d(smem_a + s * A_BYTES, &map_a, kb * BK, m_tile * BM, bar);
-          tma_load_2d(smem_b + s * B_BYTES, &map_b, n_tile * BN, kb * BK, bar);
-          tma_load_2d(smem_b + s * B_BYTES + B_BOX_BYTES, &map_b, n_tile * BN + 128, kb * BK, bar);
+          if (B_K_MAJOR) {
+            tma_load_2d(smem_b + s * B_BYTES, &map_b, kb * BK, n_tile * BN, bar);
+          } else {
+            tma_load_2d(smem_b + s * B_BYTES, &map_b, n_tile * BN, kb * BK, bar);
+            tma_load_2d(smem_b + s * B_BYTES + B_BOX_BYTES, &map_b, n_tile * BN + 128, kb * BK, bar);
+          }
         }
       }
       if (!ok) atomicExch(&g_w8a8_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -101,7 +108,7 @@ i8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // s32 accumulator, signed 8-bit operands, A K-major, B MN-major (N contiguous)
-      constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, 1, BM, BN);
+      constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, B_K_MAJOR ? 0 : 1, BM, BN);
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
@@ -115,11 +122,13 @@ i8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tcgen05_fence_after();
           const uint64_t desc_a = umma_desc_k_major_sw128(smem_a + s * A_BYTES);
           // 128-column spans are one box (16 KiB) apart, 8-row k groups 1 KiB apart
-          const uint64_t desc_b = umma_desc_mn_major_sw128(smem_b + s * B_BYTES, B_BOX_BYTES);
+          const uint64_t desc_b = B_K_MAJOR ? umma_desc_k_major_sw128(smem_b + s * B_BYTES)
+                                            : umma_desc_mn_major_sw128(smem_b + s * B_BYTES, B_BOX_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / 32; ++kk)
             // A: 32 k = 32 bytes along its 128-byte row (2 units); B: 32 k rows of 128 bytes (256 units)
-            umma_i8(tmem_d, desc_a + uint64_t(2 * kk), desc_b + uint64_t(256 * kk), idesc, (kb | kk) != 0);
+            umma_i8(tmem_d, desc_a + uint64_t(2 * kk), desc_b + uint64_t((B_K_MAJOR ? 2 : 256) * kk), idesc,
+                    (kb | kk) != 0);
           umma_commit(empty + 8 * s);
         }
         if (ok) umma_commit(tmem_full + 8 * acc);
@@ -209,10 +218,11 @@ int device_sms() {
   return sms;
 }
 
-template <int EPILOGUE>
+// b is [K,N] (N contiguous), or [N,K] (K contiguous) with B_K_MAJOR
+template <int EPILOGUE, bool B_K_MAJOR = false>
 int run(View2 a, View2 b, void* out, const int32_t* bias, const float* sa, const float* sb, cudaStream_t stream) {
-  const int64_t M = a.d0, K = a.d1, N = b.d1;
-  if (b.d0 != K) return INTENT_B200_ERR_SHAPE;
+  const int64_t M = a.d0, K = a.d1, N = B_K_MAJOR ? b.d0 : b.d1;
+  if ((B_K_MAJOR ? b.d1 : b.d0) != K) return INTENT_B200_ERR_SHAPE;
   if (M == 0 || N == 0) return INTENT_B200_OK;
   if (!a.p || !b.p || !out) return INTENT_B200_ERR_NULL;
   if (!contiguous(a) || !contiguous(b)) return INTENT_B200_ERR_LAYOUT;
@@ -235,10 +245,12 @@ int run(View2 a, View2 b, void* out, const int32_t* bias, const float* sa, const
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.p, uint64_t(M), uint64_t(K), uint64_t(K), BM, BK,
                           CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b.p, uint64_t(K), uint64_t(N), uint64_t(N), BK, 128,
-                          CU_TENSOR_MAP_SWIZZLE_128B))
+      !(B_K_MAJOR ? make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b.p, uint64_t(N), uint64_t(K), uint64_t(K),
+                                       BN, BK, CU_TENSOR_MAP_SWIZZLE_128B)
+                  : make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b.p, uint64_t(K), uint64_t(N), uint64_t(N),
+                                       BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)))
     return INTENT_B200_ERR_UNSUPPORTED;
-  auto kernel = i8_gemm_kernel<EPILOGUE>;
+  auto kernel = i8_gemm_kernel<EPILOGUE, B_K_MAJOR>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
@@ -248,6 +260,12 @@ int run(View2 a, View2 b, void* out, const int32_t* bias, const float* sa, const
 }
 
 }  // namespace
+
+int i8_gemm_nt(const void* a, int64_t M, int64_t K, const void* b, int64_t N, int32_t* out, cudaStream_t stream) {
+  View2 va{const_cast<void*>(a), M, K, K, 1}, vb{const_cast<void*>(b), N, K, K, 1};
+  return run<1, true>(va, vb, out, nullptr, nullptr, nullptr, stream);
+}
+
 }  // namespace ib200
 
 extern "C" int intent_b200_gemm_i8(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW1(a2),

@@ -419,3 +419,68 @@ moe_expert_ffn = KernelDefinition(
 
 ALL.update({d.name: d for d in (ragged_grouped_gemm, ragged_grouped_gemm_bf16, routed_expert_projection_bf16,
                                 moe_expert_ffn)})
+
+
+# ---------------------------------------------------------------------------------
+# Packed-weight contractions next to weight_only_int4_matmul: decode once into a workspace,
+# then the dense tensor-core kernels
+# ---------------------------------------------------------------------------------
+def _lower_w4a8(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "activation", dtypes.i8, ("M", "K"), IN),
+        ViewParameter(1, "packed_weight", dtypes.u8, ("N", "P"), IN),
+        ViewParameter(2, "output", dtypes.i32, ("N", "M"), OUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["P"] * 2 == d["K"], lambda d: f"packed_weight.shape[1] must be K/2 = {d['K'] // 2}"),
+        _rule(lambda d: d["K"] % 32 == 0 and d["M"] % 16 == 0,
+              "this backend requires K to be a multiple of 32 and M a multiple of 16"),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_w4a8_packed_matmul", device=device,
+                         workspace=lambda d: _align256(d["N"] * d["K"]),
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+w4a8_packed_matmul = KernelDefinition(
+    "w4a8_packed_matmul", {}, _lower_w4a8, "examples/kernels/contraction/weight_only_int4.py:54-91",
+    "out[N,M] = i32(int4(W)[N,K] @ A[M,K].T), two nibbles per byte, exact")
+
+
+def _lower_bitnet(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "activation", dtypes.i8, ("M", "K"), IN),
+        ViewParameter(1, "packed_weight", dtypes.u8, ("N", "P"), IN),
+        ViewParameter(2, "output", dtypes.i32, ("M", "N"), OUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["P"] * 4 == d["K"], lambda d: f"packed_weight.shape[1] must be K/4 = {d['K'] // 4}"),
+        _rule(lambda d: d["K"] % 16 == 0 and d["N"] % 16 == 0,
+              "this backend requires K and N to be multiples of 16"),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_bitnet_int2_matmul", device=device,
+                         workspace=lambda d: _align256(d["N"] * d["K"]),
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+bitnet_int2_matmul = KernelDefinition(
+    "bitnet_int2_matmul", {}, _lower_bitnet, "examples/kernels/contraction/weight_only_int4.py:94-123",
+    "out[M,N] = i32(A[M,K] @ int2(W)[N,K].T), interleaved 16-value words, exact")
+
+
+def _lower_fp4(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "activation", dtypes.bf16, ("M", "K"), IN),
+        ViewParameter(1, "packed_weight", dtypes.u8, ("N", "P"), IN),
+        ViewParameter(2, "output", dtypes.bf16, ("M", "N"), OUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["P"] * 2 == d["K"], lambda d: f"packed_weight.shape[1] must be K/2 = {d['K'] // 2}"),
+        _rule(lambda d: d["K"] % 8 == 0 and d["N"] % 8 == 0, "this backend requires K and N to be multiples of 8"),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_dequant_bf16_fp4_matmul", device=device,
+                         workspace=lambda d: _align256(d["N"] * d["K"] * 2) + 256,
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+dequant_bf16_fp4_matmul = KernelDefinition(
+    "dequant_bf16_fp4_matmul", {}, _lower_fp4, "examples/kernels/contraction/weight_only_int4.py:126-175",
+    "out[M,N] = bf16(A[M,K] @ e2m1(W)[N,K].T), four fp4 codes per 16-bit word")
+
+ALL.update({d.name: d for d in (w4a8_packed_matmul, bitnet_int2_matmul, dequant_bf16_fp4_matmul)})

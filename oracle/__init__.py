@@ -41,3 +41,11 @@ from .moe import (  # noqa: F401
     moe_w4a16_swiglu_ffn,
     grouped_w4a16_gemm,
 )
+from .packed import (  # noqa: F401
+    bitnet_int2_matmul,
+    decode_fp4_bf16,
+    dequant_bf16_fp4_matmul,
+    unpack_bitnet_int2,
+    unpack_w4a8,
+    w4a8_packed_matmul,
+)

@@ -141,6 +141,27 @@ def main(root: Path) -> None:
     save("moe_expert_ffn", x=xf, route_offsets=expert_offsets, member_routes=member_routes,
          route_token=route_token, route_weights=route_weights, w1=w1, w2=w2, y=y)
 
+    # --- interleaved int2 ("bitnet") and fp4 -> bf16 packed weights; recipes of
+    # experiments/cpu/providers/mojo/contraction.py:209-224 at small sizes.  Appended last so the
+    # random stream of the fixtures above is unchanged.
+    generator = torch.Generator().manual_seed(7)
+    for tag, (M, N, K, high) in {"small": (3, 40, 128, 2), "full_range": (24, 72, 192, 4)}.items():
+        activation = torch.randint(-8, 8, (M, K), dtype=torch.int8, generator=generator)
+        logical = torch.randint(0, high, (N, K), dtype=torch.int8, generator=generator).reshape(N, K // 16, 4, 4)
+        packed = torch.zeros((N, K // 16, 4), dtype=torch.uint8)
+        for lane in range(4):
+            packed |= logical[:, :, lane, :].to(torch.uint8) << (lane * 2)
+        packed = packed.flatten(1)
+        save(f"bitnet_int2_{tag}", activation=activation, packed=packed,
+             output=ref.bitnet_int2_matmul(activation, packed))
+    for tag, (M, N, K) in {"small": (8, 40, 128), "all_codes": (16, 128, 256)}.items():
+        activation = (torch.randn((M, K), generator=generator) * 0.125).bfloat16()
+        packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=generator)
+        if tag == "all_codes":      # every 16-bit word value's high and low byte patterns appear
+            packed[:, 0::2] = torch.arange(N * K // 4, dtype=torch.int32).reshape(N, K // 4).remainder(256).to(torch.uint8)
+        save(f"dequant_bf16_fp4_{tag}", activation=activation, packed=packed,
+             output=ref.dequant_bf16_fp4_matmul(activation, packed))
+
 
 if __name__ == "__main__":
     main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))

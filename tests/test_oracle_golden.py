@@ -147,3 +147,26 @@ def test_moe_w4a16_swiglu_ffn_consistent_with_dense_form():
             h = torch.nn.functional.silu(gu[:128]) * gu[128:]
             expected[t] += weights[t, c] * (h @ wd)
     assert torch.allclose(y, expected, rtol=1e-4, atol=1e-6)
+
+
+# ---- packed-weight contractions next to the W4A16 path ---------------------------------------
+def test_w4a8_packed_matmul_matches_reference():
+    g = load_golden("w4a8_small")
+    out = oracle.w4a8_packed_matmul(g["activation"], g["packed"])
+    assert out.dtype == torch.int32 and torch.equal(out, g["output"])
+
+
+@pytest.mark.parametrize("tag", ["small", "full_range"])
+def test_bitnet_int2_matmul_matches_reference(tag):
+    g = load_golden(f"bitnet_int2_{tag}")
+    out = oracle.bitnet_int2_matmul(g["activation"], g["packed"])
+    assert out.dtype == torch.int32 and torch.equal(out, g["output"])
+
+
+@pytest.mark.parametrize("tag", ["small", "all_codes"])
+def test_dequant_bf16_fp4_matmul_matches_reference(tag):
+    g = load_golden(f"dequant_bf16_fp4_{tag}")
+    out = oracle.dequant_bf16_fp4_matmul(g["activation"], g["packed"])
+    assert torch.equal(out.view(torch.int16), g["output"].view(torch.int16))
+    decoded = oracle.decode_fp4_bf16(g["packed"]).float().abs().unique().tolist()
+    assert set(decoded) <= {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
