@@ -221,6 +221,18 @@ INTENT_B200_API int intent_b200_moe_expert_ffn_bf16(INTENT_B200_VIEW2(a0), INTEN
                                                     INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW3(a5),
                                                     INTENT_B200_VIEW3(a6), INTENT_B200_VIEW2(a7), void* workspace,
                                                     int64_t workspace_bytes, void* stream);
+/* Dense forms on the same kernel (examples/kernels/contraction/gemm.py:40-106); K and N multiples of 8.
+ * gemm: a0 a [M,K] f16, a1 b [K,N] f16 -> a2 c [M,N] f16; activation 0 = none, 1 = ReLU (the ACTIVATION constexpr).
+ * bf16_gemm: the same on bf16 without activation.
+ * quantized_gemm: a0 a [M,K] f16, a1 b [K,N] f16, a2 bias [N] f32, a3 residual [M,N] f16, a4 output_scale [N] f32
+ *   -> a5 output [M,N] i8 = i8(trunc(clamp((relu(acc + bias[n]) + f32(residual[m,n])) / scale[n], -128, 127))). */
+INTENT_B200_API int intent_b200_gemm_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                         int32_t activation, void* stream);
+INTENT_B200_API int intent_b200_bf16_gemm(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                          void* stream);
+INTENT_B200_API int intent_b200_quantized_gemm_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW1(a2),
+                                                   INTENT_B200_VIEW2(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW2(a5),
+                                                   void* stream);
 /* Status word of the dense grouped kernels (a bounded device wait that expired); synchronises the device. */
 INTENT_B200_API int intent_b200_grouped_gemm16_device_status(void);
 

@@ -7,6 +7,9 @@
 //                                   expert listed by member_routes (grouped_gemm.py:101-138)
 //   moe_expert_ffn                  y[token] += w[route] * (f16(relu(x[token] W1[e])) W2[e])
 //                                   (examples/kernels/ragged/moe.py:12-53)
+//   gemm / bf16_gemm / quantized_gemm  the dense forms (examples/kernels/contraction/gemm.py:40-106): a single
+//                                   group covering every row, optional ReLU, or the int8 epilogue
+//                                   i8(clamp((relu(acc + bias[n]) + residual[m,n]) / scale[n]))
 //
 // One persistent CTA per SM walks 128 x 256 output tiles.  The tile list is ragged: every CTA
 // reads the group offsets once, clamps them to the row count and builds the per-group tile
@@ -41,10 +44,10 @@ constexpr int MAX_GROUPS = 1024;
 constexpr int TABLE_BYTES = 3 * (MAX_GROUPS + 1) * 4;
 constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256 + TABLE_BYTES;
 
-enum Epilogue { kCast = 0, kReluCast = 1, kWeightedAdd = 2 };
+enum Epilogue { kCast = 0, kReluCast = 1, kWeightedAdd = 2, kQuantize = 3 };
 
 struct Params {
-  const int32_t* offsets;      // [groups + 1]
+  const int32_t* offsets;      // [groups + 1]; null = one group covering every row
   int groups, rows, N, K;
   int k_blocks, n_tiles;
   void* out;
@@ -53,6 +56,9 @@ struct Params {
   const int32_t* route_token;  // kWeightedAdd: token of a route
   const float* route_weights;  // kWeightedAdd: weight of a route
   int64_t routes;              // extent of route_token / route_weights
+  const float* bias;           // kQuantize: [N]
+  const void* residual;        // kQuantize: [rows, N], element type T
+  const float* out_scale;      // kQuantize: [N]
 };
 
 __device__ __forceinline__ void red_add_v4(float* address, float a, float b, float c, float d) {
@@ -102,8 +108,8 @@ grouped_gemm16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int lane = tid & 31;
 
   for (int g = tid; g < p.groups; g += THREADS) {
-    const int b = min(max(p.offsets[g], 0), p.rows);
-    const int e = min(max(p.offsets[g + 1], 0), p.rows);
+    const int b = p.offsets ? min(max(p.offsets[g], 0), p.rows) : 0;
+    const int e = p.offsets ? min(max(p.offsets[g + 1], 0), p.rows) : p.rows;
     s_begin[g] = b;
     s_count[g] = max(e - b, 0);
   }
@@ -237,7 +243,29 @@ grouped_gemm16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           for (int q = 0; q < 4; ++q) {
             const int n0 = col + q * 8;
             if (n0 < p.N) {  // N is a multiple of 8
-              if (EPILOGUE == kWeightedAdd) {
+              if (EPILOGUE == kQuantize) {
+                // i8(trunc(clamp((relu(acc + bias) + residual) / scale, -128, 127))), all in f32
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + n0));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + n0 + 4));
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.out_scale + n0));
+                const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.out_scale + n0 + 4));
+                const uint4 r = __ldg(reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const uint16_t*>(p.residual) + size_t(out_row) * p.N + n0));
+                const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const float scale[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                const uint32_t res[4] = {r.x, r.y, r.z, r.w};
+                uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float residual = Elem<T>::to_float(uint16_t(res[j >> 1] >> (16 * (j & 1))));
+                  float value = fmaxf(__uint_as_float(v[8 * q + j]) + bias[j], 0.f) + residual;
+                  value = __fdiv_rn(value, scale[j]);
+                  value = fminf(fmaxf(value, -128.f), 127.f);
+                  packed[j >> 2] |= (uint32_t(__float2int_rz(value)) & 0xFFu) << (8 * (j & 3));
+                }
+                *reinterpret_cast<uint2*>(reinterpret_cast<int8_t*>(p.out) + size_t(out_row) * p.N + n0) =
+                    make_uint2(packed[0], packed[1]);
+              } else if (EPILOGUE == kWeightedAdd) {
                 float* dst = reinterpret_cast<float*>(p.out) + size_t(out_row) * p.N + n0;
                 red_add_v4(dst, weight * __uint_as_float(v[8 * q + 0]), weight * __uint_as_float(v[8 * q + 1]),
                            weight * __uint_as_float(v[8 * q + 2]), weight * __uint_as_float(v[8 * q + 3]));
@@ -323,6 +351,9 @@ struct Problem {
   const int32_t* route_token;
   const float* route_weights;
   int64_t routes;
+  const float* bias = nullptr;
+  const void* residual = nullptr;
+  const float* out_scale = nullptr;
 };
 
 template <typename T, bool B_K_MAJOR, int EPILOGUE>
@@ -347,6 +378,9 @@ int launch(const Problem& q, cudaStream_t stream) {
   p.route_token = q.route_token;
   p.route_weights = q.route_weights;
   p.routes = q.routes;
+  p.bias = q.bias;
+  p.residual = q.residual;
+  p.out_scale = q.out_scale;
   // groups may overlap, so the tile count is bounded per group, not by the row count
   if (q.groups * (q.rows / BM + 1) * int64_t(p.n_tiles) >= (int64_t(1) << 31)) return INTENT_B200_ERR_UNSUPPORTED;
   const int64_t tile_bound = (q.rows / BM + q.groups) * int64_t(p.n_tiles);
@@ -457,6 +491,23 @@ int moe_expert_ffn(View2 x, View1 offsets, View1 members, View1 route_token, Vie
 
 }  // namespace
 
+// a [M,K], b [K,N] -> c [M,N]; one row group, no offsets array
+template <typename T, int EPILOGUE>
+int dense_gemm(View2 a, View2 b, View2 c, const float* bias, const void* residual, const float* out_scale,
+               cudaStream_t stream) {
+  const int64_t M = a.d0, K = a.d1, N = b.d1;
+  if (b.d0 != K || c.d0 != M || c.d1 != N) return INTENT_B200_ERR_SHAPE;
+  if (M == 0 || N == 0) return INTENT_B200_OK;
+  if (!a.p || !b.p || !c.p) return INTENT_B200_ERR_NULL;
+  if (!contiguous(a) || !contiguous(b) || !contiguous(c) || !aligned16(a.p) || !aligned16(b.p) || !aligned16(c.p))
+    return INTENT_B200_ERR_LAYOUT;
+  Problem q{a.p, M, K, N, 1, b.p, nullptr, c.p, M, nullptr, nullptr, nullptr, 0};
+  q.bias = bias;
+  q.residual = residual;
+  q.out_scale = out_scale;
+  return launch<T, false, EPILOGUE>(q, stream);
+}
+
 int bf16_gemm_nt(const void* a, int64_t M, int64_t K, const void* b, int64_t N, void* out, const int32_t* row_span,
                  cudaStream_t stream) {
   Problem q{a, M, K, N, 1, b, row_span, out, M, nullptr, nullptr, nullptr, 0};
@@ -505,4 +556,39 @@ extern "C" int intent_b200_grouped_gemm16_device_status(void) {
   if (e != cudaSuccess) return ib200::cuda_status(e);
   if (value != 0) cudaMemcpyToSymbol(ib200::g_grouped16_status, &zero, sizeof(int));
   return value;
+}
+
+// gemm (examples/kernels/contraction/gemm.py:40-61): f16, activation 0 = none, 1 = ReLU
+extern "C" int intent_b200_gemm_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                    int32_t activation, void* stream) {
+  using namespace ib200;
+  if (activation != 0 && activation != 1) return INTENT_B200_ERR_UNSUPPORTED;
+  return activation ? dense_gemm<__half, kReluCast>(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2),
+                                                    nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream))
+                    : dense_gemm<__half, kCast>(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2),
+                                                nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+// bf16_gemm (gemm.py:64-80)
+extern "C" int intent_b200_bf16_gemm(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                     void* stream) {
+  using namespace ib200;
+  return dense_gemm<__nv_bfloat16, kCast>(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2), nullptr,
+                                          nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+// quantized_gemm (gemm.py:83-106): a0 a [M,K] f16, a1 b [K,N] f16, a2 bias [N] f32, a3 residual [M,N] f16,
+// a4 output_scale [N] f32 -> a5 output [M,N] i8
+extern "C" int intent_b200_quantized_gemm_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW1(a2),
+                                              INTENT_B200_VIEW2(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW2(a5),
+                                              void* stream) {
+  using namespace ib200;
+  if (a2_d0 != a1_d1 || a4_d0 != a1_d1 || a3_d0 != a0_d0 || a3_d1 != a1_d1) return INTENT_B200_ERR_SHAPE;
+  if (a0_d0 > 0 && a1_d1 > 0 && (!a2 || !a3 || !a4)) return INTENT_B200_ERR_NULL;
+  if (!contiguous(IB200_VIEW1_ARG(a2)) || !contiguous(IB200_VIEW2_ARG(a3)) || !contiguous(IB200_VIEW1_ARG(a4)) ||
+      !aligned16(a2) || !aligned16(a3) || !aligned16(a4))
+    return INTENT_B200_ERR_LAYOUT;
+  return dense_gemm<__half, kQuantize>(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a5),
+                                       static_cast<const float*>(a2), a3, static_cast<const float*>(a4),
+                                       static_cast<cudaStream_t>(stream));
 }

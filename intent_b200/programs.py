@@ -484,3 +484,53 @@ dequant_bf16_fp4_matmul = KernelDefinition(
     "out[M,N] = bf16(A[M,K] @ e2m1(W)[N,K].T), four fp4 codes per 16-bit word")
 
 ALL.update({d.name: d for d in (w4a8_packed_matmul, bitnet_int2_matmul, dequant_bf16_fp4_matmul)})
+
+
+# ---------------------------------------------------------------------------------
+# Dense 16-bit GEMMs of the reference's gemm.py on the ragged kernel (one row group)
+# ---------------------------------------------------------------------------------
+def _dense_interface(element, out):
+    return PublicInterface((
+        ViewParameter(0, "a", element, ("M", "K"), IN),
+        ViewParameter(1, "b", element, ("K", "N"), IN),
+        ViewParameter(2, "c", out, ("M", "N"), OUT),
+    ), dimension_rules=_DENSE_RULES)
+
+
+def _lower_gemm(c, device):
+    activation = c["ACTIVATION"]
+    code = {"none": 0, "NONE": 0, 0: 0, "relu": 1, "RELU": 1, 1: 1}.get(getattr(activation, "name", activation))
+    if code is None:
+        raise CompilationStageError("frontend_kir", "ACTIVATION must be 'none' (0) or 'relu' (1)")
+    return NativeProgram(interface=_dense_interface(dtypes.f16, dtypes.f16), entry_name="intent_b200_gemm_f16",
+                         constants=(code,), device=device, empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+gemm = KernelDefinition("gemm", {"ACTIVATION": "none"}, _lower_gemm,
+                        "examples/kernels/contraction/gemm.py:40-61", "C = f16(act(A @ B)), f32 accumulation")
+bf16_gemm = KernelDefinition(
+    "bf16_gemm", {},
+    lambda c, device: NativeProgram(interface=_dense_interface(dtypes.bf16, dtypes.bf16),
+                                    entry_name="intent_b200_bf16_gemm", device=device,
+                                    empty=lambda d: d["M"] == 0 or d["N"] == 0),
+    "examples/kernels/contraction/gemm.py:64-80", "C = bf16(A @ B), f32 accumulation")
+
+
+def _lower_quantized_gemm(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "a", dtypes.f16, ("M", "K"), IN),
+        ViewParameter(1, "b", dtypes.f16, ("K", "N"), IN),
+        ViewParameter(2, "bias", dtypes.f32, ("N",), IN),
+        ViewParameter(3, "residual", dtypes.f16, ("M", "N"), IN),
+        ViewParameter(4, "output_scale", dtypes.f32, ("N",), IN),
+        ViewParameter(5, "output", dtypes.i8, ("M", "N"), OUT),
+    ), dimension_rules=_DENSE_RULES)
+    return NativeProgram(interface=interface, entry_name="intent_b200_quantized_gemm_f16", device=device,
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+
+
+quantized_gemm = KernelDefinition(
+    "quantized_gemm", {}, _lower_quantized_gemm, "examples/kernels/contraction/gemm.py:83-106",
+    "i8(clamp((relu(A @ B + bias) + residual) / scale)), truncating cast")
+
+ALL.update({d.name: d for d in (gemm, bf16_gemm, quantized_gemm)})

@@ -16,6 +16,8 @@ cpu_runtime.py``) imported unmodified; the vectors are committed under
 reference itself ships no golden vectors for this path.
 """
 from .contraction import (  # noqa: F401
+    gemm,
+    quantized_gemm,
     pack_int4,
     unpack_int4,
     dequantize_int4,

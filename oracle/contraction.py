@@ -122,3 +122,20 @@ def w8a8_scaled_gemm(a, b, a_scales, b_scales, *, out_dtype=torch.bfloat16):
     """
     acc = gemm_i8(a, b)
     return ((acc.float() * a_scales.float()[:, None]) * b_scales.float()[None, :]).to(out_dtype), acc
+
+
+def gemm(a, b, *, relu: bool = False):
+    """Dense 16-bit GEMM with f32 accumulation and one rounding to the input type
+    (examples/kernels/contraction/gemm.py:40-80)."""
+    accumulator = a.float() @ b.float()
+    if relu:
+        accumulator = torch.relu(accumulator)
+    return accumulator.to(a.dtype)
+
+
+def quantized_gemm(a, b, bias, residual, scale):
+    """GEMM + bias + ReLU + residual + per-channel scale + clamp + truncating int8 cast
+    (examples/kernels/contraction/gemm.py:83-106, cpu_runtime.py:91-94)."""
+    accumulator = a.float() @ b.float()
+    fused = torch.relu(accumulator + bias) + residual.float()
+    return (fused / scale).clamp(-128.0, 127.0).to(torch.int8)

@@ -162,6 +162,16 @@ def main(root: Path) -> None:
         save(f"dequant_bf16_fp4_{tag}", activation=activation, packed=packed,
              output=ref.dequant_bf16_fp4_matmul(activation, packed))
 
+    # quantized_gemm, recipe of experiments/cpu/providers/mojo/contraction.py:177-186 at a small size
+    M, K, N = 48, 256, 136
+    lhs = (torch.randn((M, K), generator=generator) / math.sqrt(K)).half()
+    rhs = torch.randn((K, N), generator=generator).half()
+    bias = torch.randn((N,), generator=generator) * 0.25
+    residual = (torch.randn((M, N), generator=generator) * 0.25).half()
+    scale = torch.linspace(1.0 / 48.0, 1.0 / 24.0, N, dtype=torch.float32)
+    save("quantized_gemm_small", a=lhs, b=rhs, bias=bias, residual=residual, scale=scale,
+         output=ref.quantized_gemm(lhs, rhs, bias, residual, scale))
+
 
 if __name__ == "__main__":
     main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))

@@ -170,3 +170,9 @@ def test_dequant_bf16_fp4_matmul_matches_reference(tag):
     assert torch.equal(out.view(torch.int16), g["output"].view(torch.int16))
     decoded = oracle.decode_fp4_bf16(g["packed"]).float().abs().unique().tolist()
     assert set(decoded) <= {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
+
+
+def test_quantized_gemm_matches_reference():
+    g = load_golden("quantized_gemm_small")
+    out = oracle.quantized_gemm(g["a"], g["b"], g["bias"], g["residual"], g["scale"])
+    assert out.dtype == torch.int8 and torch.equal(out, g["output"])
