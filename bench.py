@@ -520,7 +520,8 @@ def run_moe(args, rank: int, world: int, device):
     weights = [data[k][ex].contiguous().to(device) for k in ("up_gate_packed", "up_gate_scales", "down_packed",
                                                              "down_scales")]
     if world == 1:
-        ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts, target=ib.B200Target(device.index))
+        ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts,
+                          block_size=args.moe_block, target=ib.B200Target(device.index))
 
         def forward(lg, xx):
             ids, w = ffn.route(lg)
@@ -542,7 +543,7 @@ def run_moe(args, rank: int, world: int, device):
         # fixed-capacity exchange (1.5x the mean rows per destination): no device -> host read in the step;
         # an overflow would be recorded on the device and is checked after the timed region
         ep = ExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
-                               capacity_factor=1.5, target=ib.B200Target(device.index))
+                               capacity_factor=1.5, block_size=args.moe_block, target=ib.B200Target(device.index))
 
         def forward(lg, xx):
             return ep(lg, xx, *weights)
@@ -579,6 +580,7 @@ def run_moe(args, rank: int, world: int, device):
                    f"expert parallel: {e_local} experts and {t_local} tokens per gpu, NCCL all-to-all each way, "
                    "fixed-capacity exchange (factor 1.5)",
                    "step": "router + alignment + gather + up|gate GEMM (SiLU) + down GEMM + combine",
+                   "expert_block_rows": args.moe_block,
                    "l2": "expert weights (571 MB) and row buffers exceed the 126 MB L2"},
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4), "traffic": None,
@@ -815,6 +817,8 @@ def main() -> int:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--load-seconds", type=float, default=1.5)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--moe-block", type=int, default=256, choices=[128, 256],
+                        help="rows every expert span is padded to (= row tile of the grouped contraction)")
     parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()
     if args.steps is None:

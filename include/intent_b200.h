@@ -159,7 +159,8 @@ INTENT_B200_API int intent_b200_moe_route_positions(INTENT_B200_VIEW1(a0), INTEN
  * a0 x [T,H] 16-bit, a1 sorted_route_ids [P], a2 total_padded [1] -> a3 rows [P,H]; padding rows are zero. */
 INTENT_B200_API int intent_b200_moe_gather_rows(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
                                                 INTENT_B200_VIEW2(a3), int32_t top_k, void* stream);
-/* Grouped int4 contractions over expert-sorted rows padded to 128 per expert (tcgen05 kernel of
+/* Grouped int4 contractions over expert-sorted rows padded to block_rows (128 or 256, the alignment's
+ * BLOCK_SIZE) per expert; a1 expert_blocks holds one expert id per block_rows rows (tcgen05 kernel of
  * weight_only_int4_matmul with a per-block expert; reference programs
  * examples/kernels/ragged/grouped_gemm.py:42-70 and examples/kernels/ragged/moe.py:37-47):
  *   a0 rows [P,K] T, a1 expert_blocks [B] i32, a2 total_padded [1] i32, a3 packed [E,K/8,WN] i32,
@@ -169,7 +170,8 @@ INTENT_B200_API int intent_b200_moe_gather_rows(INTENT_B200_VIEW2(a0), INTENT_B2
  * down_f32:    output [P,WN] f32. */
 #define INTENT_B200_GROUPED_SLOTS                                                                          \
   INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3),              \
-      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point, void *stream
+      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point,               \
+      int32_t block_rows, void *stream
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_bf16(INTENT_B200_GROUPED_SLOTS);
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_f16(INTENT_B200_GROUPED_SLOTS);
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_bf16(INTENT_B200_GROUPED_SLOTS);

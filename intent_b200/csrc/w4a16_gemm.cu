@@ -81,8 +81,8 @@ struct GemmParams {
   int twos_complement;
   int second_half_offset;    // weight-column distance of accumulator columns 128..255 (128, or I for up|gate)
   int out_cols;              // columns of the output matrix
-  const int* total_rows;     // grouped modes: device pointer to the padded row count (multiple of 128)
-  const int* tile_expert;    // grouped modes: expert of each 128-row block
+  const int* total_rows;     // grouped modes: device pointer to the padded row count (multiple of MT*128)
+  const int* tile_expert;    // grouped modes: expert of each (MT*128)-row block
 };
 
 constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
@@ -121,7 +121,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
   const int warp = tid >> 5;
   const int lane = tid & 31;
   // grouped modes: row blocks actually in use, read from device memory
-  const int m_tiles = MODE == MODE_DENSE ? p.m_tiles : min(p.m_tiles, (*p.total_rows + BM - 1) / BM);
+  const int m_tiles = MODE == MODE_DENSE ? p.m_tiles : min(p.m_tiles, (*p.total_rows + MT * BM - 1) / (MT * BM));
   const int tiles = m_tiles * p.n_tiles;
 
   if (tid == 0) {
@@ -469,17 +469,19 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
                                        stream);
 }
 
-// Grouped contractions over expert-sorted, 128-padded rows.
-//   x [P, K]; tile_expert [>= P/128]; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; out [P, out_cols]
+// Grouped contractions over expert-sorted rows padded to `block_rows` (128 or 256) per expert; with 256
+// two row blocks share every dequantised weight tile.
+//   x [P, K]; tile_expert [>= P/block_rows]; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; out [P, out_cols]
 template <typename T, int MODE>
 int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2 out, int group_size, int zero_point,
-                cudaStream_t stream) {
+                int block_rows, cudaStream_t stream) {
   const int64_t P = x.d0, K = x.d1, E = w.d0, WN = w.d2;
   const int64_t out_cols = MODE == MODE_UPGATE_SILU ? WN / 2 : WN;
   if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
   if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
   if (K % group_size != 0 || w.d1 * 8 != K || s.d0 != E || s.d1 * group_size != K || s.d2 != WN || out.d0 != P ||
-      out.d1 != out_cols || total.d0 < 1 || tile_expert.d0 * BM < P)
+      out.d1 != out_cols || total.d0 < 1 || (block_rows != BM && block_rows != 2 * BM) ||
+      tile_expert.d0 * block_rows < P)
     return INTENT_B200_ERR_SHAPE;
   if (P == 0 || WN == 0 || E == 0) return INTENT_B200_OK;
   if (!x.p || !w.p || !s.p || !out.p || !tile_expert.p || !total.p) return INTENT_B200_ERR_NULL;
@@ -489,6 +491,9 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
   if (K == 0 || WN % 8 != 0 || (MODE == MODE_UPGATE_SILU && (WN % 256 != 0)) ||
       P > (1 << 24) || K > (1 << 24) || WN > (1 << 24))
     return INTENT_B200_ERR_UNSUPPORTED;
+  if (block_rows == 2 * BM)
+    return launch_gemm<T, MODE, 2>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
+                                   static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
   return launch_gemm<T, MODE, 1>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
                                  static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
 }
@@ -519,10 +524,11 @@ extern "C" int intent_b200_w4a16_gemm_device_status(void) {
 #define IB200_GROUPED_ENTRY(NAME, TYPE, MODE)                                                                   \
   extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3), \
                       INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point,      \
-                      void* stream) {                                                                            \
+                      int32_t block_rows, void* stream) {                                                        \
     return ib200::run_grouped<TYPE, ib200::MODE>(IB200_VIEW2_ARG(a0), IB200_VIEW1_ARG(a1), IB200_VIEW1_ARG(a2),  \
                                                  IB200_VIEW3_ARG(a3), IB200_VIEW3_ARG(a4), IB200_VIEW2_ARG(a5),  \
-                                                 group_size, zero_point, static_cast<cudaStream_t>(stream));     \
+                                                 group_size, zero_point, block_rows,                             \
+                                                 static_cast<cudaStream_t>(stream));                             \
   }
 IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_bf16, __nv_bfloat16, MODE_UPGATE_SILU)
 IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_f16, __half, MODE_UPGATE_SILU)

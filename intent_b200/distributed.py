@@ -92,7 +92,8 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
-                 act_dtype="bf16", capacity_rows=None, capacity_factor=None, target=None, group=None):
+                 act_dtype="bf16", capacity_rows=None, capacity_factor=None, block_size=128, target=None,
+                 group=None):
         import torch
         import torch.distributed as dist
 
@@ -125,7 +126,7 @@ class ExpertParallelMoE:
                                constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k})
         self.local = MoEW4A16FFN(tokens=self.capacity, hidden=hidden, intermediate=intermediate,
                                  experts=self.local_experts, top_k=1, group_size=group_size,
-                                 zero_point=zero_point, act_dtype=act_dtype, target=target)
+                                 zero_point=zero_point, act_dtype=act_dtype, block_size=block_size, target=target)
         self.combine = _compile(programs.moe_combine, target=target)
         self._overflow = None
         self._torch = torch

@@ -129,13 +129,16 @@ class MoEW4A16FFN:
         self.alignment = MoEAlignment.build(tokens=tokens, top_k=top_k, experts=experts, block_size=block_size,
                                             target=target)
         align = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": block_size}
+        if block_size not in (128, 256):
+            raise ValueError("block_size must be 128 or 256 (rows of one tile of the grouped contraction)")
         quant = {"GROUP_SIZE": group_size, "ZERO_POINT": zero_point, "ACT_DTYPE": act_dtype}
         self.router = _compile(programs.moe_route_top2, target=target)
         self.positions = _compile(programs.moe_route_positions, target=target, constexprs=align)
         self.gather = _compile(programs.moe_gather_rows, target=target,
                                constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k})
-        self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=quant)
-        self.down = _compile(programs.moe_grouped_down, target=target, constexprs=quant)
+        grouped = dict(quant, BLOCK_ROWS=block_size)
+        self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=grouped)
+        self.down = _compile(programs.moe_grouped_down, target=target, constexprs=grouped)
         self.combine = _compile(programs.moe_combine, target=target)
 
     def route(self, logits):

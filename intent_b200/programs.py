@@ -277,6 +277,9 @@ def _grouped_constants(c):
 def _lower_grouped(c, device, *, gated):
     act = _act_dtype(c)
     group, zp = _grouped_constants(c)
+    block = int(c["BLOCK_ROWS"])
+    if block not in (128, 256):
+        raise CompilationStageError("provider_native_compilation", "BLOCK_ROWS must be 128 or 256")
     out_cols = Derived("I", lambda d: d["WN"] // 2) if gated else "WN"
     interface = PublicInterface((
         ViewParameter(0, "rows", act, ("P", "K"), IN),
@@ -288,14 +291,14 @@ def _lower_grouped(c, device, *, gated):
     ), dimension_rules=(
         _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
               "packed_weight / scales do not match K and GROUP_SIZE"),
-        _rule(lambda d: d["B"] * 128 >= d["P"], "expert_blocks must cover every 128-row block of rows"),
+        _rule(lambda d: d["B"] * block >= d["P"], f"expert_blocks must cover every {block}-row block of rows"),
     ))
     stem = "upgate_silu" if gated else "down_f32"
     return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_{stem}_{act.name}",
-                         constants=(group, zp), device=device)
+                         constants=(group, zp, block), device=device)
 
 
-_GROUPED_CONSTEXPRS = {"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16"}
+_GROUPED_CONSTEXPRS = {"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16", "BLOCK_ROWS": 128}
 moe_grouped_upgate_silu = KernelDefinition(
     "moe_grouped_upgate_silu", dict(_GROUPED_CONSTEXPRS), lambda c, d: _lower_grouped(c, d, gated=True),
     "examples/kernels/ragged/grouped_gemm.py:42-70, examples/kernels/ragged/moe.py:37-42, "

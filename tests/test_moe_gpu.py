@@ -76,9 +76,10 @@ def _ffn_case(tokens, hidden, intermediate, experts, dtype, seed):
     (torch.float16, 300, 256, 128, 4),
     (torch.bfloat16, 1024, 1024, 384, 16),
 ])
-def test_moe_ffn_matches_oracle(cuda_device, dtype, tokens, hidden, intermediate, experts):
+@pytest.mark.parametrize("block_size", [128, 256])
+def test_moe_ffn_matches_oracle(cuda_device, dtype, tokens, hidden, intermediate, experts, block_size):
     data, ids, weights = _ffn_case(tokens, hidden, intermediate, experts, dtype, seed=11)
-    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts,
+    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts, block_size=block_size,
                       act_dtype="bf16" if dtype == torch.bfloat16 else "f16", target=ib.B200Target(0))
     dev = {k: v.to(cuda_device) for k, v in data.items()}
     got_ids, got_weights = ffn.route(dev["logits"])
