@@ -817,7 +817,7 @@ def main() -> int:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--load-seconds", type=float, default=1.5)
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--moe-block", type=int, default=256, choices=[128, 256],
+    parser.add_argument("--moe-block", type=int, default=128, choices=[128, 256],
                         help="rows every expert span is padded to (= row tile of the grouped contraction)")
     parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()

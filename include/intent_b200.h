@@ -183,6 +183,30 @@ INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_V
                                             INTENT_B200_VIEW2(a3), void* stream);
 
 /* ------------------------------------------------------------------------
+ * Expert-parallel exchange over peer memory (NVLink), no collective on the data path.  The caller maps
+ * every rank's row buffer [capacity_rows, H] (16-bit) and result buffer [capacity_rows, H] (f32) into this
+ * process (symmetric memory / CUDA IPC) and passes the device addresses as int64 tables; it orders the
+ * phases across ranks with stream-ordered barriers (all rows written before any owner computes, all
+ * results written before any rank combines).  No kernel waits on another GPU.
+ * Owner layout: local experts in order, spans padded to block_rows; inside a span source rank 0 first.
+ * ------------------------------------------------------------------------ */
+/* a0 counts [W,E] i32 (routes of every source rank to every global expert, E = W * experts per rank)
+ * -> a1 dest_base [E] (first row, in the owner's buffer, of this rank's routes to expert e),
+ *    a2 local_offsets [E/W + 1] (span starts of this rank's own experts; last = padded total), a3 total_padded [1] */
+INTENT_B200_API int intent_b200_moe_peer_layout(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                INTENT_B200_VIEW1(a3), int32_t rank, int32_t block_rows, void* stream);
+/* a0 x [T,H] 16-bit, a1 sorted_routes [R] (route ids grouped by expert, stable, no padding), a2 send_offsets [E+1]
+ * (exclusive prefix of this rank's per-expert counts), a3 dest_base [E], a4 peer_rows [W] i64
+ * -> writes row x[route / top_k] to peer_rows[owner] + position * H; a5 route_dest [R,2] = (owner, position) */
+INTENT_B200_API int intent_b200_moe_peer_dispatch(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                                  INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW2(a5),
+                                                  int32_t top_k, int32_t capacity_rows, void* stream);
+/* a0 peer_out [W] i64, a1 route_dest [R,2], a2 weights [T,K] f32, a3 y [T,H] f32 (InOut):
+ * y[t,:] += sum over choices c in order of weights[t,c] * (peer_out[owner] + position * H)[:] */
+INTENT_B200_API int intent_b200_moe_peer_combine(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
+                                                 INTENT_B200_VIEW2(a3), int32_t capacity_rows, void* stream);
+
+/* ------------------------------------------------------------------------
  * Ragged grouped contractions with dense 16-bit weights (tcgen05 kind::f16, f32 accumulation).
  * Group offsets are read on the device (clamped to the row count); K and N multiples of 8,
  * at most 1024 groups.  Rows of an empty group and rows outside every group are not written.

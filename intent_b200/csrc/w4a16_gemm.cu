@@ -62,11 +62,15 @@ constexpr int DQ_ROWS = (BK / 8) / DQ_PARTS; // packed words per thread and k bl
 constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
 constexpr int BAND_TILES = 8;         // row tiles per band of the tile walk
 
+constexpr int PAIR_LIST_BLOCKS = 8192;  // most 128-row blocks the in-kernel block pairing handles
+
 template <int MT>
 struct Stages {
   static constexpr int A = MT == 1 ? 5 : 3;   // stages of X
   static constexpr int B = 3;                 // stages of the dequantised tile
   static constexpr int SMEM = 1024 + A * MT * A_BYTES + B * B_BYTES + 256;
+  // grouped modes with two row blocks per tile keep the list of block pairs behind the barriers
+  static constexpr int SMEM_PAIRED = SMEM + PAIR_LIST_BLOCKS * 2 + 16;
 };
 
 struct GemmParams {
@@ -82,7 +86,9 @@ struct GemmParams {
   int second_half_offset;    // weight-column distance of accumulator columns 128..255 (128, or I for up|gate)
   int out_cols;              // columns of the output matrix
   const int* total_rows;     // grouped modes: device pointer to the padded row count (multiple of MT*128)
-  const int* tile_expert;    // grouped modes: expert of each (MT*128)-row block
+  const int* tile_expert;    // grouped modes: expert of each (MT*128)-row block; of each 128-row block with pair_blocks
+  int pair_blocks;           // grouped modes, MT = 2: rows are padded to 128 per expert and the kernel pairs
+                             // neighbouring blocks of one expert itself (an odd last block runs as half a tile)
 };
 
 constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
@@ -120,9 +126,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  // grouped modes: row blocks actually in use, read from device memory
-  const int m_tiles = MODE == MODE_DENSE ? p.m_tiles : min(p.m_tiles, (*p.total_rows + MT * BM - 1) / (MT * BM));
-  const int tiles = m_tiles * p.n_tiles;
+  constexpr bool CAN_PAIR = MODE != MODE_DENSE && MT == 2;
+  const bool paired = CAN_PAIR && p.pair_blocks != 0;
+  // tile list of the paired form: low 15 bits = first 128-row block, bit 15 = the next block belongs to it too
+  uint16_t* pair_list = reinterpret_cast<uint16_t*>(base_ptr + (tmem_slot - base) + 16);
+  volatile int* pair_count = reinterpret_cast<volatile int*>(base_ptr + (tmem_slot - base) + 8);
 
   if (tid == 0) {
     for (int s = 0; s < A_STAGES; ++s) {
@@ -140,10 +148,57 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
+  if (CAN_PAIR && paired && warp == 0) {
+    // Pair neighbouring 128-row blocks of one expert: a block whose position inside its expert's run
+    // is even starts a tile; the tile has a second half when the next block has the same expert.
+    const int blocks = min(min(2 * p.m_tiles, PAIR_LIST_BLOCKS), (*p.total_rows + BM - 1) / BM);
+    int count = 0, carry_expert = -1, carry_start = 0;
+    for (int b0 = 0; b0 < blocks; b0 += 32) {
+      const int b = b0 + lane;
+      const int e = b < blocks ? __ldg(p.tile_expert + b) : -1;
+      int previous = __shfl_up_sync(0xffffffffu, e, 1);
+      if (lane == 0) previous = carry_expert;
+      int next = __shfl_down_sync(0xffffffffu, e, 1);
+      if (lane == 31) next = b + 1 < blocks ? __ldg(p.tile_expert + b + 1) : -1;
+      int start = (b < blocks && (b == 0 || e != previous)) ? b : -1;  // first block of its expert's run
+      if (lane == 0 && start < 0) start = carry_start;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {  // running maximum: the latest run start at or before this block
+        const int v = __shfl_up_sync(0xffffffffu, start, o);
+        if (lane >= o) start = max(start, v);
+      }
+      const bool first = b < blocks && ((b - start) & 1) == 0;
+      const uint32_t ballot = __ballot_sync(0xffffffffu, first);
+      if (first) {
+        const int t = count + __popc(ballot & ((1u << lane) - 1u));
+        pair_list[t] = uint16_t(b | ((b + 1 < blocks && next == e) ? 0x8000 : 0));
+      }
+      count += __popc(ballot);
+      carry_expert = __shfl_sync(0xffffffffu, e, 31);
+      carry_start = __shfl_sync(0xffffffffu, start, 31);
+    }
+    if (lane == 0) *pair_count = count;
+  }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // grouped modes: row blocks actually in use, read from device memory
+  const int m_tiles = MODE == MODE_DENSE ? p.m_tiles
+                      : paired           ? *pair_count
+                                         : min(p.m_tiles, (*p.total_rows + MT * BM - 1) / (MT * BM));
+  const int tiles = m_tiles * p.n_tiles;
+  // first 128-row block of a row tile and whether its second block is present
+  auto tile_blocks = [&](int m_tile, int& first_block, int& halves) {
+    if (CAN_PAIR && paired) {
+      const uint32_t entry = pair_list[m_tile];
+      first_block = int(entry & 0x7FFFu);
+      halves = (entry & 0x8000u) ? 2 : 1;
+    } else {
+      first_block = m_tile * MT;
+      halves = MT;
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -153,14 +208,17 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         int m_tile, n_tile;
         tile_coords(tile, m_tiles, p.n_tiles, m_tile, n_tile);
+        int first_block, halves;
+        tile_blocks(m_tile, first_block, halves);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % A_STAGES;
           if (!mbar_wait(empty_a + 8 * s, ((it / A_STAGES) & 1) ^ 1)) { ok = false; break; }
           const uint32_t bar = full_a + 8 * s;
-          mbar_expect_tx(bar, MT * A_BYTES);
+          mbar_expect_tx(bar, halves * A_BYTES);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
-            tma_load_2d(smem_a + (s * MT + mt) * A_BYTES, &map_x, kb * BK, (m_tile * MT + mt) * BM, bar);
+            if (mt < halves)
+              tma_load_2d(smem_a + (s * MT + mt) * A_BYTES, &map_x, kb * BK, (first_block + mt) * BM, bar);
         }
       }
       if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -173,6 +231,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+        int first_block = 0, halves = MT;
+        if (CAN_PAIR && paired) {
+          int m_tile, n_tile;
+          tile_coords(tile, m_tiles, p.n_tiles, m_tile, n_tile);
+          tile_blocks(m_tile, first_block, halves);
+        }
         const uint32_t acc = local % ACC_BUFFERS;
         if (!mbar_wait(tmem_empty + 8 * acc, ((local / ACC_BUFFERS) & 1) ^ 1)) { ok = false; break; }
         tcgen05_fence_after();
@@ -185,6 +249,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
           const uint64_t desc_b = umma_desc_k_major_sw128(smem_b + t * B_BYTES);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
+            if (mt >= halves) break;
             const uint64_t desc_a = umma_desc_k_major_sw128(smem_a + (s * MT + mt) * A_BYTES);
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements of 2 bytes = 32 bytes = 2 descriptor units
@@ -205,6 +270,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       int m_tile, n_tile;
       tile_coords(tile, m_tiles, p.n_tiles, m_tile, n_tile);
+      int first_block, halves;
+      tile_blocks(m_tile, first_block, halves);
       const uint32_t acc = local % ACC_BUFFERS;
       if (!__all_sync(0xffffffffu, mbar_wait(tmem_full + 8 * acc, (local / ACC_BUFFERS) & 1))) {
         if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
@@ -212,8 +279,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       }
       tcgen05_fence_after();
 #pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
-        const int row = (m_tile * MT + mt) * BM + quadrant * 32 + lane;
+      for (int mt = 0; mt < halves; ++mt) {
+        const int row = (first_block + mt) * BM + quadrant * 32 + lane;
         const uint32_t taddr = tmem_base + acc * (MT * BN) + mt * BN + (uint32_t(quadrant * 32) << 16);
         if (MODE == MODE_UPGATE_SILU) {
           // accumulator columns 0..127 = gate, 128..255 = the matching up columns
@@ -314,7 +381,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       if (f_kb == 0) {
         int m_tile, n_tile;
         tile_coords(f_tile, m_tiles, p.n_tiles, m_tile, n_tile);
-        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[m_tile];
+        int first_block, halves;
+        tile_blocks(m_tile, first_block, halves);
+        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[(CAN_PAIR && paired) ? first_block : m_tile];
         const int col = (MODE == MODE_UPGATE_SILU ? n_tile * 128 : n_tile * BN) +
                         (n < 128 ? n : p.second_half_offset + (n - 128));
         f_col_ok = col < p.WN;
@@ -409,7 +478,7 @@ int device_sms() {
 template <typename T, int MODE, int MT>
 int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t WN, void* out,
                 int64_t out_cols, int group_size, int zero_point, const int* total_rows, const int* tile_expert,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool pair_blocks = false) {
   const int sms = device_sms();
   if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
   const CUtensorMapDataType type =
@@ -430,6 +499,7 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
   p.out_cols = int(out_cols);
   p.total_rows = total_rows;
   p.tile_expert = tile_expert;
+  p.pair_blocks = pair_blocks ? 1 : 0;
 
   CUtensorMap map_x;
   if (!make_tensor_map_2d(&map_x, type, x, uint64_t(rows), uint64_t(K), uint64_t(K) * 2, BM, BK,
@@ -437,11 +507,12 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
     return INTENT_B200_ERR_UNSUPPORTED;
 
   auto kernel = w4a16_gemm_kernel<T, MODE, MT>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Stages<MT>::SMEM);
+  constexpr int smem = (MODE != MODE_DENSE && MT == 2) ? Stages<MT>::SMEM_PAIRED : Stages<MT>::SMEM;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, THREADS, Stages<MT>::SMEM, stream>>>(map_x, p);
+  kernel<<<grid, THREADS, smem, stream>>>(map_x, p);
   note_launch();
   return launch_status();
 }
@@ -491,9 +562,10 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
   if (K == 0 || WN % 8 != 0 || (MODE == MODE_UPGATE_SILU && (WN % 256 != 0)) ||
       P > (1 << 24) || K > (1 << 24) || WN > (1 << 24))
     return INTENT_B200_ERR_UNSUPPORTED;
-  if (block_rows == 2 * BM)
+  if (block_rows == 2 * BM || (P + BM - 1) / BM <= PAIR_LIST_BLOCKS)   // 128-row blocks are paired by the kernel
     return launch_gemm<T, MODE, 2>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
-                                   static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
+                                   static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream,
+                                   block_rows == BM);
   return launch_gemm<T, MODE, 1>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
                                  static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
 }

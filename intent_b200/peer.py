@@ -1,0 +1,199 @@
+"""Expert-parallel MoE over peer memory: no collective on the data path.
+
+Every rank writes the token rows of its routes straight into the expert-sorted row buffer
+of the rank that owns the expert (NVLink stores), the owners run the grouped int4 FFN on
+rows that are already in place, and every rank then reads the finished f32 rows straight
+out of the owners' result buffers while it combines them (NVLink loads).  Only real rows
+cross the links: there are no padded spans, no staging copy and no second gather.  The
+per-step host traffic is one 4*E-byte count all-gather and two barriers, all stream-ordered
+NCCL calls; no kernel waits on another GPU.
+
+The owner's layout (experts in local order, spans padded to the tile rows, source rank 0
+first inside a span) equals the single-GPU stable alignment over all tokens when the
+tokens are split contiguously over the ranks, so the result is bit-identical to one GPU.
+
+``PeerExchangeRank`` is one rank's side with the cross-rank steps left to the caller; the
+tests drive several of them on one GPU in sequence (the ranks' buffers are then plain
+local tensors).  ``PeerExpertParallelMoE`` binds it to ``torch.distributed``: the buffers
+live in symmetric memory so every rank can address every other rank's copy.
+"""
+from __future__ import annotations
+
+from . import programs
+from .compiler import compile as _compile
+
+
+class PeerExchangeRank:
+    def __init__(self, *, rank, world, tokens, hidden, intermediate, experts, top_k=2, group_size=128,
+                 zero_point=8, act_dtype="bf16", block_rows=128, target=None):
+        if experts % world:
+            raise ValueError("the expert count must be a multiple of the number of ranks")
+        if block_rows not in (128, 256):
+            raise ValueError("block_rows must be 128 or 256")
+        self.rank, self.world = rank, world
+        self.tokens, self.hidden, self.intermediate = tokens, hidden, intermediate
+        self.experts, self.local_experts, self.top_k = experts, experts // world, top_k
+        self.routes = tokens * top_k
+        self.block_rows = block_rows
+        self.act_dtype = act_dtype
+        # worst case: every route of every rank goes to this rank's experts
+        self.capacity_rows = world * self.routes + self.local_experts * (block_rows - 1)
+        send = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": 1}
+        own = {"TOKENS": world * self.routes, "TOP_K": 1, "EXPERTS": self.local_experts, "BLOCK_SIZE": block_rows}
+        quant = {"GROUP_SIZE": group_size, "ZERO_POINT": zero_point, "ACT_DTYPE": act_dtype,
+                 "BLOCK_ROWS": block_rows}
+        self.router = _compile(programs.moe_route_top2, target=target)
+        self.count = _compile(programs.moe_count_routes, target=target, constexprs=send)
+        self.prefix = _compile(programs.moe_prefix_routes, target=target, constexprs=send)
+        self.scatter = _compile(programs.moe_scatter_routes, target=target, constexprs=send)
+        self.layout = _compile(programs.moe_peer_layout, target=target,
+                               constexprs={"WORLD": world, "EXPERTS": experts, "RANK": rank,
+                                           "BLOCK_ROWS": block_rows})
+        self.mark = _compile(programs.moe_mark_expert_blocks, target=target, constexprs=own)
+        self.dispatch = _compile(programs.moe_peer_dispatch, target=target,
+                                 constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k,
+                                             "CAPACITY_ROWS": self.capacity_rows})
+        self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=quant)
+        self.down = _compile(programs.moe_grouped_down, target=target, constexprs=quant)
+        self.combine = _compile(programs.moe_peer_combine, target=target,
+                                constexprs={"CAPACITY_ROWS": self.capacity_rows})
+
+    def buffer_shapes(self):
+        """(shape, torch dtype) of the row buffer and of the f32 result buffer every rank exposes."""
+        import torch
+
+        rows = torch.bfloat16 if self.act_dtype == "bf16" else torch.float16
+        return ((self.capacity_rows, self.hidden), rows), ((self.capacity_rows, self.hidden), torch.float32)
+
+    def prepare(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y, *, rows, out,
+                peer_rows, peer_out, counts_all):
+        """Bind one step to fixed buffers.  ``rows`` / ``out``: this rank's buffers; ``peer_rows`` /
+        ``peer_out``: int64 [world] device tensors with every rank's buffer address as seen from
+        this device; ``counts_all``: int32 [world, experts] device tensor the caller fills between
+        ``route()`` and ``dispatch_rows()`` (this rank's own row is ``step.counts``)."""
+        return PeerStep(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y, rows, out,
+                        peer_rows, peer_out, counts_all)
+
+
+class PeerStep:
+    """The four phases of one bound step; the caller puts the cross-rank steps between them:
+
+        route()          -> exchange ``counts`` into ``counts_all``
+        dispatch_rows()  -> barrier (all rows are in their owners' buffers)
+        experts()        -> barrier (all result rows are written)
+        combine()
+    """
+
+    def __init__(self, ep, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y, rows, out,
+                 peer_rows, peer_out, counts_all):
+        import torch
+
+        device = x.device
+        self.ep, self.y = ep, y
+        self.counts = torch.zeros((ep.experts,), dtype=torch.int32, device=device)
+        self.cursors = torch.zeros((ep.experts,), dtype=torch.int32, device=device)
+        self.sorted_routes = torch.empty((ep.routes,), dtype=torch.int32, device=device)
+        self._router = ep.router.prepare(logits)
+        self.ids, self.weights = self._router.result()
+        self._count = ep.count.prepare(self.ids, self.counts)
+        self._prefix = ep.prefix.prepare(self.counts)
+        self.send_offsets, _ = self._prefix.result()
+        self._scatter = ep.scatter.prepare(self.ids, self.send_offsets, self.cursors, self.sorted_routes)
+        self._layout = ep.layout.prepare(counts_all)
+        self.dest_base, self.local_offsets, self.total = self._layout.result()
+        self._mark = ep.mark.prepare(self.local_offsets)
+        self.expert_blocks = self._mark.result()
+        self._dispatch = ep.dispatch.prepare(x, self.sorted_routes, self.send_offsets, self.dest_base, peer_rows)
+        self.route_dest = self._dispatch.result()
+        self._up = ep.up_gate.prepare(rows, self.expert_blocks, self.total, up_gate_packed, up_gate_scales)
+        self._down = ep.down.prepare(self._up.result(), self.expert_blocks, self.total, down_packed, down_scales,
+                                     outputs=(out,))
+        self._combine = ep.combine.prepare(peer_out, self.route_dest, self.weights, y)
+
+    def route(self):
+        self.counts.zero_()
+        self.cursors.zero_()
+        self._router.launch()
+        self._count.launch()
+        self._prefix.launch()
+        self._scatter.launch()
+
+    def dispatch_rows(self):
+        self._layout.launch()
+        self._mark.launch()
+        self._dispatch.launch()
+
+    def experts(self):
+        self._up.launch()
+        self._down.launch()
+
+    def combine(self, accumulate=False):
+        if not accumulate:
+            self.y.zero_()
+        self._combine.launch()
+
+
+class PeerExpertParallelMoE:
+    """``PeerExchangeRank`` bound to a process group: symmetric-memory buffers, an all-gather of the
+    per-expert route counts and two barriers per step, all on the current stream."""
+
+    def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
+                 act_dtype="bf16", block_rows=128, target=None, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.side = PeerExchangeRank(rank=self.rank, world=self.world, tokens=tokens, hidden=hidden,
+                                     intermediate=intermediate, experts=experts, top_k=top_k,
+                                     group_size=group_size, zero_point=zero_point, act_dtype=act_dtype,
+                                     block_rows=block_rows, target=target)
+        device = torch.device("cuda", target.device if target is not None else torch.cuda.current_device())
+        (rows_shape, rows_dtype), (out_shape, out_dtype) = self.side.buffer_shapes()
+        self.rows = symmetric.empty(rows_shape, dtype=rows_dtype, device=device)
+        self.out = symmetric.empty(out_shape, dtype=out_dtype, device=device)
+        self.rows.zero_()
+        rows_handle = symmetric.rendezvous(self.rows, self.group)
+        out_handle = symmetric.rendezvous(self.out, self.group)
+        # keep the peer views alive: their storage is the mapping of the peer's buffer
+        self._peer_rows = [rows_handle.get_buffer(r, rows_shape, rows_dtype) for r in range(self.world)]
+        self._peer_out = [out_handle.get_buffer(r, out_shape, out_dtype) for r in range(self.world)]
+        self.peer_rows = torch.tensor([t.data_ptr() for t in self._peer_rows], dtype=torch.int64, device=device)
+        self.peer_out = torch.tensor([t.data_ptr() for t in self._peer_out], dtype=torch.int64, device=device)
+        self.counts_all = torch.zeros((self.world, experts), dtype=torch.int32, device=device)
+        self._token = torch.zeros((1,), dtype=torch.int32, device=device)
+        self._dist = dist
+
+    def barrier(self):
+        self._dist.all_reduce(self._token, group=self.group)
+
+    def prepare(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y=None):
+        import torch
+
+        if y is None:
+            y = torch.empty((x.shape[0], self.side.hidden), dtype=torch.float32, device=x.device)
+        step = self.side.prepare(logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y,
+                                 rows=self.rows, out=self.out, peer_rows=self.peer_rows, peer_out=self.peer_out,
+                                 counts_all=self.counts_all)
+        return PreparedPeerStep(self, step)
+
+    def __call__(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):
+        call = self.prepare(logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales)
+        call.launch()
+        return call.y
+
+
+class PreparedPeerStep:
+    def __init__(self, ep: PeerExpertParallelMoE, step: PeerStep):
+        self.ep, self.step, self.y = ep, step, step.y
+
+    def launch(self, accumulate=False):
+        ep, step = self.ep, self.step
+        step.route()
+        ep._dist.all_gather_into_tensor(ep.counts_all.view(-1), step.counts, group=ep.group)
+        step.dispatch_rows()
+        ep.barrier()          # every row of this step is in its owner's buffer
+        step.experts()
+        ep.barrier()          # every result row is written; also fences the row buffers for the next step
+        step.combine(accumulate)

@@ -537,3 +537,71 @@ quantized_gemm = KernelDefinition(
     "i8(clamp((relu(A @ B + bias) + residual) / scale)), truncating cast")
 
 ALL.update({d.name: d for d in (gemm, bf16_gemm, quantized_gemm)})
+
+
+# ---------------------------------------------------------------------------------
+# Expert-parallel exchange over peer memory
+# ---------------------------------------------------------------------------------
+def _lower_peer_layout(c, device):
+    world, experts, rank, block = (int(c[k]) for k in ("WORLD", "EXPERTS", "RANK", "BLOCK_ROWS"))
+    if world <= 0 or experts % world or not 0 <= rank < world or block <= 0:
+        raise CompilationStageError("frontend_kir", "EXPERTS must be a multiple of WORLD and 0 <= RANK < WORLD")
+    interface = PublicInterface((
+        ViewParameter(0, "counts", dtypes.i32, (world, experts), IN, alignment=4),
+        ViewParameter(1, "dest_base", dtypes.i32, (experts,), OUT, alignment=4),
+        ViewParameter(2, "local_offsets", dtypes.i32, (experts // world + 1,), OUT, alignment=4),
+        ViewParameter(3, "total_padded", dtypes.i32, (1,), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_layout", constants=(rank, block),
+                         device=device)
+
+
+moe_peer_layout = KernelDefinition(
+    "moe_peer_layout", {"WORLD": 1, "EXPERTS": 64, "RANK": 0, "BLOCK_ROWS": 128}, _lower_peer_layout,
+    "examples/kernels/routing/moe_align.py:32-49 (padded offsets), over the ranks' count matrix",
+    "where this rank's routes start inside every owner's expert-sorted row buffer")
+
+
+def _lower_peer_dispatch(c, device):
+    act = _act_dtype(c)
+    top_k, capacity = int(c["TOP_K"]), int(c["CAPACITY_ROWS"])
+    interface = PublicInterface((
+        ViewParameter(0, "x", act, ("T", "H"), IN),
+        ViewParameter(1, "sorted_routes", dtypes.i32, ("R",), IN, alignment=4),
+        ViewParameter(2, "send_offsets", dtypes.i32, ("E_PLUS_1",), IN, alignment=4),
+        ViewParameter(3, "dest_base", dtypes.i32, ("E",), IN, alignment=4),
+        ViewParameter(4, "peer_rows", dtypes.i64, ("W",), IN, alignment=8),
+        ViewParameter(5, "route_dest", dtypes.i32, ("R", 2), OUT, alignment=4),
+    ), dimension_rules=(
+        _rule(lambda d: d["R"] == d["T"] * top_k, "sorted_routes must have T * TOP_K entries"),
+        _rule(lambda d: d["E_PLUS_1"] == d["E"] + 1 and d["E"] % d["W"] == 0,
+              "send_offsets needs E + 1 entries and E must be a multiple of the rank count"),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_dispatch",
+                         constants=(top_k, capacity), device=device)
+
+
+moe_peer_dispatch = KernelDefinition(
+    "moe_peer_dispatch", {"ACT_DTYPE": "bf16", "TOP_K": 2, "CAPACITY_ROWS": 0}, _lower_peer_dispatch,
+    "examples/kernels/ragged/moe.py:34-36 (I.gather of token rows), written into the owner rank's buffer",
+    "rows[owner][position] = x[route // TOP_K] over peer memory")
+
+
+def _lower_peer_combine(c, device):
+    capacity = int(c["CAPACITY_ROWS"])
+    interface = PublicInterface((
+        ViewParameter(0, "peer_out", dtypes.i64, ("W",), IN, alignment=8),
+        ViewParameter(1, "route_dest", dtypes.i32, ("R", 2), IN, alignment=4),
+        ViewParameter(2, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
+        ViewParameter(3, "y", dtypes.f32, ("T", "H"), INOUT),
+    ), dimension_rules=(_rule(lambda d: d["R"] == d["T"] * d["TOP_K"], "route_dest must have T * TOP_K rows"),))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_combine", constants=(capacity,),
+                         device=device)
+
+
+moe_peer_combine = KernelDefinition(
+    "moe_peer_combine", {"CAPACITY_ROWS": 0}, _lower_peer_combine,
+    "examples/kernels/ragged/moe.py:48-53 (weighted scatter_reduce add), reading the owners' result rows",
+    "y[t] += sum_c weight[t,c] * out[owner(t,c)][position(t,c)] over peer memory")
+
+ALL.update({d.name: d for d in (moe_peer_layout, moe_peer_dispatch, moe_peer_combine)})

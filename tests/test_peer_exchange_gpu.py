@@ -1,0 +1,124 @@
+"""Expert-parallel MoE over peer memory.
+
+On one GPU the ranks are emulated in sequence: every rank's buffers are plain local tensors,
+the address tables point at them, and the phases run rank after rank (no kernel waits on
+another one).  The result must equal the single-GPU FFN over all tokens bit for bit.  The
+two-process test (skipped on a single GPU) does the same through symmetric memory and NCCL."""
+import os
+import socket
+
+import pytest
+import torch
+
+import intent_b200 as ib
+from intent_b200.moe import MoEW4A16FFN
+from intent_b200.peer import PeerExchangeRank
+
+pytestmark = pytest.mark.gpu
+
+
+def _slices(data, device, rank, world, tokens, experts):
+    t_local, e_local = tokens // world, experts // world
+    rows, ex = slice(rank * t_local, (rank + 1) * t_local), slice(rank * e_local, (rank + 1) * e_local)
+    return (data["logits"][rows].contiguous().to(device), data["x"][rows].contiguous().to(device),
+            [data[k][ex].contiguous().to(device) for k in ("up_gate_packed", "up_gate_scales", "down_packed",
+                                                            "down_scales")])
+
+
+@pytest.mark.parametrize("world,tokens,hidden,inter,experts", [(2, 512, 512, 256, 8), (4, 1024, 256, 128, 16),
+                                                               (1, 300, 256, 128, 4)])
+def test_peer_exchange_emulated_ranks(cuda_device, world, tokens, hidden, inter, experts):
+    data = ib.workloads.moe_inputs(tokens, hidden, experts, inter, dtype=torch.bfloat16, seed=5)
+    target = ib.B200Target(0)
+    full = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts, target=target)
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    ids, weights = full.route(dev["logits"])
+    expected = full(dev["x"], ids, weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
+                    dev["down_scales"])
+
+    t_local = tokens // world
+    sides = [PeerExchangeRank(rank=r, world=world, tokens=t_local, hidden=hidden, intermediate=inter,
+                              experts=experts, target=target) for r in range(world)]
+    (rows_shape, rows_dtype), (out_shape, out_dtype) = sides[0].buffer_shapes()
+    rows = [torch.zeros(rows_shape, dtype=rows_dtype, device=cuda_device) for _ in range(world)]
+    out = [torch.zeros(out_shape, dtype=out_dtype, device=cuda_device) for _ in range(world)]
+    peer_rows = torch.tensor([t.data_ptr() for t in rows], dtype=torch.int64, device=cuda_device)
+    peer_out = torch.tensor([t.data_ptr() for t in out], dtype=torch.int64, device=cuda_device)
+    counts_all = torch.zeros((world, experts), dtype=torch.int32, device=cuda_device)
+    ys, steps = [], []
+    for r, side in enumerate(sides):
+        logits, x, w = _slices(data, cuda_device, r, world, tokens, experts)
+        y = torch.full((t_local, hidden), 3.0, dtype=torch.float32, device=cuda_device)
+        ys.append(y)
+        steps.append(side.prepare(logits, x, *w, y, rows=rows[r], out=out[r], peer_rows=peer_rows,
+                                  peer_out=peer_out, counts_all=counts_all))
+    for repeat in range(2):          # the second pass runs over buffers that hold the first pass's rows
+        for step in steps:
+            step.route()
+        for r, step in enumerate(steps):
+            counts_all[r].copy_(step.counts)
+        for step in steps:
+            step.dispatch_rows()
+        for step in steps:
+            step.experts()
+        for step in steps:
+            step.combine()
+        torch.cuda.synchronize()
+        assert torch.equal(torch.cat(ys), expected), f"pass {repeat}"
+    # every route was placed: owners and positions are in range, positions are unique per owner
+    placed = torch.cat([s.route_dest for s in steps]).cpu()
+    assert placed[:, 0].min() >= 0 and placed[:, 0].max() < world
+    keys = placed[:, 0].long() * sides[0].capacity_rows + placed[:, 1].long()
+    assert keys.unique().numel() == keys.numel()
+    assert int(counts_all.sum()) == tokens * 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _peer_worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    from intent_b200.peer import PeerExpertParallelMoE
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        tokens, hidden, inter, experts = 512, 512, 256, 8
+        data = ib.workloads.moe_inputs(tokens, hidden, experts, inter, dtype=torch.bfloat16, seed=21)
+        target = ib.B200Target(rank)
+        full = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts, target=target)
+        dev = {k: v.to(device) for k, v in data.items()}
+        ids, weights = full.route(dev["logits"])
+        expected = full(dev["x"], ids, weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
+                        dev["down_scales"])
+        logits, x, w = _slices(data, device, rank, world, tokens, experts)
+        ep = PeerExpertParallelMoE(tokens=tokens // world, hidden=hidden, intermediate=inter, experts=experts,
+                                   target=target)
+        call = ep.prepare(logits, x, *w)
+        ok = True
+        for _ in range(3):
+            call.launch()
+            torch.cuda.synchronize()
+            t_local = tokens // world
+            ok = ok and bool(torch.equal(call.y, expected[rank * t_local:(rank + 1) * t_local]))
+        results[rank] = ok
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_peer_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+    assert dict(results) == {0: True, 1: True}
