@@ -290,10 +290,18 @@ def timed_steps(step, steps: int, warmup: int, world: int, device, rank: int, lo
     sampler = ClockSampler(device.index)
     if rank == 0:
         sampler.start()
-    until = time.perf_counter() + load_seconds
-    while time.perf_counter() < until:
+    # hold the load for about load_seconds; every rank runs the same number of steps (a step may
+    # contain collectives, so the count is agreed on, not decided by each rank's own clock)
+    load_steps = 0
+    if load_seconds > 0:
+        t0 = time.perf_counter()
         step()
         torch.cuda.synchronize()
+        one = max(time.perf_counter() - t0, 1e-5)
+        load_steps = int(reduce_max(min(load_seconds / one, 1e6), world, device))
+    for _ in range(load_steps):
+        step()
+    torch.cuda.synchronize()
     barrier(world)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -537,6 +545,25 @@ def run_moe(args, rank: int, world: int, device):
                 router.launch()
                 return chain.launch()
             return launch
+    elif args.moe_exchange == "peer":
+        from intent_b200.peer import PeerExpertParallelMoE
+
+        # rows go straight into the owners' buffers over NVLink and results are read straight back:
+        # no collective on the data path, worst-case buffers (no overflow case)
+        ep = PeerExpertParallelMoE(tokens=t_local, hidden=hidden, intermediate=inter, experts=experts,
+                                   block_rows=args.moe_block, target=ib.B200Target(device.index))
+        bound = {}
+
+        def prepare(lg, xx):
+            call = ep.prepare(lg, xx, *weights)
+            bound.update(logits=lg, x=xx, call=call)
+            return call.launch
+
+        def forward(lg, xx):      # end to end: the bound input buffers are refilled, the bound step is launched
+            bound["logits"].copy_(lg, non_blocking=True)
+            bound["x"].copy_(xx, non_blocking=True)
+            bound["call"].launch()
+            return bound["call"].y
     else:
         from intent_b200.distributed import ExpertParallelMoE
 
@@ -559,13 +586,16 @@ def run_moe(args, rank: int, world: int, device):
     pinned_y = torch.empty((t_local, hidden), dtype=torch.float32).pin_memory()
 
     def e2e_step():
-        y = forward(pinned_l.to(device, non_blocking=True), pinned_x.to(device, non_blocking=True))
+        if world > 1 and args.moe_exchange == "peer":
+            y = forward(pinned_l, pinned_x)
+        else:
+            y = forward(pinned_l.to(device, non_blocking=True), pinned_x.to(device, non_blocking=True))
         pinned_y.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = max(1, min(args.steps, 20))
     e2e_s = timed_e2e(e2e_step, e2e_steps, args.warmup, world, device)
-    if world > 1:
+    if world > 1 and args.moe_exchange != "peer":
         ep.check_overflow()
     flops = tokens * cfg["top_k"] * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
     ms = elapsed_ms / args.steps
@@ -577,8 +607,11 @@ def run_moe(args, rank: int, world: int, device):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "moe_w4a16_swiglu_ffn 16384 tokens H=4096 E=64 top-2 I=1408 g128 (configs[4])",
                    "parallelism": "all experts local" if world == 1 else
-                   f"expert parallel: {e_local} experts and {t_local} tokens per gpu, NCCL all-to-all each way, "
-                   "fixed-capacity exchange (factor 1.5)",
+                   (f"expert parallel: {e_local} experts and {t_local} tokens per gpu, rows written into the owners' "
+                    "buffers and results read back over NVLink peer memory (no data-path collective; one count "
+                    "all-gather and two barriers per step)" if args.moe_exchange == "peer" else
+                    f"expert parallel: {e_local} experts and {t_local} tokens per gpu, NCCL all-to-all each way, "
+                    "fixed-capacity exchange (factor 1.5)"),
                    "step": "router + alignment + gather + up|gate GEMM (SiLU) + down GEMM + combine",
                    "expert_block_rows": args.moe_block,
                    "l2": "expert weights (571 MB) and row buffers exceed the 126 MB L2"},
@@ -819,6 +852,8 @@ def main() -> int:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--moe-block", type=int, default=128, choices=[128, 256],
                         help="rows every expert span is padded to (= row tile of the grouped contraction)")
+    parser.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
+                        help="expert-parallel exchange: direct peer-memory stores/loads, or NCCL all-to-all")
     parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()
     if args.steps is None:
