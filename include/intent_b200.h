@@ -178,9 +178,10 @@ INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_bf16(INTENT_B200_GROU
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_f16(INTENT_B200_GROUPED_SLOTS);
 /* Weighted combine (the scatter_reduce add of moe.py:48-53, made order-fixed):
  * y[t,:] += sum over choices c in order of weights[t,c] * rows[route_positions[t*K + c], :]
- *   a0 rows [P,H] f32, a1 route_positions [T*K] i32, a2 weights [T,K] f32, a3 y [T,H] f32 (InOut) */
+ *   a0 rows [P,H] f32, a1 route_positions [T*K] i32, a2 weights [T,K] f32, a3 y [T,H] f32 (InOut);
+ *   accumulate = 0 starts the sum from zero instead of the old y (the caller then need not clear it) */
 INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW2(a2),
-                                            INTENT_B200_VIEW2(a3), void* stream);
+                                            INTENT_B200_VIEW2(a3), int32_t accumulate, void* stream);
 
 /* ------------------------------------------------------------------------
  * Expert-parallel exchange over peer memory (NVLink), no collective on the data path.  The caller maps
@@ -192,9 +193,11 @@ INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_V
  * ------------------------------------------------------------------------ */
 /* a0 counts [W,E] i32 (routes of every source rank to every global expert, E = W * experts per rank)
  * -> a1 dest_base [E] (first row, in the owner's buffer, of this rank's routes to expert e),
- *    a2 local_offsets [E/W + 1] (span starts of this rank's own experts; last = padded total), a3 total_padded [1] */
+ *    a2 local_offsets [E/W + 1] (span starts of this rank's own experts; last = padded total), a3 total_padded [1],
+ *    a4 expert_blocks [B] (local expert of every block_rows-row block of this rank's buffer, as moe_align.py:76-86) */
 INTENT_B200_API int intent_b200_moe_peer_layout(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
-                                                INTENT_B200_VIEW1(a3), int32_t rank, int32_t block_rows, void* stream);
+                                                INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), int32_t rank,
+                                                int32_t block_rows, void* stream);
 /* a0 x [T,H] 16-bit, a1 sorted_routes [R] (route ids grouped by expert, stable, no padding), a2 send_offsets [E+1]
  * (exclusive prefix of this rank's per-expert counts), a3 dest_base [E], a4 peer_rows [W] i64
  * -> writes row x[route / top_k] to peer_rows[owner] + position * H; a5 route_dest [R,2] = (owner, position) */
@@ -202,9 +205,11 @@ INTENT_B200_API int intent_b200_moe_peer_dispatch(INTENT_B200_VIEW2(a0), INTENT_
                                                   INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), INTENT_B200_VIEW2(a5),
                                                   int32_t top_k, int32_t capacity_rows, void* stream);
 /* a0 peer_out [W] i64, a1 route_dest [R,2], a2 weights [T,K] f32, a3 y [T,H] f32 (InOut):
- * y[t,:] += sum over choices c in order of weights[t,c] * (peer_out[owner] + position * H)[:] */
+ * y[t,:] (+)= sum over choices c in order of weights[t,c] * (peer_out[owner] + position * H)[:];
+ * accumulate = 0 starts from zero instead of the old y (the caller then need not clear it) */
 INTENT_B200_API int intent_b200_moe_peer_combine(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
-                                                 INTENT_B200_VIEW2(a3), int32_t capacity_rows, void* stream);
+                                                 INTENT_B200_VIEW2(a3), int32_t capacity_rows, int32_t accumulate,
+                                                 void* stream);
 
 /* ------------------------------------------------------------------------
  * Ragged grouped contractions with dense 16-bit weights (tcgen05 kind::f16, f32 accumulation).

@@ -20,9 +20,12 @@ namespace {
 // counts [W, E]: routes of every source rank to every global expert (E = W * experts_per_rank).
 // dest_base[e]     first row, inside the owner's buffer, of this rank's routes to expert e
 // local_offsets[l] first row of local expert l in this rank's own buffer; [EL] = padded total
+// expert_blocks[b] local expert of the b-th block_rows-row block of this rank's buffer (blocks past the
+//                  padded total are not written)
 __global__ void moe_peer_layout_kernel(const int* __restrict__ counts, int world, int experts, int experts_per_rank,
                                        int rank, int block_rows, int* __restrict__ dest_base,
-                                       int* __restrict__ local_offsets, int* __restrict__ total_padded) {
+                                       int* __restrict__ local_offsets, int* __restrict__ total_padded,
+                                       int* __restrict__ expert_blocks, int block_capacity) {
   extern __shared__ int padded[];  // [experts] padded span of every global expert
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     int total = 0;
@@ -39,6 +42,8 @@ __global__ void moe_peer_layout_kernel(const int* __restrict__ counts, int world
     dest_base[e] = offset + before;
     if (owner_first == rank * experts_per_rank) {
       local_offsets[e - owner_first] = offset;
+      for (int b = offset / block_rows; b < (offset + padded[e]) / block_rows && b < block_capacity; ++b)
+        expert_blocks[b] = e - owner_first;
       if (e - owner_first == experts_per_rank - 1) {
         local_offsets[experts_per_rank] = offset + padded[e];
         total_padded[0] = offset + padded[e];
@@ -82,10 +87,10 @@ __global__ void moe_peer_dispatch_kernel(const uint4* __restrict__ x, int row_ve
 __global__ void moe_peer_combine_kernel(const long long* __restrict__ peer_out, int world,
                                         const int* __restrict__ route_dest, const float* __restrict__ weights,
                                         int tokens, int top_k, int row_vectors, long long capacity_rows,
-                                        float4* __restrict__ y) {
+                                        bool accumulate, float4* __restrict__ y) {
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
     for (int i = threadIdx.x; i < row_vectors; i += blockDim.x) {
-      float4 acc = y[size_t(t) * row_vectors + i];
+      float4 acc = accumulate ? y[size_t(t) * row_vectors + i] : make_float4(0.f, 0.f, 0.f, 0.f);
       for (int c = 0; c < top_k; ++c) {
         const int owner = route_dest[2 * (t * top_k + c)];
         const int position = route_dest[2 * (t * top_k + c) + 1];
@@ -102,20 +107,21 @@ __global__ void moe_peer_combine_kernel(const long long* __restrict__ peer_out, 
 }  // namespace
 }  // namespace ib200
 
-// a0 counts [W,E] i32 -> a1 dest_base [E], a2 local_offsets [E/W + 1], a3 total_padded [1]
+// a0 counts [W,E] i32 -> a1 dest_base [E], a2 local_offsets [E/W + 1], a3 total_padded [1], a4 expert_blocks [B]
 extern "C" int intent_b200_moe_peer_layout(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
-                                           INTENT_B200_VIEW1(a3), int32_t rank, int32_t block_rows, void* stream) {
+                                           INTENT_B200_VIEW1(a3), INTENT_B200_VIEW1(a4), int32_t rank,
+                                           int32_t block_rows, void* stream) {
   using namespace ib200;
   const int64_t world = a0_d0, experts = a0_d1;
   if (world <= 0 || experts <= 0 || experts % world != 0 || a1_d0 != experts || a2_d0 != experts / world + 1 ||
       a3_d0 != 1 || rank < 0 || rank >= world || block_rows <= 0)
     return INTENT_B200_ERR_SHAPE;
-  if (!a0 || !a1 || !a2 || !a3) return INTENT_B200_ERR_NULL;
+  if (!a0 || !a1 || !a2 || !a3 || !a4) return INTENT_B200_ERR_NULL;
   if (!contiguous(IB200_VIEW2_ARG(a0))) return INTENT_B200_ERR_LAYOUT;
-  if (experts > 8192 || world > 1024) return INTENT_B200_ERR_UNSUPPORTED;
+  if (experts > 8192 || world > 1024 || a4_d0 > (1 << 30)) return INTENT_B200_ERR_UNSUPPORTED;
   moe_peer_layout_kernel<<<1, 256, size_t(experts) * 4, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const int*>(a0), int(world), int(experts), int(experts / world), rank, block_rows,
-      static_cast<int*>(a1), static_cast<int*>(a2), static_cast<int*>(a3));
+      static_cast<int*>(a1), static_cast<int*>(a2), static_cast<int*>(a3), static_cast<int*>(a4), int(a4_d0));
   note_launch();
   return launch_status();
 }
@@ -145,9 +151,10 @@ extern "C" int intent_b200_moe_peer_dispatch(INTENT_B200_VIEW2(a0), INTENT_B200_
 }
 
 // a0 peer_out [W] i64 (device addresses of every rank's f32 result rows [capacity_rows, H]), a1 route_dest [R,2],
-// a2 weights [T,K] f32, a3 y [T,H] f32 (InOut)
+// a2 weights [T,K] f32, a3 y [T,H] f32 (InOut; with accumulate = 0 the old contents are not read)
 extern "C" int intent_b200_moe_peer_combine(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),
-                                            INTENT_B200_VIEW2(a3), int32_t capacity_rows, void* stream) {
+                                            INTENT_B200_VIEW2(a3), int32_t capacity_rows, int32_t accumulate,
+                                            void* stream) {
   using namespace ib200;
   const int64_t world = a0_d0, tokens = a3_d0, width = a3_d1, top_k = a2_d1;
   if (world <= 0 || a2_d0 != tokens || a1_d0 != tokens * top_k || a1_d1 != 2 || capacity_rows < 0)
@@ -161,7 +168,7 @@ extern "C" int intent_b200_moe_peer_combine(INTENT_B200_VIEW1(a0), INTENT_B200_V
   const int grid = int(tokens < 148 * 16 ? tokens : 148 * 16);
   moe_peer_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const long long*>(a0), int(world), static_cast<const int*>(a1), static_cast<const float*>(a2),
-      int(tokens), int(top_k), int(width / 4), capacity_rows, static_cast<float4*>(a3));
+      int(tokens), int(top_k), int(width / 4), capacity_rows, accumulate != 0, static_cast<float4*>(a3));
   note_launch();
   return launch_status();
 }

@@ -169,10 +169,10 @@ __global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int* _
 // ---- combine: y[t, :] += sum over the token's choices, in choice order, of weight * rows[position] ----
 __global__ void moe_combine_kernel(const float4* __restrict__ rows, const int* __restrict__ position,
                                    const float* __restrict__ weights, int tokens, int top_k, int row_vectors,
-                                   float4* __restrict__ y) {
+                                   bool accumulate, float4* __restrict__ y) {
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
     for (int i = threadIdx.x; i < row_vectors; i += blockDim.x) {
-      float4 acc = y[size_t(t) * row_vectors + i];
+      float4 acc = accumulate ? y[size_t(t) * row_vectors + i] : make_float4(0.f, 0.f, 0.f, 0.f);
       for (int c = 0; c < top_k; ++c) {
         const float w = weights[t * top_k + c];
         const float4 v = rows[size_t(position[t * top_k + c]) * row_vectors + i];
@@ -289,9 +289,10 @@ extern "C" int intent_b200_moe_gather_rows(INTENT_B200_VIEW2(a0), INTENT_B200_VI
   return launch_status();
 }
 
-// rows [P,H] f32, route_positions [T*K] i32, route_weights [T,K] f32, y [T,H] f32 (InOut)
+// rows [P,H] f32, route_positions [T*K] i32, route_weights [T,K] f32, y [T,H] f32 (InOut; with
+// accumulate = 0 the sum starts from zero and the old contents of y are not read)
 extern "C" int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW2(a2),
-                                       INTENT_B200_VIEW2(a3), void* stream) {
+                                       INTENT_B200_VIEW2(a3), int32_t accumulate, void* stream) {
   if (a3_d1 != a0_d1 || a2_d0 != a3_d0 || a1_d0 != a2_d0 * a2_d1) return INTENT_B200_ERR_SHAPE;
   if (a3_d0 == 0 || a3_d1 == 0) return INTENT_B200_OK;
   if (!a0 || !a1 || !a2 || !a3) return INTENT_B200_ERR_NULL;
@@ -301,7 +302,7 @@ extern "C" int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(
   if (a3_d1 % 4 != 0) return INTENT_B200_ERR_UNSUPPORTED;
   moe_combine_kernel<<<grid_for(a3_d0, 1, 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float4*>(a0), static_cast<const int*>(a1), static_cast<const float*>(a2), int(a3_d0),
-      int(a2_d1), int(a3_d1 / 4), static_cast<float4*>(a3));
+      int(a2_d1), int(a3_d1 / 4), accumulate != 0, static_cast<float4*>(a3));
   note_launch();
   return launch_status();
 }

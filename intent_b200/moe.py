@@ -140,6 +140,7 @@ class MoEW4A16FFN:
         self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=grouped)
         self.down = _compile(programs.moe_grouped_down, target=target, constexprs=grouped)
         self.combine = _compile(programs.moe_combine, target=target)
+        self.combine_overwrite = _compile(programs.moe_combine, target=target, constexprs={"ACCUMULATE": False})
 
     def route(self, logits):
         """logits [T, E_total] f32 -> (ids [T,2] i32, weights [T,2] f32)."""
@@ -179,8 +180,8 @@ class MoEW4A16FFN:
     def prepare(self, x, topk_ids, topk_weights, up_gate_packed, up_gate_scales, down_packed, down_scales, y,
                 clear_positions=False):
         """Bind the whole chain to fixed buffers once; ``launch()`` then replays it without any
-        per-call validation or allocation (same results as :meth:`forward`).  ``y`` is zeroed by
-        every launch unless ``launch(accumulate=True)``."""
+        per-call validation or allocation (same results as :meth:`forward`).  Every launch overwrites
+        ``y`` unless ``launch(accumulate=True)``."""
         import torch
 
         align = self.alignment.prepare(topk_ids)
@@ -193,8 +194,9 @@ class MoEW4A16FFN:
         up_call = self.up_gate.prepare(gather_call.result(), expert_blocks, total, up_gate_packed, up_gate_scales)
         down_call = self.down.prepare(up_call.result(), expert_blocks, total, down_packed, down_scales)
         combine_call = self.combine.prepare(down_call.result(), positions, topk_weights, y)
-        return PreparedFFN(align, position_call, gather_call, up_call, down_call, combine_call, full_positions, y,
-                           clear_positions)
+        overwrite_call = self.combine_overwrite.prepare(down_call.result(), positions, topk_weights, y)
+        return PreparedFFN(align, position_call, gather_call, up_call, down_call, combine_call, overwrite_call,
+                           full_positions, y, clear_positions)
 
 
 @dataclass
@@ -205,6 +207,7 @@ class PreparedFFN:
     up_call: object
     down_call: object
     combine_call: object
+    overwrite_call: object
     positions: object
     y: object
     clear_positions: bool
@@ -217,7 +220,5 @@ class PreparedFFN:
         self.gather_call.launch()
         self.up_call.launch()
         self.down_call.launch()
-        if not accumulate:
-            self.y.zero_()
-        self.combine_call.launch()
+        (self.combine_call if accumulate else self.overwrite_call).launch()   # overwrite: y is not read or cleared
         return self.y

@@ -39,7 +39,6 @@ class PeerExchangeRank:
         # worst case: every route of every rank goes to this rank's experts
         self.capacity_rows = world * self.routes + self.local_experts * (block_rows - 1)
         send = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": 1}
-        own = {"TOKENS": world * self.routes, "TOP_K": 1, "EXPERTS": self.local_experts, "BLOCK_SIZE": block_rows}
         quant = {"GROUP_SIZE": group_size, "ZERO_POINT": zero_point, "ACT_DTYPE": act_dtype,
                  "BLOCK_ROWS": block_rows}
         self.router = _compile(programs.moe_route_top2, target=target)
@@ -48,15 +47,16 @@ class PeerExchangeRank:
         self.scatter = _compile(programs.moe_scatter_routes, target=target, constexprs=send)
         self.layout = _compile(programs.moe_peer_layout, target=target,
                                constexprs={"WORLD": world, "EXPERTS": experts, "RANK": rank,
-                                           "BLOCK_ROWS": block_rows})
-        self.mark = _compile(programs.moe_mark_expert_blocks, target=target, constexprs=own)
+                                           "BLOCK_ROWS": block_rows, "CAPACITY_ROWS": self.capacity_rows})
         self.dispatch = _compile(programs.moe_peer_dispatch, target=target,
                                  constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k,
                                              "CAPACITY_ROWS": self.capacity_rows})
         self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=quant)
         self.down = _compile(programs.moe_grouped_down, target=target, constexprs=quant)
         self.combine = _compile(programs.moe_peer_combine, target=target,
-                                constexprs={"CAPACITY_ROWS": self.capacity_rows})
+                                constexprs={"CAPACITY_ROWS": self.capacity_rows, "ACCUMULATE": False})
+        self.combine_add = _compile(programs.moe_peer_combine, target=target,
+                                    constexprs={"CAPACITY_ROWS": self.capacity_rows, "ACCUMULATE": True})
 
     def buffer_shapes(self):
         """(shape, torch dtype) of the row buffer and of the f32 result buffer every rank exposes."""
@@ -90,8 +90,8 @@ class PeerStep:
 
         device = x.device
         self.ep, self.y = ep, y
-        self.counts = torch.zeros((ep.experts,), dtype=torch.int32, device=device)
-        self.cursors = torch.zeros((ep.experts,), dtype=torch.int32, device=device)
+        self._counters = torch.zeros((2 * ep.experts,), dtype=torch.int32, device=device)  # cleared together
+        self.counts, self.cursors = self._counters[:ep.experts], self._counters[ep.experts:]
         self.sorted_routes = torch.empty((ep.routes,), dtype=torch.int32, device=device)
         self._router = ep.router.prepare(logits)
         self.ids, self.weights = self._router.result()
@@ -100,19 +100,17 @@ class PeerStep:
         self.send_offsets, _ = self._prefix.result()
         self._scatter = ep.scatter.prepare(self.ids, self.send_offsets, self.cursors, self.sorted_routes)
         self._layout = ep.layout.prepare(counts_all)
-        self.dest_base, self.local_offsets, self.total = self._layout.result()
-        self._mark = ep.mark.prepare(self.local_offsets)
-        self.expert_blocks = self._mark.result()
+        self.dest_base, self.local_offsets, self.total, self.expert_blocks = self._layout.result()
         self._dispatch = ep.dispatch.prepare(x, self.sorted_routes, self.send_offsets, self.dest_base, peer_rows)
         self.route_dest = self._dispatch.result()
         self._up = ep.up_gate.prepare(rows, self.expert_blocks, self.total, up_gate_packed, up_gate_scales)
         self._down = ep.down.prepare(self._up.result(), self.expert_blocks, self.total, down_packed, down_scales,
                                      outputs=(out,))
         self._combine = ep.combine.prepare(peer_out, self.route_dest, self.weights, y)
+        self._combine_add = ep.combine_add.prepare(peer_out, self.route_dest, self.weights, y)
 
     def route(self):
-        self.counts.zero_()
-        self.cursors.zero_()
+        self._counters.zero_()
         self._router.launch()
         self._count.launch()
         self._prefix.launch()
@@ -120,7 +118,6 @@ class PeerStep:
 
     def dispatch_rows(self):
         self._layout.launch()
-        self._mark.launch()
         self._dispatch.launch()
 
     def experts(self):
@@ -128,9 +125,7 @@ class PeerStep:
         self._down.launch()
 
     def combine(self, accumulate=False):
-        if not accumulate:
-            self.y.zero_()
-        self._combine.launch()
+        (self._combine_add if accumulate else self._combine).launch()
 
 
 class PeerExpertParallelMoE:

@@ -317,10 +317,11 @@ def _lower_combine(c, device):
         ViewParameter(2, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
         ViewParameter(3, "y", dtypes.f32, ("T", "H"), INOUT),
     ), dimension_rules=(_rule(lambda d: d["R"] == d["T"] * d["TOP_K"], "route_positions must have T * TOP_K entries"),))
-    return NativeProgram(interface=interface, entry_name="intent_b200_moe_combine", device=device)
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_combine",
+                         constants=(1 if c["ACCUMULATE"] else 0,), device=device)
 
 
-moe_combine = KernelDefinition("moe_combine", {}, _lower_combine,
+moe_combine = KernelDefinition("moe_combine", {"ACCUMULATE": True}, _lower_combine,
                                "examples/kernels/ragged/moe.py:48-53 (weighted scatter_reduce add)",
                                "y[t] += sum_c weight[t,c] * rows[position[t,c]] in choice order")
 
@@ -544,20 +545,23 @@ ALL.update({d.name: d for d in (gemm, bf16_gemm, quantized_gemm)})
 # ---------------------------------------------------------------------------------
 def _lower_peer_layout(c, device):
     world, experts, rank, block = (int(c[k]) for k in ("WORLD", "EXPERTS", "RANK", "BLOCK_ROWS"))
-    if world <= 0 or experts % world or not 0 <= rank < world or block <= 0:
+    capacity = int(c["CAPACITY_ROWS"])
+    if world <= 0 or experts % world or not 0 <= rank < world or block <= 0 or capacity < 0:
         raise CompilationStageError("frontend_kir", "EXPERTS must be a multiple of WORLD and 0 <= RANK < WORLD")
     interface = PublicInterface((
         ViewParameter(0, "counts", dtypes.i32, (world, experts), IN, alignment=4),
         ViewParameter(1, "dest_base", dtypes.i32, (experts,), OUT, alignment=4),
         ViewParameter(2, "local_offsets", dtypes.i32, (experts // world + 1,), OUT, alignment=4),
         ViewParameter(3, "total_padded", dtypes.i32, (1,), OUT, alignment=4),
+        ViewParameter(4, "expert_blocks", dtypes.i32, (capacity // block + 1,), OUT, alignment=4),
     ))
     return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_layout", constants=(rank, block),
                          device=device)
 
 
 moe_peer_layout = KernelDefinition(
-    "moe_peer_layout", {"WORLD": 1, "EXPERTS": 64, "RANK": 0, "BLOCK_ROWS": 128}, _lower_peer_layout,
+    "moe_peer_layout", {"WORLD": 1, "EXPERTS": 64, "RANK": 0, "BLOCK_ROWS": 128, "CAPACITY_ROWS": 0},
+    _lower_peer_layout,
     "examples/kernels/routing/moe_align.py:32-49 (padded offsets), over the ranks' count matrix",
     "where this rank's routes start inside every owner's expert-sorted row buffer")
 
@@ -595,12 +599,12 @@ def _lower_peer_combine(c, device):
         ViewParameter(2, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
         ViewParameter(3, "y", dtypes.f32, ("T", "H"), INOUT),
     ), dimension_rules=(_rule(lambda d: d["R"] == d["T"] * d["TOP_K"], "route_dest must have T * TOP_K rows"),))
-    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_combine", constants=(capacity,),
-                         device=device)
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_combine",
+                         constants=(capacity, 1 if c["ACCUMULATE"] else 0), device=device)
 
 
 moe_peer_combine = KernelDefinition(
-    "moe_peer_combine", {"CAPACITY_ROWS": 0}, _lower_peer_combine,
+    "moe_peer_combine", {"CAPACITY_ROWS": 0, "ACCUMULATE": True}, _lower_peer_combine,
     "examples/kernels/ragged/moe.py:48-53 (weighted scatter_reduce add), reading the owners' result rows",
     "y[t] += sum_c weight[t,c] * out[owner(t,c)][position(t,c)] over peer memory")
 
