@@ -62,5 +62,47 @@ def compile(definition: KernelDefinition, *, target: B200Target | None = None,
     description = (f"// {definition.name}  [{definition.reference}]\n"
                    f"// provider: b200 (prebuilt sm_100a), entry: {program.entry_name}\n"
                    f"// constexprs: {constants}\n")
-    return CompiledArtifact(source=description, mlir=description, device=target.device, runtime=program,
-                            device_type=target.device_type)
+    artifact = CompiledArtifact(source=description, mlir=description, device=target.device, runtime=program,
+                                device_type=target.device_type)
+    artifact.metadata = {"provider": "b200", "program": definition.name, "entry_name": program.entry_name,
+                         "constexprs": {k: _plain(v) for k, v in constants.items()},
+                         "reference": definition.reference,
+                         "parameters": [p.name for p in program.interface.parameters]}
+    return artifact
+
+
+def _plain(value):
+    """Compile-time constants as JSON values (enum members by name)."""
+    if isinstance(value, (bool, int, float, str)) or value is None:
+        return value
+    return getattr(value, "name", str(value))
+
+
+def load(directory, *, target: B200Target | None = None, resolve_target: bool = True) -> CompiledArtifact:
+    """Rebuild an artifact from a directory written by ``CompiledArtifact.save``: the stored program
+    id and compile-time constants select the prebuilt entry again and bind it to ``target``.  Stands
+    where ``GeneratedProgram.load(...).materialize(target=...)`` stands in the reference
+    (python/intent/compiler/artifact.py:131-177); no native code is stored in the directory."""
+    import json
+    from pathlib import Path
+
+    from . import programs
+
+    path = Path(directory).expanduser().absolute()
+    try:
+        source = (path / "kernel.source").read_text(encoding="utf-8")
+        metadata = json.loads((path / "artifact.json").read_text(encoding="utf-8"))
+        if not source.strip() or not isinstance(metadata, dict):
+            raise ValueError("a saved program needs nonempty source and object metadata")
+        if metadata.get("provider") != "b200":
+            raise ValueError(f"artifact was written by provider {metadata.get('provider')!r}, not 'b200'")
+        definition = programs.ALL[metadata["program"]]
+        constants = metadata["constexprs"]
+        if not isinstance(constants, dict):
+            raise TypeError("constexprs must be an object")
+    except (OSError, UnicodeError, ValueError, KeyError, TypeError) as error:
+        raise CompilationStageError("generated_program_loading", f"{type(error).__name__}: {error}",
+                                    cache_directory=path) from error
+    artifact = compile(definition, target=target, constexprs=constants, resolve_target=resolve_target)
+    artifact.cache_directory = path
+    return artifact

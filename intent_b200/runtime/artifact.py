@@ -224,6 +224,36 @@ class CompiledArtifact:
     cache_directory: Path | None = field(default=None, kw_only=True)
     backend_ir: dict = field(default_factory=dict, init=False)
 
+    metadata: dict = field(default_factory=dict, init=False, repr=False)
+
+    def save(self, directory) -> Path:
+        """Write ``kernel.source``, ``kernel.mlir`` and ``artifact.json`` into a new directory (the
+        reference's artifact layout, python/intent/compiler/artifact.py:105-129).  The device binding
+        and native handles are not stored; ``intent_b200.load`` binds the program again."""
+        import json
+        import tempfile
+
+        from ..errors import CompilationStageError
+
+        path = Path(directory).expanduser().absolute()
+        try:
+            if path.exists():
+                raise FileExistsError(f"generated program destination already exists: {path}")
+            if not self.metadata:
+                raise ValueError("this artifact was not produced by intent_b200.compile")
+            path.parent.mkdir(parents=True, exist_ok=True)
+            with tempfile.TemporaryDirectory(prefix=f".{path.name}-", dir=path.parent) as temporary:
+                staging = Path(temporary) / "program"
+                staging.mkdir()
+                (staging / "kernel.source").write_text(self.source, encoding="utf-8")
+                (staging / "kernel.mlir").write_text(self.mlir, encoding="utf-8")
+                (staging / "artifact.json").write_text(json.dumps(self.metadata, indent=2) + "\n", encoding="utf-8")
+                staging.rename(path)
+        except (OSError, UnicodeError, TypeError, ValueError) as error:
+            raise CompilationStageError("generated_program_export", str(error),
+                                        cache_directory=self.cache_directory) from error
+        return path
+
     @property
     def observation(self):
         """Latest native invocation snapshot, or None before the first launch."""

@@ -160,3 +160,24 @@ def test_dense_grouped_declarations():
         routed.interface.bind((x.half(), offsets, members, w), device=CPU)
     with pytest.raises(TypeError):
         ffn.interface.bind((x.half(),), device=CPU)
+
+
+# ---- artifact persistence (the reference's save / load / materialize) ------------------------------
+def test_artifact_save_and_load(tmp_path):
+    artifact = ib.compile(ib.programs.weight_only_int4_matmul, resolve_target=False,
+                          constexprs={"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16"})
+    path = artifact.save(tmp_path / "w4a16")
+    assert sorted(p.name for p in path.iterdir()) == ["artifact.json", "kernel.mlir", "kernel.source"]
+    restored = ib.load(path, resolve_target=False)
+    assert restored.metadata == artifact.metadata and restored.cache_directory == path
+    assert [p.name for p in restored.interface.parameters] == [p.name for p in artifact.interface.parameters]
+    assert restored.runtime.entry_name == artifact.runtime.entry_name == "intent_b200_weight_only_int4_matmul_bf16"
+    with pytest.raises(ib.CompilationStageError) as error:
+        artifact.save(path)                                   # the destination must be new
+    assert error.value.stage == "generated_program_export"
+    (path / "artifact.json").write_text('{"provider": "other"}')
+    with pytest.raises(ib.CompilationStageError) as error:
+        ib.load(path, resolve_target=False)
+    assert error.value.stage == "generated_program_loading"
+    with pytest.raises(ib.CompilationStageError):
+        ib.load(tmp_path / "missing", resolve_target=False)
