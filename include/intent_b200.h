@@ -292,6 +292,14 @@ INTENT_B200_API int intent_b200_dequant_bf16_fp4_matmul(INTENT_B200_VIEW2(a0), I
                                                         INTENT_B200_VIEW2(a2), void* workspace,
                                                         int64_t workspace_bytes, void* stream);
 
+/* quantized_projection (examples/kernels/quantization/quantized_projection.py:5-19; record formats and
+ * rounding order doc/dsl/quantized-operations.en.md sections 2-4): a0 weights u8 [N,G,144] (Q4_K records),
+ * a1 activation f32 [G,256] -> a2 output f32 [N].  The activation is quantized to Q8_K records inside the
+ * call; workspace >= G*292 bytes rounded up to 256, not cleared. */
+INTENT_B200_API int intent_b200_quantized_projection(INTENT_B200_VIEW3(a0), INTENT_B200_VIEW2(a1),
+                                                     INTENT_B200_VIEW1(a2), void* workspace,
+                                                     int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.
  * This entry has no counterpart in the reference.  It exists for callers that

@@ -8,7 +8,8 @@
 // Each program decodes the packed operand once into a K-major workspace (a bandwidth-bound
 // pass: it reads the packed bytes and writes 2x / 4x / 4x as many) and then runs the dense
 // tcgen05 kernel on it (kind::i8 with exact s32 accumulation, or kind::f16 on bf16).  The
-// integer programs are bit-exact with wrapping int32 arithmetic.
+// integer programs are bit-exact with wrapping int32 arithmetic.  The int2 program with at most 16
+// activation rows (decode) skips both: a dp4a GEMV reads the packed weights once.
 #include "common.cuh"
 #include "dense.cuh"
 
@@ -79,6 +80,47 @@ __global__ void expand_fp4_kernel(const uint32_t* __restrict__ packed, uint4* __
   }
 }
 
+// Few activation rows (decode): no decode pass and no tensor core.  One warp per weight row n walks
+// the packed row once; (word >> 2L) & 0x03030303 are the four values 16j + 4L .. + 3 as bytes, which
+// meet the four activation bytes of the same k in one dp4a.  Exact int32 arithmetic.
+template <int ROWS>
+__global__ void int2_gemv_kernel(const int8_t* __restrict__ activation, const uint32_t* __restrict__ packed,
+                                 int32_t* __restrict__ out, int M, int N, int K) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int words = K >> 4;  // 16 values per packed word
+  for (int n = warp; n < N; n += warps) {
+    const uint32_t* row = packed + size_t(n) * words;
+    for (int m0 = 0; m0 < M; m0 += ROWS) {
+      int acc[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) acc[r] = 0;
+      for (int j = lane; j < words; j += 32) {
+        const uint32_t w = __ldg(row + j);
+        const uint32_t v0 = w & 0x03030303u, v1 = (w >> 2) & 0x03030303u, v2 = (w >> 4) & 0x03030303u,
+                       v3 = (w >> 6) & 0x03030303u;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          if (m0 + r < M) {
+            const int4 a = __ldg(reinterpret_cast<const int4*>(activation + size_t(m0 + r) * K) + j);
+            acc[r] = __dp4a(int(v0), a.x, acc[r]);
+            acc[r] = __dp4a(int(v1), a.y, acc[r]);
+            acc[r] = __dp4a(int(v2), a.z, acc[r]);
+            acc[r] = __dp4a(int(v3), a.w, acc[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], d);
+        if (lane == 0 && m0 + r < M) out[size_t(m0 + r) * N + n] = acc[r];
+      }
+    }
+  }
+}
+
 inline int grid_for(int64_t items, int threads) {
   const int64_t blocks = (items + threads - 1) / threads;
   return int(blocks < 148 * 8 ? (blocks > 0 ? blocks : 1) : 148 * 8);
@@ -130,6 +172,18 @@ extern "C" int intent_b200_bitnet_int2_matmul(INTENT_B200_VIEW2(a0), INTENT_B200
   int status = check_views(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2));
   if (status != INTENT_B200_OK) return status;
   if (K == 0 || K % 16 != 0 || N % 16 != 0) return INTENT_B200_ERR_UNSUPPORTED;
+  if (M <= 16) {  // decode: one pass over the packed weights
+    const int64_t warps_needed = N;
+    const int blocks = int(warps_needed / 8 < 148 * 8 ? (warps_needed + 7) / 8 : 148 * 8);
+    if (M <= 4)
+      int2_gemv_kernel<4><<<blocks, 256, 0, stream>>>(static_cast<const int8_t*>(a0), static_cast<const uint32_t*>(a1),
+                                                     static_cast<int32_t*>(a2), int(M), int(N), int(K));
+    else
+      int2_gemv_kernel<8><<<blocks, 256, 0, stream>>>(static_cast<const int8_t*>(a0), static_cast<const uint32_t*>(a1),
+                                                     static_cast<int32_t*>(a2), int(M), int(N), int(K));
+    note_launch();
+    return launch_status();
+  }
   if (!workspace || !aligned16(workspace) || workspace_bytes < align256(N * K)) return INTENT_B200_ERR_WORKSPACE;
   const int64_t words = N * P / 4;
   expand_int2_kernel<<<grid_for(words, 256), 256, 0, stream>>>(static_cast<const uint32_t*>(a1),

@@ -609,3 +609,24 @@ moe_peer_combine = KernelDefinition(
     "y[t] += sum_c weight[t,c] * out[owner(t,c)][position(t,c)] over peer memory")
 
 ALL.update({d.name: d for d in (moe_peer_layout, moe_peer_dispatch, moe_peer_combine)})
+
+
+# ---------------------------------------------------------------------------------
+# Q4_K x Q8_K quantized projection (a second bandwidth-bound GEMV format)
+# ---------------------------------------------------------------------------------
+def _lower_quantized_projection(c, device):
+    interface = PublicInterface((
+        ViewParameter(0, "weights", dtypes.u8, ("N", "G", 144), IN),
+        ViewParameter(1, "activation", dtypes.f32, ("G", 256), IN),
+        ViewParameter(2, "output", dtypes.f32, ("N",), OUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_quantized_projection", device=device,
+                         workspace=lambda d: _align256(d["G"] * 292), empty=lambda d: d["N"] == 0)
+
+
+quantized_projection = KernelDefinition(
+    "quantized_projection", {}, _lower_quantized_projection,
+    "examples/kernels/quantization/quantized_projection.py:5-19",
+    "out[n] = sum over records of quantized_dot(Q4_K weights[n], Q8_K(activation))")
+
+ALL.update({quantized_projection.name: quantized_projection})

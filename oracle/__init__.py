@@ -51,3 +51,9 @@ from .packed import (  # noqa: F401
     unpack_w4a8,
     w4a8_packed_matmul,
 )
+from .quantized import (  # noqa: F401
+    q4_k_fields,
+    q8_k_quantize,
+    quantized_dot,
+    quantized_projection,
+)

@@ -176,3 +176,44 @@ def test_quantized_gemm_matches_reference():
     g = load_golden("quantized_gemm_small")
     out = oracle.quantized_gemm(g["a"], g["b"], g["bias"], g["residual"], g["scale"])
     assert out.dtype == torch.int8 and torch.equal(out, g["output"])
+
+
+# ---- Q4_K x Q8_K: no reference vectors exist; check the restatement against the published contract ----
+def test_q8_k_quantize_contract():
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    values = rng.standard_normal((5, 256)).astype(np.float32)
+    values[1] = 0.0
+    values[2] = np.clip(values[2], -1.25, 1.25)
+    values[2, 7], values[2, 9] = -1.5, 1.5              # tie between the extremes: the minimum wins
+    records = oracle.q8_k_quantize(values)
+    assert records.shape == (5, 292) and records.dtype == np.uint8
+    ds = records[:, 0:4].copy().view("<f4")[:, 0]
+    q = records[:, 4:260].view(np.int8)
+    bsum = records[:, 260:292].copy().view("<i2")
+    assert np.array_equal(bsum, q.astype(np.int16).reshape(5, 16, 16).sum(axis=2))   # the data contract
+    assert ds[1] == 0 and not q[1].any() and not bsum[1].any()
+    assert ds[2] > 0 and q[2, 7] == -127 and q[2, 9] == 127              # -127 / (negative extreme) > 0
+    assert np.abs(q * ds[:, None] - values).max() <= np.abs(ds).max() * 0.5 + 1e-6
+
+
+def test_quantized_dot_matches_dequantised_dot():
+    import numpy as np
+
+    rng = np.random.default_rng(1)
+    weights = rng.integers(0, 256, (3, 2, 144), dtype=np.uint8)
+    weights[:, :, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+    weights[:, :, 2:4] = np.frombuffer(np.float16(0.02).tobytes(), dtype=np.uint8)
+    activation = rng.standard_normal((2, 256)).astype(np.float32)
+    records = oracle.q8_k_quantize(activation)
+    ds = records[:, 0:4].copy().view("<f4")[:, 0].astype(np.float64)
+    xq = records[:, 4:260].view(np.int8).astype(np.float64) * ds[:, None]
+    for row in weights:
+        expected = 0.0
+        for g in range(2):
+            d, dmin, sc, m, wq = oracle.q4_k_fields(row[g])
+            dequantised = np.concatenate([float(d) * sc[s] * wq[32 * s:32 * s + 32] - float(dmin) * m[s]
+                                          for s in range(8)])
+            expected += dequantised @ xq[g]
+        assert abs(float(oracle.quantized_dot(row, records)) - expected) <= 1e-4 * max(1.0, abs(expected))
