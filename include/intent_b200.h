@@ -191,6 +191,17 @@ INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_V
  * results written before any rank combines).  No kernel waits on another GPU.
  * Owner layout: local experts in order, spans padded to block_rows; inside a span source rank 0 first.
  * ------------------------------------------------------------------------ */
+/* Cross-rank sync points without a collective: every rank owns a flag array [channels, W] i32 that all ranks can
+ * address.  post bumps this rank's sequence number of the channel, optionally copies a small payload (a3, C ints)
+ * into row `rank` of every rank's table [W, C] (a2: their addresses; extent 0 = no payload), fences, and stores the
+ * number into slot [channel][rank] of every rank's flag array (a0: their addresses).  wait returns when every slot
+ * [channel][*] of this rank's own array (a0) has reached this rank's number; it gives up after max_polls polls
+ * (200 ns apart) and then writes INTENT_B200_ERR_TIMEOUT into a2 status[0] instead of hanging.
+ * a1 sequence [2 * channels] i32 is private to the rank (post and wait counters), zero before the first use. */
+INTENT_B200_API int intent_b200_moe_peer_post(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                              INTENT_B200_VIEW1(a3), int32_t rank, int32_t channel, void* stream);
+INTENT_B200_API int intent_b200_moe_peer_wait(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                              int32_t channel, int32_t max_polls, void* stream);
 /* a0 counts [W,E] i32 (routes of every source rank to every global expert, E = W * experts per rank)
  * -> a1 dest_base [E] (first row, in the owner's buffer, of this rank's routes to expert e),
  *    a2 local_offsets [E/W + 1] (span starts of this rank's own experts; last = padded total), a3 total_padded [1],

@@ -104,8 +104,89 @@ __global__ void moe_peer_combine_kernel(const long long* __restrict__ peer_out, 
   }
 }
 
+// ---- cross-rank signalling over peer memory ---------------------------------------------------
+// Every rank owns a flag array [channels][W] in memory all ranks can address.  To pass a sync
+// point a rank first POSTS: it bumps its private sequence number of the channel, optionally copies a
+// small payload (its per-expert counts) into every rank's table, fences, and stores the sequence
+// number into slot [channel][rank] of every rank's flag array.  It then WAITS until every slot of
+// its own array [channel][*] has reached the same number.  Sequence numbers only grow, so a rank
+// that runs ahead never confuses a slower one.  The wait is bounded: after `max_polls` polls it
+// records INTENT_B200_ERR_TIMEOUT in `status` and returns, so a missing rank cannot hang the GPU.
+__global__ void moe_peer_post_kernel(const long long* __restrict__ peer_flags, int world, int rank, int channel,
+                                     int* __restrict__ sequence, const long long* __restrict__ peer_tables,
+                                     const int* __restrict__ payload, int payload_count) {
+  __shared__ int seq;
+  if (threadIdx.x == 0) seq = ++sequence[2 * channel];   // launches of one stream are ordered: no race
+  if (peer_tables != nullptr)
+    for (int i = threadIdx.x; i < world * payload_count; i += blockDim.x) {
+      const int dst = i / payload_count, e = i - dst * payload_count;
+      reinterpret_cast<int*>(peer_tables[dst])[rank * payload_count + e] = payload[e];
+    }
+  __threadfence_system();
+  __syncthreads();
+  for (int dst = threadIdx.x; dst < world; dst += blockDim.x) {
+    int* flag = reinterpret_cast<int*>(peer_flags[dst]) + channel * world + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+  }
+}
+
+__global__ void moe_peer_wait_kernel(const int* __restrict__ my_flags, int world, int channel,
+                                     int* __restrict__ sequence, int max_polls, int* __restrict__ status) {
+  __shared__ int seq;
+  if (threadIdx.x == 0) seq = ++sequence[2 * channel + 1];
+  __syncthreads();
+  for (int src = threadIdx.x; src < world; src += blockDim.x) {
+    const int* flag = my_flags + channel * world + src;
+    bool seen = false;
+    for (int poll = 0; poll < max_polls; ++poll) {
+      int value;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(value) : "l"(flag) : "memory");
+      if (value - seq >= 0) { seen = true; break; }
+      __nanosleep(200);
+    }
+    if (!seen) atomicExch(status, INTENT_B200_ERR_TIMEOUT);
+  }
+  __threadfence_system();
+}
+
 }  // namespace
 }  // namespace ib200
+
+// a0 peer_flags [W] i64 (device addresses of every rank's flag array [channels, W] i32), a1 sequence [2*channels] i32
+// (private to this rank; a post counter and a wait counter per channel), a2 peer_tables [W] i64 and a3 payload [C] i32:
+// optional payload copied into row `rank` of every rank's table [W, C] (pass a2 with extent 0 for none)
+extern "C" int intent_b200_moe_peer_post(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                         INTENT_B200_VIEW1(a3), int32_t rank, int32_t channel, void* stream) {
+  using namespace ib200;
+  const int64_t world = a0_d0;
+  if (world <= 0 || rank < 0 || rank >= world || channel < 0 || a1_d0 < 2 * (channel + 1) ||
+      (a2_d0 != 0 && a2_d0 != world))
+    return INTENT_B200_ERR_SHAPE;
+  if (!a0 || !a1 || (a2_d0 != 0 && (!a2 || !a3))) return INTENT_B200_ERR_NULL;
+  if (world > 1024 || a3_d0 > 8192) return INTENT_B200_ERR_UNSUPPORTED;
+  moe_peer_post_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(a0), int(world), rank, channel, static_cast<int*>(a1),
+      a2_d0 != 0 ? static_cast<const long long*>(a2) : nullptr, static_cast<const int*>(a3), int(a3_d0));
+  note_launch();
+  return launch_status();
+}
+
+// a0 my_flags [channels, W] i32 (this rank's own flag array), a1 sequence [2*channels] i32, a2 status [1] i32
+// (set to INTENT_B200_ERR_TIMEOUT when a slot did not reach the sequence number within max_polls polls)
+extern "C" int intent_b200_moe_peer_wait(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
+                                         int32_t channel, int32_t max_polls, void* stream) {
+  using namespace ib200;
+  const int64_t world = a0_d1;
+  if (world <= 0 || channel < 0 || channel >= a0_d0 || a1_d0 < 2 * (channel + 1) || a2_d0 < 1 || max_polls <= 0)
+    return INTENT_B200_ERR_SHAPE;
+  if (!a0 || !a1 || !a2) return INTENT_B200_ERR_NULL;
+  if (!contiguous(IB200_VIEW2_ARG(a0))) return INTENT_B200_ERR_LAYOUT;
+  if (world > 1024) return INTENT_B200_ERR_UNSUPPORTED;
+  moe_peer_wait_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int*>(a0), int(world), channel, static_cast<int*>(a1), max_polls, static_cast<int*>(a2));
+  note_launch();
+  return launch_status();
+}
 
 // a0 counts [W,E] i32 -> a1 dest_base [E], a2 local_offsets [E/W + 1], a3 total_padded [1], a4 expert_blocks [B]
 extern "C" int intent_b200_moe_peer_layout(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),

@@ -128,12 +128,52 @@ class PeerStep:
         (self._combine_add if accumulate else self._combine).launch()
 
 
+class PeerSignals:
+    """One rank's sync points over peer memory: ``flags`` [3, world] is this rank's flag array,
+    ``peer_flags`` the int64 table of every rank's array, ``peer_tables`` the table of every rank's count
+    matrix.  Channel 0 carries the per-expert counts, channels 1 and 2 are plain barriers.  The waits are
+    bounded; ``status`` holds a timeout code if one gave up."""
+
+    CHANNELS = 3
+
+    def __init__(self, *, rank, world, flags, peer_flags, peer_tables, counts, target=None, max_polls=1 << 21):
+        import torch
+
+        device = flags.device
+        self.flags, self.status = flags, torch.zeros((1,), dtype=torch.int32, device=device)
+        self.sequence = torch.zeros((2 * self.CHANNELS,), dtype=torch.int32, device=device)
+        none = torch.empty((0,), dtype=torch.int64, device=device)
+        self.posts, self.waits = [], []
+        for channel in range(self.CHANNELS):
+            post = _compile(programs.moe_peer_post, target=target,
+                            constexprs={"RANK": rank, "CHANNEL": channel, "PAYLOAD": channel == 0})
+            wait = _compile(programs.moe_peer_wait, target=target,
+                            constexprs={"CHANNEL": channel, "MAX_POLLS": max_polls})
+            self.posts.append(post.prepare(peer_flags, self.sequence, peer_tables if channel == 0 else none, counts))
+            self.waits.append(wait.prepare(flags, self.sequence, self.status))
+
+    def post(self, channel):
+        self.posts[channel].launch()
+
+    def wait(self, channel):
+        self.waits[channel].launch()
+
+    def check(self):
+        """Raise if a wait has given up since the last check (reads one device word)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"a cross-rank wait expired (status {code}): a rank did not reach the sync point")
+
+
 class PeerExpertParallelMoE:
-    """``PeerExchangeRank`` bound to a process group: symmetric-memory buffers, an all-gather of the
-    per-expert route counts and two barriers per step, all on the current stream."""
+    """``PeerExchangeRank`` bound to a process group: symmetric-memory buffers and three sync points per
+    step (the first one carries the per-expert route counts), all on the current stream.
+    ``signals='peer'``: the sync points are flag writes and bounded flag waits over peer memory;
+    ``signals='nccl'``: an all-gather and two one-word all-reduces."""
 
     def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
-                 act_dtype="bf16", block_rows=128, target=None, group=None):
+                 act_dtype="bf16", block_rows=128, target=None, group=None, signals="peer"):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symmetric
@@ -156,9 +196,32 @@ class PeerExpertParallelMoE:
         self._peer_out = [out_handle.get_buffer(r, out_shape, out_dtype) for r in range(self.world)]
         self.peer_rows = torch.tensor([t.data_ptr() for t in self._peer_rows], dtype=torch.int64, device=device)
         self.peer_out = torch.tensor([t.data_ptr() for t in self._peer_out], dtype=torch.int64, device=device)
-        self.counts_all = torch.zeros((self.world, experts), dtype=torch.int32, device=device)
+        if signals not in ("peer", "nccl"):
+            raise ValueError("signals must be 'peer' or 'nccl'")
+        self.signals = signals
         self._token = torch.zeros((1,), dtype=torch.int32, device=device)
         self._dist = dist
+        self._target = target
+        if signals == "nccl":
+            self.counts_all = torch.zeros((self.world, experts), dtype=torch.int32, device=device)
+        else:
+            self.counts_all = symmetric.empty((self.world, experts), dtype=torch.int32, device=device)
+            self.flags = symmetric.empty((PeerSignals.CHANNELS, self.world), dtype=torch.int32, device=device)
+            self.counts_all.zero_()
+            self.flags.zero_()
+            counts_handle = symmetric.rendezvous(self.counts_all, self.group)
+            flags_handle = symmetric.rendezvous(self.flags, self.group)
+            self._peer_counts = [counts_handle.get_buffer(r, tuple(self.counts_all.shape), torch.int32)
+                                 for r in range(self.world)]
+            self._peer_flags = [flags_handle.get_buffer(r, tuple(self.flags.shape), torch.int32)
+                                for r in range(self.world)]
+            self.peer_counts = torch.tensor([t.data_ptr() for t in self._peer_counts], dtype=torch.int64,
+                                            device=device)
+            self.peer_flags = torch.tensor([t.data_ptr() for t in self._peer_flags], dtype=torch.int64,
+                                           device=device)
+        # every rank's buffers are cleared before any rank may write into them
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
 
     def barrier(self):
         self._dist.all_reduce(self._token, group=self.group)
@@ -171,7 +234,11 @@ class PeerExpertParallelMoE:
         step = self.side.prepare(logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales, y,
                                  rows=self.rows, out=self.out, peer_rows=self.peer_rows, peer_out=self.peer_out,
                                  counts_all=self.counts_all)
-        return PreparedPeerStep(self, step)
+        signals = None
+        if self.signals == "peer":
+            signals = PeerSignals(rank=self.rank, world=self.world, flags=self.flags, peer_flags=self.peer_flags,
+                                  peer_tables=self.peer_counts, counts=step.counts, target=self._target)
+        return PreparedPeerStep(self, step, signals)
 
     def __call__(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):
         call = self.prepare(logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales)
@@ -180,15 +247,28 @@ class PeerExpertParallelMoE:
 
 
 class PreparedPeerStep:
-    def __init__(self, ep: PeerExpertParallelMoE, step: PeerStep):
-        self.ep, self.step, self.y = ep, step, step.y
+    def __init__(self, ep: PeerExpertParallelMoE, step: PeerStep, signals: PeerSignals | None = None):
+        self.ep, self.step, self.y, self.signals = ep, step, step.y, signals
+
+    def _sync(self, channel):
+        if self.signals is not None:
+            self.signals.post(channel)
+            self.signals.wait(channel)
+        elif channel == 0:
+            self.ep._dist.all_gather_into_tensor(self.ep.counts_all.view(-1), self.step.counts, group=self.ep.group)
+        else:
+            self.ep.barrier()
 
     def launch(self, accumulate=False):
-        ep, step = self.ep, self.step
+        step = self.step
         step.route()
-        ep._dist.all_gather_into_tensor(ep.counts_all.view(-1), step.counts, group=ep.group)
+        self._sync(0)         # every rank's per-expert counts are in every rank's count matrix
         step.dispatch_rows()
-        ep.barrier()          # every row of this step is in its owner's buffer
+        self._sync(1)         # every row of this step is in its owner's buffer
         step.experts()
-        ep.barrier()          # every result row is written; also fences the row buffers for the next step
+        self._sync(2)         # every result row is written; also fences the row buffers for the next step
         step.combine(accumulate)
+
+    def check(self):
+        if self.signals is not None:
+            self.signals.check()

@@ -630,3 +630,38 @@ quantized_projection = KernelDefinition(
     "out[n] = sum over records of quantized_dot(Q4_K weights[n], Q8_K(activation))")
 
 ALL.update({quantized_projection.name: quantized_projection})
+
+
+def _lower_peer_post(c, device):
+    rank, channel, payload = int(c["RANK"]), int(c["CHANNEL"]), bool(c["PAYLOAD"])
+    interface = PublicInterface((
+        ViewParameter(0, "peer_flags", dtypes.i64, ("W",), IN, alignment=8),
+        ViewParameter(1, "sequence", dtypes.i32, ("S",), INOUT, alignment=4),
+        ViewParameter(2, "peer_tables", dtypes.i64, ("W",) if payload else (0,), IN, alignment=8),
+        ViewParameter(3, "payload", dtypes.i32, ("C",), IN, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_post", constants=(rank, channel),
+                         device=device)
+
+
+def _lower_peer_wait(c, device):
+    channel, polls = int(c["CHANNEL"]), int(c["MAX_POLLS"])
+    interface = PublicInterface((
+        ViewParameter(0, "flags", dtypes.i32, ("CHANNELS", "W"), IN, alignment=4),
+        ViewParameter(1, "sequence", dtypes.i32, ("S",), INOUT, alignment=4),
+        ViewParameter(2, "status", dtypes.i32, (1,), INOUT, alignment=4),
+    ))
+    return NativeProgram(interface=interface, entry_name="intent_b200_moe_peer_wait", constants=(channel, polls),
+                         device=device)
+
+
+moe_peer_post = KernelDefinition(
+    "moe_peer_post", {"RANK": 0, "CHANNEL": 0, "PAYLOAD": False}, _lower_peer_post,
+    "no counterpart in the reference (it has no multi-GPU path)",
+    "announce this rank at a sync point (optionally with its per-expert counts) in every rank's flag array")
+moe_peer_wait = KernelDefinition(
+    "moe_peer_wait", {"CHANNEL": 0, "MAX_POLLS": 1 << 21}, _lower_peer_wait,
+    "no counterpart in the reference (it has no multi-GPU path)",
+    "bounded wait until every rank has announced itself at the sync point")
+
+ALL.update({d.name: d for d in (moe_peer_post, moe_peer_wait)})

@@ -52,18 +52,42 @@ def test_peer_exchange_emulated_ranks(cuda_device, world, tokens, hidden, inter,
         ys.append(y)
         steps.append(side.prepare(logits, x, *w, y, rows=rows[r], out=out[r], peer_rows=peer_rows,
                                   peer_out=peer_out, counts_all=counts_all))
+    # the ranks' sync points: every rank has its own flag array and its own view of the count matrix
+    from intent_b200.peer import PeerSignals
+
+    flags = [torch.zeros((PeerSignals.CHANNELS, world), dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    tables = [counts_all] + [torch.zeros_like(counts_all) for _ in range(world - 1)]   # rank 0's is the bound one
+    peer_flags = torch.tensor([t.data_ptr() for t in flags], dtype=torch.int64, device=cuda_device)
+    peer_tables = torch.tensor([t.data_ptr() for t in tables], dtype=torch.int64, device=cuda_device)
+    signals = [PeerSignals(rank=r, world=world, flags=flags[r], peer_flags=peer_flags, peer_tables=peer_tables,
+                           counts=steps[r].counts, target=target) for r in range(world)]
     for repeat in range(2):          # the second pass runs over buffers that hold the first pass's rows
         for step in steps:
             step.route()
-        for r, step in enumerate(steps):
-            counts_all[r].copy_(step.counts)
+        if repeat == 0:              # counts by hand
+            for r, step in enumerate(steps):
+                counts_all[r].copy_(step.counts)
+        else:                        # counts through the signalling kernels: all ranks post, then all wait
+            counts_all.zero_()
+            for s in signals:
+                s.post(0)
+            for s in signals:
+                s.wait(0)
+            assert all(torch.equal(t, counts_all) for t in tables)
         for step in steps:
             step.dispatch_rows()
+        for channel in (1, 2):
+            for s in signals:
+                s.post(channel)
+            for s in signals:
+                s.wait(channel)
         for step in steps:
             step.experts()
         for step in steps:
             step.combine()
         torch.cuda.synchronize()
+        for s in signals:
+            s.check()
         assert torch.equal(torch.cat(ys), expected), f"pass {repeat}"
     # every route was placed: owners and positions are in range, positions are unique per owner
     placed = torch.cat([s.route_dest for s in steps]).cpu()
@@ -71,6 +95,36 @@ def test_peer_exchange_emulated_ranks(cuda_device, world, tokens, hidden, inter,
     keys = placed[:, 0].long() * sides[0].capacity_rows + placed[:, 1].long()
     assert keys.unique().numel() == keys.numel()
     assert int(counts_all.sum()) == tokens * 2
+
+
+def test_peer_wait_gives_up(cuda_device):
+    """A sync point that one rank never reaches: the wait must return with a timeout status instead of
+    hanging (a flag that nothing sets; the context stays usable)."""
+    from intent_b200.peer import PeerSignals
+
+    world = 2
+    flags = torch.zeros((PeerSignals.CHANNELS, world), dtype=torch.int32, device=cuda_device)
+    other = torch.zeros_like(flags)
+    peer_flags = torch.tensor([flags.data_ptr(), other.data_ptr()], dtype=torch.int64, device=cuda_device)
+    table = torch.zeros((world, 8), dtype=torch.int32, device=cuda_device)
+    peer_tables = torch.tensor([table.data_ptr(), table.data_ptr()], dtype=torch.int64, device=cuda_device)
+    counts = torch.arange(8, dtype=torch.int32, device=cuda_device)
+    signals = PeerSignals(rank=0, world=world, flags=flags, peer_flags=peer_flags, peer_tables=peer_tables,
+                          counts=counts, target=ib.B200Target(0), max_polls=2000)
+    signals.post(1)
+    signals.wait(1)                      # rank 1 never posts
+    torch.cuda.synchronize()
+    assert flags[1].tolist() == [1, 0] and other[1].tolist() == [1, 0]
+    with pytest.raises(RuntimeError, match="expired"):
+        signals.check()
+    signals.check()                      # the status is cleared by the failed check
+    other_side = torch.tensor([2, 2], dtype=torch.int32, device=cuda_device)
+    flags[1].copy_(other_side)           # "rank 1" arrives (and is already one step ahead)
+    signals.post(1)
+    signals.wait(1)
+    torch.cuda.synchronize()
+    signals.check()
+    assert torch.equal(torch.ones(1, device=cuda_device), torch.ones(1, device=cuda_device))   # context is usable
 
 
 def _free_port():
@@ -98,15 +152,17 @@ def _peer_worker(rank, world, port, results):
         expected = full(dev["x"], ids, weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
                         dev["down_scales"])
         logits, x, w = _slices(data, device, rank, world, tokens, experts)
-        ep = PeerExpertParallelMoE(tokens=tokens // world, hidden=hidden, intermediate=inter, experts=experts,
-                                   target=target)
-        call = ep.prepare(logits, x, *w)
         ok = True
-        for _ in range(3):
-            call.launch()
-            torch.cuda.synchronize()
-            t_local = tokens // world
-            ok = ok and bool(torch.equal(call.y, expected[rank * t_local:(rank + 1) * t_local]))
+        for signals in ("peer", "nccl"):
+            ep = PeerExpertParallelMoE(tokens=tokens // world, hidden=hidden, intermediate=inter, experts=experts,
+                                       target=target, signals=signals)
+            call = ep.prepare(logits, x, *w)
+            for _ in range(3):
+                call.launch()
+                torch.cuda.synchronize()
+                call.check()
+                t_local = tokens // world
+                ok = ok and bool(torch.equal(call.y, expected[rank * t_local:(rank + 1) * t_local]))
         results[rank] = ok
         dist.barrier()
     finally:
