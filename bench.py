@@ -557,12 +557,24 @@ def run_moe(args, rank: int, world: int, device):
         def prepare(lg, xx):
             call = ep.prepare(lg, xx, *weights)
             bound.update(logits=lg, x=xx, call=call)
-            return call.launch
+            if not args.moe_graph:
+                return call.launch
+            # the step holds no collective call (flag posts and bounded flag waits over peer memory),
+            # so it can be replayed as one CUDA graph
+            for _ in range(3):
+                call.launch()
+            torch.cuda.synchronize()
+            barrier(world)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                call.launch()
+            bound["graph"] = graph
+            return graph.replay
 
         def forward(lg, xx):      # end to end: the bound input buffers are refilled, the bound step is launched
             bound["logits"].copy_(lg, non_blocking=True)
             bound["x"].copy_(xx, non_blocking=True)
-            bound["call"].launch()
+            (bound["graph"].replay if "graph" in bound else bound["call"].launch)()
             return bound["call"].y
     else:
         from intent_b200.distributed import ExpertParallelMoE
@@ -597,6 +609,8 @@ def run_moe(args, rank: int, world: int, device):
     e2e_s = timed_e2e(e2e_step, e2e_steps, args.warmup, world, device)
     if world > 1 and args.moe_exchange != "peer":
         ep.check_overflow()
+    if world > 1 and args.moe_exchange == "peer":
+        bound["call"].check()          # a cross-rank wait that gave up would invalidate the run
     flops = tokens * cfg["top_k"] * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
     ms = elapsed_ms / args.steps
     peaks = measured_peaks()
@@ -608,8 +622,9 @@ def run_moe(args, rank: int, world: int, device):
         "config": {"workload": "moe_w4a16_swiglu_ffn 16384 tokens H=4096 E=64 top-2 I=1408 g128 (configs[4])",
                    "parallelism": "all experts local" if world == 1 else
                    (f"expert parallel: {e_local} experts and {t_local} tokens per gpu, rows written into the owners' "
-                    "buffers and results read back over NVLink peer memory (no data-path collective; one count "
-                    "all-gather and two barriers per step)" if args.moe_exchange == "peer" else
+                    "buffers and results read back over NVLink peer memory; three sync points per step as flag "
+                    "posts and bounded flag waits over peer memory, no collective call"
+                    + (", replayed as one CUDA graph" if args.moe_graph else "") if args.moe_exchange == "peer" else
                     f"expert parallel: {e_local} experts and {t_local} tokens per gpu, NCCL all-to-all each way, "
                     "fixed-capacity exchange (factor 1.5)"),
                    "step": "router + alignment + gather + up|gate GEMM (SiLU) + down GEMM + combine",
@@ -854,6 +869,8 @@ def main() -> int:
                         help="rows every expert span is padded to (= row tile of the grouped contraction)")
     parser.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores/loads, or NCCL all-to-all")
+    parser.add_argument("--moe-graph", action="store_true",
+                        help="replay the expert-parallel step (peer exchange) as one CUDA graph")
     parser.add_argument("--no-decode", action="store_true", help="prefill line without the attached decode figures")
     args = parser.parse_args()
     if args.steps is None:

@@ -110,7 +110,8 @@ __global__ void moe_peer_combine_kernel(const long long* __restrict__ peer_out, 
 // small payload (its per-expert counts) into every rank's table, fences, and stores the sequence
 // number into slot [channel][rank] of every rank's flag array.  It then WAITS until every slot of
 // its own array [channel][*] has reached the same number.  Sequence numbers only grow, so a rank
-// that runs ahead never confuses a slower one.  The wait is bounded: after `max_polls` polls it
+// that runs ahead never confuses a slower one.  The wait is bounded: after `max_polls` polls (about a
+// microsecond apart) it
 // records INTENT_B200_ERR_TIMEOUT in `status` and returns, so a missing rank cannot hang the GPU.
 __global__ void moe_peer_post_kernel(const long long* __restrict__ peer_flags, int world, int rank, int channel,
                                      int* __restrict__ sequence, const long long* __restrict__ peer_tables,
@@ -142,7 +143,7 @@ __global__ void moe_peer_wait_kernel(const int* __restrict__ my_flags, int world
       int value;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(value) : "l"(flag) : "memory");
       if (value - seq >= 0) { seen = true; break; }
-      __nanosleep(200);
+      __nanosleep(1000);
     }
     if (!seen) atomicExch(status, INTENT_B200_ERR_TIMEOUT);
   }

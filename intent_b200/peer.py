@@ -132,11 +132,12 @@ class PeerSignals:
     """One rank's sync points over peer memory: ``flags`` [3, world] is this rank's flag array,
     ``peer_flags`` the int64 table of every rank's array, ``peer_tables`` the table of every rank's count
     matrix.  Channel 0 carries the per-expert counts, channels 1 and 2 are plain barriers.  The waits are
-    bounded; ``status`` holds a timeout code if one gave up."""
+    bounded (``max_polls`` polls about a microsecond apart: the default rides out a rank that is still loading
+    its kernels, roughly 20 s); ``status`` holds a timeout code if one gave up."""
 
     CHANNELS = 3
 
-    def __init__(self, *, rank, world, flags, peer_flags, peer_tables, counts, target=None, max_polls=1 << 21):
+    def __init__(self, *, rank, world, flags, peer_flags, peer_tables, counts, target=None, max_polls=1 << 24):
         import torch
 
         device = flags.device

@@ -660,7 +660,7 @@ moe_peer_post = KernelDefinition(
     "no counterpart in the reference (it has no multi-GPU path)",
     "announce this rank at a sync point (optionally with its per-expert counts) in every rank's flag array")
 moe_peer_wait = KernelDefinition(
-    "moe_peer_wait", {"CHANNEL": 0, "MAX_POLLS": 1 << 21}, _lower_peer_wait,
+    "moe_peer_wait", {"CHANNEL": 0, "MAX_POLLS": 1 << 24}, _lower_peer_wait,
     "no counterpart in the reference (it has no multi-GPU path)",
     "bounded wait until every rank has announced itself at the sync point")
 
