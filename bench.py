@@ -565,10 +565,13 @@ def run_moe(args, rank: int, world: int, device):
                 call.launch()
             torch.cuda.synchronize()
             barrier(world)
+            from intent_b200.runtime import native
+
             graph = torch.cuda.CUDAGraph()
+            before = native.launch_count()
             with torch.cuda.graph(graph):
                 call.launch()
-            bound["graph"] = graph
+            bound["graph"], bound["launches_per_replay"] = graph, native.launch_count() - before
             return graph.replay
 
         def forward(lg, xx):      # end to end: the bound input buffers are refilled, the bound step is launched
@@ -594,6 +597,8 @@ def run_moe(args, rank: int, world: int, device):
     lgd, xd = logits.to(device), x.to(device)
     elapsed_ms, clocks, launches = timed_steps(prepare(lgd, xd), args.steps, args.warmup, world, device,
                                                rank, args.load_seconds)
+    if world > 1 and args.moe_exchange == "peer" and "launches_per_replay" in bound:
+        launches = bound["launches_per_replay"] * args.steps      # kernels inside the replayed graph
     pinned_l, pinned_x = logits.pin_memory(), x.pin_memory()
     pinned_y = torch.empty((t_local, hidden), dtype=torch.float32).pin_memory()
 
