@@ -63,6 +63,9 @@ struct StreamParams {
   int slots;       // shared-memory slots per CTA
   int slot_bytes;  // weight unit (+ activation box), multiple of 1024
   int own_tiles;   // column tiles every CTA owns whole (reduced in shared memory); the rest is split over K
+  int left_local;  // K-split tiles: a CTA first adds its own consecutive chunks of a tile in shared memory and
+                   // publishes one partial per (CTA, tile); 0 = one global partial per unit
+  int left_max;    // most K-split units any CTA gets (size of the shared-memory partial area)
   int twos_complement;
   int overlap;
   int* status;
@@ -100,6 +103,10 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const size_t own_offset = corr_offset + size_t(p.groups) * CP * 4 + (XSTAGED ? size_t(p.chunks) * kUnitRows * p.M * 16 : 0);
   int* own_count = reinterpret_cast<int*>(base_ptr + own_offset);
   float* own_part = reinterpret_cast<float*>(base_ptr + own_offset + 256);
+  // K-split units of this CTA: per-unit partials and one ticket per tile segment
+  const size_t left_offset = own_offset + 256 + size_t(p.own_tiles) * p.chunks * p.M * kUnitCols * 4;
+  int* left_count = reinterpret_cast<int*>(base_ptr + left_offset);
+  float* left_part = reinterpret_cast<float*>(base_ptr + left_offset + 256);
 
   // ---- this CTA's unit range -----------------------------------------------------
   // Units of this CTA: first its share of the K-split ("left-over") column tiles, whose partial sums
@@ -163,39 +170,54 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // in RPG adjacent lanes and are added by a fixed-order butterfly.
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
     const int k8 = p.K >> 3;
-    const bool all_chunks = XSTAGED || p.own_tiles > 0;
+    const bool all_chunks = XSTAGED || p.own_tiles > 0 || p.left_local != 0;
     const int touched = all_chunks ? p.chunks : min(p.chunks, n_left);
     const int rows = touched * kUnitRows;
     const int total = rows * p.M;
-    for (int start = 0; start < total; start += THREADS) {
-      const int i = start + tid;
-      float partial = 0.f;
-      int m = 0, row = 0;
-      bool active = i < total;
-      if (active) {
-        m = i / rows;
-        const int lr = i - m * rows;
-        const int chunk = all_chunks ? lr / kUnitRows : (left_base + l0 + lr / kUnitRows) % p.chunks;
-        row = chunk * kUnitRows + (lr % kUnitRows);
-        active = row < k8;
+    // four items per thread and pass: their loads are issued together, so the passes (M times as many
+    // as for one activation row) do not each pay a full memory latency
+    constexpr int BATCH = 4;
+    for (int start = 0; start < total; start += THREADS * BATCH) {
+      uint4 v[BATCH];
+      int ms[BATCH], row_of_item[BATCH];
+      bool in_range[BATCH], active[BATCH];
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        const int i = start + b * THREADS + tid;
+        in_range[b] = i < total;
+        ms[b] = 0;
+        row_of_item[b] = 0;
+        if (in_range[b]) {
+          ms[b] = i / rows;
+          const int lr = i - ms[b] * rows;
+          const int chunk = all_chunks ? lr / kUnitRows : (left_base + l0 + lr / kUnitRows) % p.chunks;
+          row_of_item[b] = chunk * kUnitRows + (lr % kUnitRows);
+        }
+        active[b] = in_range[b] && row_of_item[b] < k8;
+        v[b] = active[b] ? xg[size_t(ms[b]) * k8 + row_of_item[b]] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        const int m = ms[b], row = row_of_item[b];
+        float partial = 0.f;
         uint4 o = make_uint4(0, 0, 0, 0);  // rows past K/8 (last chunk) are staged as zeros
-        if (active) {
-          const uint4 v = xg[size_t(m) * k8 + row];
-          o.x = prmt(v.x, v.z, 0x5410);                        // (k0, k4)
-          o.y = Expand<T>::scale_odd(prmt(v.x, v.z, 0x7632));  // (k1, k5)
-          o.z = prmt(v.y, v.w, 0x5410);                        // (k2, k6)
-          o.w = Expand<T>::scale_odd(prmt(v.y, v.w, 0x7632));  // (k3, k7)
+        if (active[b]) {
+          o.x = prmt(v[b].x, v[b].z, 0x5410);                        // (k0, k4)
+          o.y = Expand<T>::scale_odd(prmt(v[b].x, v[b].z, 0x7632));  // (k1, k5)
+          o.z = prmt(v[b].y, v[b].w, 0x5410);                        // (k2, k6)
+          o.w = Expand<T>::scale_odd(prmt(v[b].y, v[b].w, 0x7632));  // (k3, k7)
           partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
                     Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
         }
-        if (XSTAGED) xs[row * p.M + m] = o;
-      }
+        if (XSTAGED && in_range[b]) xs[row * p.M + m] = o;
 #pragma unroll
-      for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
-      if (active && (row % RPG) == 0) corr[(row / RPG) * CP + m] = -partial;
+        for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+        if (active[b] && (row % RPG) == 0) corr[(row / RPG) * CP + m] = -partial;
+      }
     }
   }
   for (int i = tid; i < p.own_tiles; i += THREADS) own_count[i] = 0;
+  if (p.left_local && tid < 64) left_count[tid] = 0;
   __syncthreads();
 
   uint32_t magic_a, magic_b;
@@ -298,11 +320,24 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
 
-    // ---- the unit's partial goes to scratch; the last ticket of the tile finishes it ----
+    // ---- the unit's partial is stored; the last ticket of its group of partials finishes the group ----
     // accumulator element (mb, i): row m = 8*mb + 2t + (i & 1), column 4g + (i >> 1)
+    // Three kinds of group: an owned tile (all chunks in this CTA, shared memory), a segment (this CTA's
+    // consecutive chunks of a K-split tile, shared memory; its sum becomes ONE global partial of the tile),
+    // and, without left_local, the K-split tile itself with one global partial per unit.
     const int tile_local = tile - int(blockIdx.x) * p.own_tiles;
-    float* mine = owned ? own_part + (size_t(tile_local) * p.chunks + chunk) * part
-                        : p.scratch + (size_t(tile) * p.chunks + chunk) * part;
+    const bool segment = !owned && p.left_local != 0;
+    int seg = 0, seg_first = 0, seg_len = p.chunks;     // segment: index in this CTA, first local unit, units
+    if (segment) {
+      const int first_tile = (left_base + l0) / p.chunks;
+      seg = tile - first_tile;
+      const int begin = max(tile * p.chunks, left_base + l0), end = min((tile + 1) * p.chunks, left_base + l1);
+      seg_first = begin - (left_base + l0);
+      seg_len = end - begin;
+    }
+    float* mine = owned     ? own_part + (size_t(tile_local) * p.chunks + chunk) * part
+                  : segment ? left_part + size_t(j) * part
+                            : p.scratch + (size_t(tile) * p.chunks + chunk) * part;
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
@@ -312,59 +347,108 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           *reinterpret_cast<float4*>(mine + m * kUnitCols + 4 * g) =
               make_float4(facc[mb][0 + hh], facc[mb][2 + hh], facc[mb][4 + hh], facc[mb][6 + hh]);
       }
-    // One ticket per unit.  Owned tiles: shared-memory partials and counter, block-scope fences.
-    // K-split tiles: global scratch, one acq_rel atomic (the warp barrier orders every lane's stores
-    // before lane 0's release; the acquire side covers the reads of the last arriver).
+    // One ticket per unit.  Shared-memory groups: block-scope fences around a shared counter.  Global
+    // partials: one acq_rel atomic (the warp barrier orders every lane's stores before lane 0's release;
+    // the acquire side covers the reads of the last arriver).
     __syncwarp();
     int last = 0;
     if (lane == 0) {
       int old;
-      if (owned) {
+      if (owned || segment) {
         __threadfence_block();
-        old = atomicAdd(own_count + tile_local, 1);
+        old = atomicAdd(owned ? own_count + tile_local : left_count + seg, 1);
+        last = old == seg_len - 1;
       } else {
         asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile) : "memory");
+        last = old == p.chunks - 1;
       }
-      last = old == p.chunks - 1;
     }
     last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      if (owned) __threadfence_block();
-      // lane = 8*q + v: quarter q adds chunks q, q+4, ... for columns 4v..4v+3 (independent loads,
-      // all in flight together), then the four quarters are added in a fixed order
-      const float* all = owned ? own_part + size_t(tile_local) * p.chunks * part
-                               : p.scratch + size_t(tile) * p.chunks * part;
-      const int q = lane >> 3, v = lane & 7;
-      for (int m = 0; m < p.M; ++m) {
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = q; c < p.chunks; c += 4) {
-          const float4* src = reinterpret_cast<const float4*>(all + size_t(c) * part + m * kUnitCols + 4 * v);
-          const float4 a = owned ? *src : __ldcg(src);
-          sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+    if (!last) continue;
+    if (owned || segment) __threadfence_block();
+
+    // lane = 8*q + v: quarter q adds partials q, q+4, ... for columns 4v..4v+3 (four loads in flight at
+    // a time), then the four quarters are added in a fixed order: bitwise reproducible
+    const int q = lane >> 3, v = lane & 7;
+    auto sum_partials = [&](const float* first, int count, bool global, int m) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = q; c < count; c += 16) {
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c + 4 * u;
+          a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cc < count) {
+            const float4* src = reinterpret_cast<const float4*>(first + size_t(cc) * part + m * kUnitCols + 4 * v);
+            a[u] = global ? __ldcg(src) : *src;
+          }
         }
 #pragma unroll
-        for (int d = 16; d >= 8; d >>= 1) {
-          sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
-          sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
-          sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
-          sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
-        }
-        const int n = tile * kUnitCols + 4 * v;
-        if (q == 0 && n < p.N) {  // N is a multiple of 8, so the four columns are inside together
-          uint2 out;
-          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
-          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
-          *reinterpret_cast<uint2*>(y + size_t(m) * p.N + n) = out;
+        for (int u = 0; u < 4; ++u) {
+          sum.x += a[u].x; sum.y += a[u].y; sum.z += a[u].z; sum.w += a[u].w;
         }
       }
-      if (lane == 0 && !owned) p.counters[tile] = 0;  // ready for the next launch
+#pragma unroll
+      for (int d = 16; d >= 8; d >>= 1) {
+        sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
+        sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
+        sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
+        sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+      }
+      return sum;
+    };
+    auto write_row = [&](int m, float4 sum) {
+      const int n = tile * kUnitCols + 4 * v;
+      if (q == 0 && n < p.N) {  // N is a multiple of 8, so the four columns are inside together
+        uint2 out;
+        out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
+        out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+        *reinterpret_cast<uint2*>(y + size_t(m) * p.N + n) = out;
+      }
+    };
+
+    if (owned || (segment && seg_len == p.chunks)) {
+      // every chunk of the tile was added here: the sum is the result
+      const float* first = owned ? own_part + size_t(tile_local) * p.chunks * part : left_part + size_t(seg_first) * part;
+      for (int m = 0; m < p.M; ++m) write_row(m, sum_partials(first, p.chunks, false, m));
+    } else if (segment) {
+      // publish the segment's sum as partial number (this CTA - first CTA of the tile) of the tile, then
+      // take the tile's global ticket; the CTA that takes the last one adds the tile's few partials
+      const long long left_total_ll = left_total;
+      auto cta_of = [&](int left_unit) {   // the CTA whose K-split range holds this unit
+        return int(((long long)(left_unit + 1) * grid + left_total_ll - 1) / left_total_ll) - 1;
+      };
+      const int tile_begin = tile * p.chunks - left_base;
+      const int first_cta = cta_of(tile_begin), last_cta = cta_of(tile_begin + p.chunks - 1);
+      float* slot = p.scratch + (size_t(tile) * p.chunks + (int(blockIdx.x) - first_cta)) * part;
+      for (int m = 0; m < p.M; ++m) {
+        const float4 sum = sum_partials(left_part + size_t(seg_first) * part, seg_len, false, m);
+        if (q == 0) *reinterpret_cast<float4*>(slot + m * kUnitCols + 4 * v) = sum;
+      }
+      __syncwarp();
+      int final_one = 0;
+      if (lane == 0) {
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile) : "memory");
+        final_one = old == last_cta - first_cta;
+      }
+      final_one = __shfl_sync(0xffffffffu, final_one, 0);
+      if (final_one) {
+        const float* first = p.scratch + size_t(tile) * p.chunks * part;
+        for (int m = 0; m < p.M; ++m) write_row(m, sum_partials(first, last_cta - first_cta + 1, true, m));
+        if (lane == 0) p.counters[tile] = 0;  // ready for the next launch
+      }
+    } else {
+      const float* first = p.scratch + size_t(tile) * p.chunks * part;
+      for (int m = 0; m < p.M; ++m) write_row(m, sum_partials(first, p.chunks, true, m));
+      if (lane == 0) p.counters[tile] = 0;  // ready for the next launch
     }
   }
 }
 
 struct Plan {
-  int grid, slots, slot_bytes, warps, tiles, chunks, units, own_tiles;
-  bool staged;
+  int grid, slots, slot_bytes, warps, tiles, chunks, units, own_tiles, left_max;
+  bool staged, left_local;
   size_t smem_bytes, counters_offset, scratch_offset, workspace_bytes;
 };
 
@@ -380,12 +464,18 @@ bool make_plan(int M, int K, int N, int mb, int sms, int warps_override, Plan* p
   q.own_tiles = q.tiles / q.grid;
   if (q.own_tiles > 64 || size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4 > 32 * 1024) q.own_tiles = 0;
   const int left_units = q.units - q.own_tiles * q.grid * q.chunks;
-  const int per_cta_max = q.own_tiles * q.chunks + (left_units + q.grid - 1) / q.grid;
+  q.left_max = (left_units + q.grid - 1) / q.grid;
+  const int per_cta_max = q.own_tiles * q.chunks + q.left_max;
+  // K-split tiles: a CTA adds its own chunks of a tile in shared memory first (at most 64 tile segments
+  // per CTA, and the per-unit partials must stay small next to the weight slots)
+  const size_t left_bytes = 256 + size_t(q.left_max) * M * kUnitCols * 4;
+  // (only when every CTA gets at least one K-split unit: the CTAs that share a tile are then consecutive)
+  q.left_local = left_units >= q.grid && (q.left_max + q.chunks - 1) / q.chunks + 1 <= 64 && left_bytes <= 56 * 1024;
   const size_t x_bytes = size_t(M) * q.chunks * kUnitRows * 16;  // staged rows are padded to whole chunks
   q.staged = x_bytes <= 32 * 1024;
   q.slot_bytes = ((kUnitActOffset + (q.staged ? 0 : M * 512) + 1023) / 1024) * 1024;
   const size_t fixed = 1024 + 16 + size_t((K + 31) / 32) * 8 * mb * 4 + (q.staged ? x_bytes : 0) + 256 + 16 +
-                       size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4;
+                       size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4 + (q.left_local ? left_bytes : 0);
   long long capacity = (long long)(size_t(kSmemLimit) - fixed) / (q.slot_bytes + 8);
   if (capacity >= per_cta_max) {
     q.slots = per_cta_max;
@@ -499,6 +589,8 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, void
   p.slots = plan.slots;
   p.slot_bytes = plan.slot_bytes;
   p.own_tiles = plan.own_tiles;
+  p.left_local = plan.left_local ? 1 : 0;
+  p.left_max = plan.left_max;
   p.twos_complement = zero_point == -1 ? 1 : 0;
   p.overlap = g_overlap;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
