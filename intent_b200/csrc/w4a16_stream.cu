@@ -73,7 +73,9 @@ struct StreamParams {
   float* scratch;  // [tile][chunk][M][32] partial sums
 };
 
-template <typename T, int MB, int STEPS, int WARPS, bool XSTAGED>
+// RING: 0 = every unit of the CTA has its own slot; 1 = fewer slots than units, a multiple of WARPS, each slot is
+// refilled by the warp that owns it; 2 = any slot count, a refill is announced through a per-slot counter
+template <typename T, int MB, int STEPS, int WARPS, bool XSTAGED, int RING>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const __grid_constant__ CUtensorMap map_x, const StreamParams p) {
@@ -95,7 +97,9 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bars = base + uint32_t(p.slots) * p.slot_bytes;
-  const size_t corr_offset = size_t(p.slots) * p.slot_bytes + ((size_t(p.slots) * 8 + 15) & ~size_t(15));
+  // after the barriers: one counter per slot, the number of loads issued into it so far
+  const size_t corr_offset = size_t(p.slots) * p.slot_bytes + ((size_t(p.slots) * (RING == 2 ? 12 : 8) + 15) & ~size_t(15));
+  volatile int* issued = reinterpret_cast<volatile int*>(base_ptr + size_t(p.slots) * p.slot_bytes + size_t(p.slots) * 8);
   float* corr = reinterpret_cast<float*>(base_ptr + corr_offset);
   uint4* xs = reinterpret_cast<uint4*>(base_ptr + corr_offset + size_t(p.groups) * CP * 4);  // [chunks*32][M]
   const uint32_t xs_addr = base + uint32_t(corr_offset) + uint32_t(p.groups) * CP * 4;
@@ -152,11 +156,16 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   };
 
   // ---- start the weight stream before anything else ----------------------------
-  // Warp w owns local units w, w + WARPS, ...; unit j lives in slot j % slots.  Either
-  // slots >= n_units or slots is a multiple of WARPS, so a slot is refilled by its owner.
+  // Warp w consumes local units w, w + WARPS, ...; unit j lives in slot j % slots.  The warp that
+  // consumed unit j refills the slot with unit j + slots and bumps the slot's issue counter; the
+  // consumer of that unit (any warp) looks at the counter before it waits on the barrier, so a
+  // barrier is never polled two phases ahead and the slot count need not be a multiple of WARPS.
   const int first_wave = min(n_units, p.slots);
   if (lane == 0) {
-    for (int s = warp; s < p.slots; s += WARPS) mbar_init(bars + uint32_t(s) * 8u, 1);
+    for (int s = warp; s < p.slots; s += WARPS) {
+      mbar_init(bars + uint32_t(s) * 8u, 1);
+      if (RING == 2) issued[s] = 1;
+    }
     fence_mbar_init();
     for (int j = warp; j < first_wave; j += WARPS) issue_weights(j);
   }
@@ -238,6 +247,11 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   for (int j = warp; j < n_units; j += WARPS) {
     int tile, chunk;
     const bool owned = unit_of(j, tile, chunk);
+    if (RING == 2 && j >= p.slots) {  // a refilled slot: wait (bounded) until the refill has been issued
+      const int need = j / p.slots + 1;
+      for (int spin = 0; spin < (1 << 22) && issued[j % p.slots] < need; ++spin) __nanosleep(20);
+      __threadfence_block();
+    }
     if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(j), (j / p.slots) & 1))) {
       if (lane == 0) atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);  // this unit's loads never completed
       break;
@@ -311,12 +325,16 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         facc[mb][7] = fmaf(gacc[mb][7], s3, facc[mb][7]);
       }
     }
-    if (j + p.slots < n_units) {  // refill this slot with the unit that maps to it next (same owner warp)
+    if (RING != 0 && j + p.slots < n_units) {  // refill this slot with the unit that maps to it next
       __syncwarp();
       fence_proxy_async();
       if (lane == 0) {
         issue_weights(j + p.slots);
         issue_activations(j + p.slots);
+        if (RING == 2) {
+          __threadfence_block();
+          issued[j % p.slots] = (j + p.slots) / p.slots + 1;
+        }
       }
     }
 
@@ -449,6 +467,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 struct Plan {
   int grid, slots, slot_bytes, warps, tiles, chunks, units, own_tiles, left_max;
   bool staged, left_local;
+  int ring;   // 0 none, 1 slots refilled by their owner warp, 2 refills announced per slot
   size_t smem_bytes, counters_offset, scratch_offset, workspace_bytes;
 };
 
@@ -460,31 +479,61 @@ bool make_plan(int M, int K, int N, int mb, int sms, int warps_override, Plan* p
   q.units = q.tiles * q.chunks;
   q.grid = q.units < sms ? q.units : sms;
   q.warps = warps_override ? warps_override : (mb == 1 ? 32 : 16);
-  // column tiles owned whole by every CTA (their partial sums live in shared memory)
-  q.own_tiles = q.tiles / q.grid;
-  if (q.own_tiles > 64 || size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4 > 32 * 1024) q.own_tiles = 0;
-  const int left_units = q.units - q.own_tiles * q.grid * q.chunks;
-  q.left_max = (left_units + q.grid - 1) / q.grid;
-  const int per_cta_max = q.own_tiles * q.chunks + q.left_max;
-  // K-split tiles: a CTA adds its own chunks of a tile in shared memory first (at most 64 tile segments
-  // per CTA, and the per-unit partials must stay small next to the weight slots)
-  const size_t left_bytes = 256 + size_t(q.left_max) * M * kUnitCols * 4;
-  // (only when every CTA gets at least one K-split unit: the CTAs that share a tile are then consecutive)
-  q.left_local = left_units >= q.grid && (q.left_max + q.chunks - 1) / q.chunks + 1 <= 64 && left_bytes <= 56 * 1024;
+  // Candidate layouts: activations staged whole in shared memory or riding with every unit; column tiles
+  // owned whole by a CTA or every tile split over K.  The layout that keeps the largest share of a CTA's
+  // units in flight wins, with a bonus for staged activations and for owned tiles.
   const size_t x_bytes = size_t(M) * q.chunks * kUnitRows * 16;  // staged rows are padded to whole chunks
-  q.staged = x_bytes <= 32 * 1024;
-  q.slot_bytes = ((kUnitActOffset + (q.staged ? 0 : M * 512) + 1023) / 1024) * 1024;
-  const size_t fixed = 1024 + 16 + size_t((K + 31) / 32) * 8 * mb * 4 + (q.staged ? x_bytes : 0) + 256 + 16 +
-                       size_t(q.own_tiles) * q.chunks * M * kUnitCols * 4 + (q.left_local ? left_bytes : 0);
-  long long capacity = (long long)(size_t(kSmemLimit) - fixed) / (q.slot_bytes + 8);
-  if (capacity >= per_cta_max) {
-    q.slots = per_cta_max;
-  } else {
-    if (capacity < q.warps && q.warps == 32) q.warps = 16;
-    q.slots = int(capacity / q.warps) * q.warps;
-    if (q.slots < q.warps) return false;
+  int own_candidate = q.tiles / q.grid;
+  if (own_candidate > 64 || size_t(own_candidate) * q.chunks * M * kUnitCols * 4 > 32 * 1024) own_candidate = 0;
+  const int wanted_warps = q.warps;
+  double best_score = -1.0;
+  size_t fixed = 0;
+  Plan best{};
+  for (int staged = 1; staged >= 0; --staged) {
+    if (staged && x_bytes > 96 * 1024) continue;
+    for (int pass = 0; pass < 2; ++pass) {
+      if (pass == 1 && own_candidate == 0) break;
+      Plan c = q;
+      c.staged = staged != 0;
+      c.own_tiles = pass == 0 ? own_candidate : 0;
+      c.warps = wanted_warps;
+      const int left_units = c.units - c.own_tiles * c.grid * c.chunks;
+      c.left_max = (left_units + c.grid - 1) / c.grid;
+      const int per_cta_max = c.own_tiles * c.chunks + c.left_max;
+      // K-split tiles: a CTA adds its own chunks of a tile in shared memory first (only when every CTA gets
+      // at least one K-split unit - the CTAs that share a tile are then consecutive -, at most 64 tile
+      // segments per CTA, and the per-unit partials must stay small next to the weight slots)
+      const size_t left_bytes = 256 + size_t(c.left_max) * M * kUnitCols * 4;
+      c.left_local = left_units >= c.grid && (c.left_max + c.chunks - 1) / c.chunks + 1 <= 64 && left_bytes <= 56 * 1024;
+      c.slot_bytes = ((kUnitActOffset + (c.staged ? 0 : M * 512) + 1023) / 1024) * 1024;
+      const size_t f = 1024 + 32 + size_t((K + 31) / 32) * 8 * mb * 4 + (c.staged ? x_bytes : 0) + 256 + 16 +
+                       size_t(c.own_tiles) * c.chunks * M * kUnitCols * 4 + (c.left_local ? left_bytes : 0);
+      if (size_t(kSmemLimit) <= f) continue;
+      const long long capacity = (long long)(size_t(kSmemLimit) - f) / (c.slot_bytes + 12);
+      if (capacity >= per_cta_max) {
+        c.ring = 0;
+        c.slots = per_cta_max;
+      } else {
+        if (capacity < c.warps && c.warps == 32) c.warps = 16;
+        if (capacity < c.warps) continue;
+        // at least one and a half slots per warp: keep them all and announce refills per slot; otherwise
+        // whole rounds of the warps, every slot refilled by its owner
+        c.ring = capacity * 2 >= c.warps * 3 && capacity % c.warps != 0 ? 2 : 1;
+        c.slots = int(c.ring == 2 ? capacity : capacity / c.warps * c.warps);
+      }
+      // staged activations save a shuffle and a multiply per load in the inner loop: worth a quarter of the
+      // CTA's units in flight; owned tiles skip the global ticket chain
+      const double score = double(c.slots) / double(per_cta_max) + (c.staged ? 0.25 : 0.0) + (c.own_tiles > 0 ? 0.05 : 0.0);
+      if (score > best_score) {
+        best_score = score;
+        best = c;
+        fixed = f;
+      }
+    }
   }
-  q.smem_bytes = fixed + size_t(q.slots) * (q.slot_bytes + 8);
+  if (best_score < 0.0) return false;
+  q = best;
+  q.smem_bytes = fixed + size_t(q.slots) * (q.slot_bytes + 12);
   q.counters_offset = 256;
   q.scratch_offset = ((q.counters_offset + size_t(q.tiles) * 4 + 255) / 256) * 256;
   q.workspace_bytes = q.scratch_offset + size_t(q.units) * M * kUnitCols * 4;
@@ -506,10 +555,10 @@ int g_overlap = 0;
 int g_grid_override = 0;
 int g_warps_override = 0;
 
-template <typename T, int MB, int STEPS, int WARPS, bool XSTAGED>
+template <typename T, int MB, int STEPS, int WARPS, bool XSTAGED, int RING>
 int launch_kernel(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUtensorMap& map_x, const StreamParams& p, const Plan& plan,
                   cudaStream_t stream) {
-  auto kernel = w4a16_stream_kernel<T, MB, STEPS, WARPS, XSTAGED>;
+  auto kernel = w4a16_stream_kernel<T, MB, STEPS, WARPS, XSTAGED, RING>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(plan.smem_bytes));
   if (e != cudaSuccess) return cuda_status(e);
   cudaLaunchConfig_t config = {};
@@ -528,15 +577,26 @@ int launch_kernel(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUte
   return launch_status();
 }
 
+template <typename T, int MB, int STEPS, int WARPS, bool XSTAGED>
+int launch_ring(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUtensorMap& map_x, const StreamParams& p,
+                const Plan& plan, cudaStream_t stream) {
+  if (plan.ring == 0) return launch_kernel<T, MB, STEPS, WARPS, XSTAGED, 0>(map_w, map_s, map_x, p, plan, stream);
+  if (plan.ring == 1) return launch_kernel<T, MB, STEPS, WARPS, XSTAGED, 1>(map_w, map_s, map_x, p, plan, stream);
+  return launch_kernel<T, MB, STEPS, WARPS, XSTAGED, 2>(map_w, map_s, map_x, p, plan, stream);
+}
+
+template <typename T, int MB, int STEPS, int WARPS>
+int launch_warps(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUtensorMap& map_x, const StreamParams& p,
+                 const Plan& plan, cudaStream_t stream) {
+  if (plan.staged) return launch_ring<T, MB, STEPS, WARPS, true>(map_w, map_s, map_x, p, plan, stream);
+  return launch_ring<T, MB, STEPS, WARPS, false>(map_w, map_s, map_x, p, plan, stream);
+}
+
 template <typename T, int MB, int STEPS>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUtensorMap& map_x, const StreamParams& p, const Plan& plan,
            cudaStream_t stream) {
-  if (MB == 1 && plan.warps == 32) {
-    if (plan.staged) return launch_kernel<T, 1, STEPS, 32, true>(map_w, map_s, map_x, p, plan, stream);
-    return launch_kernel<T, 1, STEPS, 32, false>(map_w, map_s, map_x, p, plan, stream);
-  }
-  if (plan.staged) return launch_kernel<T, MB, STEPS, 16, true>(map_w, map_s, map_x, p, plan, stream);
-  return launch_kernel<T, MB, STEPS, 16, false>(map_w, map_s, map_x, p, plan, stream);
+  if (MB == 1 && plan.warps == 32) return launch_warps<T, 1, STEPS, 32>(map_w, map_s, map_x, p, plan, stream);
+  return launch_warps<T, MB, STEPS, 16>(map_w, map_s, map_x, p, plan, stream);
 }
 
 template <typename T>
