@@ -66,6 +66,7 @@ struct StreamParams {
   int left_local;  // K-split tiles: a CTA first adds its own consecutive chunks of a tile in shared memory and
                    // publishes one partial per (CTA, tile); 0 = one global partial per unit
   int left_max;    // most K-split units any CTA gets (size of the shared-memory partial area)
+  int left_each, left_extra;  // K-split units per CTA: the first left_extra CTAs get left_each + 1, the rest left_each
   int twos_complement;
   int overlap;
   int* status;
@@ -86,6 +87,10 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
 
   if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
+  if (threadIdx.x == 0) {   // the descriptors are needed by the very first instructions that matter
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_s);
+  }
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -116,11 +121,12 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // Units of this CTA: first its share of the K-split ("left-over") column tiles, whose partial sums
   // meet in global scratch - their store/ticket round trips then overlap the rest of the stream - and
   // then every K chunk of the column tiles it owns whole, which are reduced in shared memory.
-  const long long grid = gridDim.x;
+  const int grid = int(gridDim.x);
   const int left_base = p.own_tiles * int(grid) * p.chunks;   // first unit of the K-split tiles
   const int left_total = p.units - left_base;
-  const int l0 = int((long long)blockIdx.x * left_total / grid);
-  const int l1 = int((long long)(blockIdx.x + 1) * left_total / grid);
+  // quotient and remainder come from the host: no division on the way to the first load
+  const int l0 = int(blockIdx.x) * p.left_each + min(int(blockIdx.x), p.left_extra);
+  const int l1 = l0 + p.left_each + (int(blockIdx.x) < p.left_extra ? 1 : 0);
   const int n_left = l1 - l0;
   const int n_units = n_left + p.own_tiles * p.chunks;
   auto unit_of = [&](int j, int& tile, int& chunk) {   // returns true for a unit of an owned tile
@@ -432,9 +438,10 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (segment) {
       // publish the segment's sum as partial number (this CTA - first CTA of the tile) of the tile, then
       // take the tile's global ticket; the CTA that takes the last one adds the tile's few partials
-      const long long left_total_ll = left_total;
       auto cta_of = [&](int left_unit) {   // the CTA whose K-split range holds this unit
-        return int(((long long)(left_unit + 1) * grid + left_total_ll - 1) / left_total_ll) - 1;
+        const int boundary = p.left_extra * (p.left_each + 1);
+        return left_unit < boundary ? left_unit / (p.left_each + 1)
+                                    : p.left_extra + (left_unit - boundary) / p.left_each;   // left_each > 0 here
       };
       const int tile_begin = tile * p.chunks - left_base;
       const int first_cta = cta_of(tile_begin), last_cta = cta_of(tile_begin + p.chunks - 1);
@@ -651,6 +658,11 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, void
   p.own_tiles = plan.own_tiles;
   p.left_local = plan.left_local ? 1 : 0;
   p.left_max = plan.left_max;
+  {
+    const int left_units = plan.units - plan.own_tiles * plan.grid * plan.chunks;
+    p.left_each = left_units / plan.grid;
+    p.left_extra = left_units % plan.grid;
+  }
   p.twos_complement = zero_point == -1 ? 1 : 0;
   p.overlap = g_overlap;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
