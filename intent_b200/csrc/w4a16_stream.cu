@@ -129,17 +129,26 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int l1 = l0 + p.left_each + (int(blockIdx.x) < p.left_extra ? 1 : 0);
   const int n_left = l1 - l0;
   const int n_units = n_left + p.own_tiles * p.chunks;
+  // first K-split unit of this CTA as (tile, chunk): the one division of the prologue
+  const int left_first_tile = (left_base + l0) / p.chunks;
+  const int left_first_chunk = (left_base + l0) - left_first_tile * p.chunks;
   auto unit_of = [&](int j, int& tile, int& chunk) {   // returns true for a unit of an owned tile
+    // a CTA's units are few and consecutive: counting up replaces the divisions
     if (j < n_left) {
-      const int u = left_base + l0 + j;
-      tile = u / p.chunks;
-      chunk = u - tile * p.chunks;
+      tile = left_first_tile;
+      chunk = left_first_chunk + j;
+      while (chunk >= p.chunks) {
+        chunk -= p.chunks;
+        ++tile;
+      }
       return false;
     }
-    const int jj = j - n_left;
-    const int local = jj / p.chunks;
-    tile = int(blockIdx.x) * p.own_tiles + local;
-    chunk = jj - local * p.chunks;
+    tile = int(blockIdx.x) * p.own_tiles;
+    chunk = j - n_left;
+    while (chunk >= p.chunks) {
+      chunk -= p.chunks;
+      ++tile;
+    }
     return true;
   };
   const uint32_t x_bytes = XSTAGED ? 0u : uint32_t(p.M) * 512u;
