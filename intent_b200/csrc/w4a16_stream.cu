@@ -153,8 +153,10 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   };
   const uint32_t x_bytes = XSTAGED ? 0u : uint32_t(p.M) * 512u;
 
-  auto slot_addr = [&](int j) { return base + uint32_t(j % p.slots) * p.slot_bytes; };
-  auto bar_addr = [&](int j) { return bars + uint32_t(j % p.slots) * 8u; };
+  // without a ring every unit has its own slot: no modulo, phase 0
+  auto slot_of = [&](int j) { return RING == 0 ? j : j % p.slots; };
+  auto slot_addr = [&](int j) { return base + uint32_t(slot_of(j)) * p.slot_bytes; };
+  auto bar_addr = [&](int j) { return bars + uint32_t(slot_of(j)) * 8u; };
   auto issue_weights = [&](int j) {
     int tile, chunk;
     unit_of(j, tile, chunk);
@@ -267,7 +269,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int spin = 0; spin < (1 << 22) && issued[j % p.slots] < need; ++spin) __nanosleep(20);
       __threadfence_block();
     }
-    if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(j), (j / p.slots) & 1))) {
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_addr(j), RING == 0 ? 0 : (j / p.slots) & 1))) {
       if (lane == 0) atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);  // this unit's loads never completed
       break;
     }
