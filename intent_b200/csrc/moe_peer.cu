@@ -2,8 +2,9 @@
 // data path: every rank writes its token rows straight into the expert-sorted row buffer of the
 // rank that owns the expert, and reads the finished f32 rows straight out of the owners'
 // result buffers while it combines them.  Only real rows cross the links (no padded spans, no
-// staging copy); the ranks meet at two stream-ordered barriers issued by the host between the
-// phases, so no kernel here waits on another GPU.
+// staging copy).  Between the phases the ranks meet at sync points: either stream-ordered
+// collectives issued by the host, or the post / wait kernels at the end of this file (flag writes and
+// bounded flag waits over peer memory).  The data kernels themselves never wait on another GPU.
 //
 // The reference's programs behind these kernels: route grouping examples/kernels/routing/moe_align.py:14-86,
 // row gather and weighted scatter_reduce examples/kernels/ragged/moe.py:34-53.

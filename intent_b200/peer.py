@@ -5,8 +5,9 @@ of the rank that owns the expert (NVLink stores), the owners run the grouped int
 rows that are already in place, and every rank then reads the finished f32 rows straight
 out of the owners' result buffers while it combines them (NVLink loads).  Only real rows
 cross the links: there are no padded spans, no staging copy and no second gather.  The
-per-step host traffic is one 4*E-byte count all-gather and two barriers, all stream-ordered
-NCCL calls; no kernel waits on another GPU.
+ranks meet at three sync points per step (counts exchanged, rows written, results written):
+flag posts and bounded flag waits over peer memory (``PeerSignals``), so the step holds no
+collective call, or - ``signals='nccl'`` - an all-gather and two one-word all-reduces.
 
 The owner's layout (experts in local order, spans padded to the tile rows, source rank 0
 first inside a span) equals the single-GPU stable alignment over all tokens when the
