@@ -196,7 +196,8 @@ INTENT_B200_API int intent_b200_moe_combine(INTENT_B200_VIEW2(a0), INTENT_B200_V
  * into row `rank` of every rank's table [W, C] (a2: their addresses; extent 0 = no payload), fences, and stores the
  * number into slot [channel][rank] of every rank's flag array (a0: their addresses).  wait returns when every slot
  * [channel][*] of this rank's own array (a0) has reached this rank's number; it gives up after max_polls polls
- * (about a microsecond apart) and then writes INTENT_B200_ERR_TIMEOUT into a2 status[0] instead of hanging.
+ * (about a microsecond apart) and then writes INTENT_B200_ERR_TIMEOUT into a2 status[0] instead of hanging; while
+ * status[0] is non-zero every later wait returns at once (the caller clears it after handling the failure).
  * a1 sequence [2 * channels] i32 is private to the rank (post and wait counters), zero before the first use. */
 INTENT_B200_API int intent_b200_moe_peer_post(INTENT_B200_VIEW1(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2),
                                               INTENT_B200_VIEW1(a3), int32_t rank, int32_t channel, void* stream);

@@ -135,8 +135,13 @@ __global__ void moe_peer_post_kernel(const long long* __restrict__ peer_flags, i
 __global__ void moe_peer_wait_kernel(const int* __restrict__ my_flags, int world, int channel,
                                      int* __restrict__ sequence, int max_polls, int* __restrict__ status) {
   __shared__ int seq;
-  if (threadIdx.x == 0) seq = ++sequence[2 * channel + 1];
+  __shared__ int broken;
+  if (threadIdx.x == 0) {
+    seq = ++sequence[2 * channel + 1];
+    broken = *status;   // an earlier wait already gave up: later ones return at once, so that the work
+  }                     // queued behind a lost rank drains in one bound, not one bound per wait
   __syncthreads();
+  if (broken != 0) return;
   for (int src = threadIdx.x; src < world; src += blockDim.x) {
     const int* flag = my_flags + channel * world + src;
     bool seen = false;
