@@ -13,7 +13,12 @@ shapes and value distributions of the benchmark configurations):
            [1,4096]x[4096,14336] and the down projection [1,14336]x[14336,4096];
            metric = weight GB/s (algorithmic bytes / time).  HBM-bound.  Replicas only.
   w8a8     int8 GEMM 4096x8192x8192 with the scaled bf16 epilogue, columns split.
-  moe      16384-token top-2 MoE FFN with int4 experts; expert parallel for N > 1.
+  moe      16384-token top-2 MoE FFN with int4 experts; expert parallel for N > 1
+           (--moe-exchange peer: rows and results move by direct NVLink stores and loads
+           between the ranks' buffers; nccl: all-to-all; --moe-graph: the peer step as one
+           CUDA graph).
+  grouped  the reference's published dense grouped GEMM case (8 groups x 1024 rows,
+           K=4096, N=14336, f16), columns split.
 
 `value` is measured with inputs resident in HBM, the K timed steps captured in one
 CUDA graph (the kernels are microseconds long; eager launches would measure the
@@ -48,7 +53,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # DRAM traffic per launch of the dominant kernel from an ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {"decode": 30314496, "prefill": 529902848, "w8a8": 149691136}
+NCU_TRAFFIC_BYTES = {"decode": 30314496, "prefill": 529902848, "w8a8": 149691136, "grouped": 1231225192}
 
 
 def measured_peaks():
