@@ -174,4 +174,6 @@ def main(root: Path) -> None:
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/generate.py /path/to/reference")
+    main(Path(sys.argv[1]))
