@@ -53,3 +53,39 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         native.library()
     assert info.value.stage == "native_loading"
     monkeypatch.setattr(native, "_LIBRARY", None)
+
+
+def declared_slot_counts():
+    """Number of C parameters of every declared entry, with the view macros expanded
+    (a view of rank r is a pointer, r extents and r strides)."""
+    text = (ROOT / "include" / "intent_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S).replace("\\\n", " ")
+    macros = dict(re.findall(r"#define\s+(INTENT_B200_\w+_SLOTS)\s+(.*)", text))
+    counts = {}
+    for name, arguments in re.findall(r"INTENT_B200_API\s+[\w\s\*]+?\b(intent_b200_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        for macro, body in macros.items():
+            arguments = arguments.replace(macro, body)
+        total = 0
+        for argument in (a.strip() for a in re.split(r",(?![^()]*\))", arguments)):
+            view = re.match(r"INTENT_B200_VIEW(\d)\(", argument)
+            total += 1 + 2 * int(view.group(1)) if view else (0 if argument in ("", "void") else 1)
+        counts[name] = total
+    return counts
+
+
+def test_programs_marshal_what_the_header_declares():
+    """Every shipped program passes exactly the slots its C entry declares: views, compile-time
+    constants, the optional workspace pair and the stream."""
+    import intent_b200 as ib
+
+    declared = declared_slot_counts()
+    assert declared["intent_b200_gemm_i8"] == 5 + 5 + 3 + 5 + 1
+    checked = 0
+    for definition in ib.programs.ALL.values():
+        artifact = ib.compile(definition, resolve_target=False)
+        program = artifact.runtime
+        slots = len(program._carriers_head) + (2 if program._workspace_spec is not None else 0) + 1
+        assert program.entry_name in declared, program.entry_name
+        assert declared[program.entry_name] == slots, (definition.name, program.entry_name, declared[program.entry_name], slots)
+        checked += 1
+    assert checked == len(ib.programs.ALL) >= 29
