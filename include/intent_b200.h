@@ -40,6 +40,8 @@ enum intent_b200_status {
   INTENT_B200_ERR_WORKSPACE = 5,    /* workspace missing or too small */
   INTENT_B200_ERR_NULL = 6,         /* a required pointer is NULL */
   INTENT_B200_ERR_SCRATCH_LIMIT = 7,/* problem needs more scratch than the built-in array of a no-allocation entry */
+  INTENT_B200_ERR_INDEX = 8,        /* an index read from device memory (an expert id) was out of range; the rows it
+                                       governs were computed with zero weights (read back from the status word) */
   INTENT_B200_ERR_CUDA = 1000       /* 1000 + cudaError_t of a failed runtime call */
 };
 
@@ -69,16 +71,21 @@ INTENT_B200_API int64_t intent_b200_launch_count(void);
  *   zero_point: -1 = two's-complement nibble (the reference's decoding),
  *                8 = unsigned nibble minus 8 (benchmark configurations)
  * Y[m,n] = T( sum_k f32(X[m,k]) * f32(w[k,n]) ), f32 accumulation.
- * The plain entries pick the kernel from M (bandwidth kernel for M <= 32,
+ * K must be positive (an empty contraction returns INTENT_B200_ERR_UNSUPPORTED;
+ * M == 0 or N == 0 succeed without a launch).
+ * The plain entries pick the kernel from M (bandwidth kernel for M <= 16,
  * tcgen05 tensor-core kernel above); the _gemv / _gemm entries force one.
  *
  * workspace: device scratch of at least ..._workspace_bytes(M, K, N) bytes,
  * 16-byte aligned (NULL / 0 when that query returns 0).  It must be zero-filled
- * once after allocation; every launch leaves it zero-filled again, so it can be
- * reused by later launches on the SAME stream.  Launches that may overlap on
- * the GPU (different streams) need separate workspaces.  Byte 0..3 is a status
- * word: a launch whose bounded device wait expired stores INTENT_B200_ERR_TIMEOUT
- * there.
+ * once after allocation; every launch that ends with status word 0 leaves it
+ * zero-filled again, so it can be reused by later launches on the SAME stream.
+ * Launches that may overlap on the GPU (different streams) need separate
+ * workspaces.  Byte 0..3 is a status word: a launch whose bounded device wait
+ * expired stores INTENT_B200_ERR_TIMEOUT there, stops early (parts of the output
+ * are then unwritten) and leaves ticket counters behind, so the workspace must
+ * not be reused as it is.  intent_b200_w4a16_gemv_workspace_status reads the
+ * word and, when it is set, clears the workspace for reuse.
  * ------------------------------------------------------------------------ */
 #define INTENT_B200_W4A16_SLOTS                                                                   \
   INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),     \
@@ -91,8 +98,13 @@ INTENT_B200_API int intent_b200_w4a16_gemm_f16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int intent_b200_w4a16_gemm_bf16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N);
 INTENT_B200_API int64_t intent_b200_w4a16_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N);
-/* Status word of the tensor-core W4A16 kernel: 0, or INTENT_B200_ERR_TIMEOUT if a bounded
- * device-side wait expired in an earlier launch.  Synchronises the device and clears the word. */
+/* Synchronises `stream`, returns the status word of a bandwidth-kernel workspace (0 or
+ * INTENT_B200_ERR_TIMEOUT) and, when it is set, zero-fills the workspace again so that it can be reused.
+ * Call it wherever the host synchronises anyway (end of a decode step, before results are consumed). */
+INTENT_B200_API int intent_b200_w4a16_gemv_workspace_status(void* workspace, int64_t workspace_bytes, void* stream);
+/* Status word of the tensor-core W4A16 kernels (single-CTA and CTA-pair): 0, INTENT_B200_ERR_TIMEOUT if a
+ * bounded device-side wait expired in an earlier launch, or INTENT_B200_ERR_INDEX if a grouped entry met an
+ * expert id outside [0, E).  Synchronises the device and clears the word. */
 INTENT_B200_API int intent_b200_w4a16_gemm_device_status(void);
 /* Dense W4A16 with M >= 512 runs on CTA pairs (tcgen05 cta_group::2); 0 forces the single-CTA kernel.
  * For measurement and tests; process-global. */
@@ -334,11 +346,16 @@ INTENT_B200_API int intent_b200_quantized_projection(INTENT_B200_VIEW3(a0), INTE
  *     the GPU (different streams, or different host threads on unordered
  *     streams) race on it and produce wrong results.  Order them on one
  *     stream or use the workspace entries.
+ *   - A bounded device wait that expired is recorded in the array's first word;
+ *     intent_b200_w4a16_gemv_builtin_scratch_status(stream) synchronises the
+ *     stream and returns it (0 = fine).  Read it before the next call of the
+ *     entry on that device: each call clears the word.
  * ------------------------------------------------------------------------ */
 INTENT_B200_API int intent_b200_w4a16_gemv_f16_builtin_scratch(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
                                                                INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
                                                                int32_t group_size, int32_t zero_point,
                                                                void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemv_builtin_scratch_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -61,8 +61,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         done = subprocess.run(command, capture_output=True, text=True)
         if done.returncode != 0:
             raise RuntimeError(f"nvcc failed for {source.name}:\n{done.stdout}\n{done.stderr}")
+        # Compiler warnings are never dropped.  One of them is fatal here: without relocatable device code
+        # an `extern __device__` declaration silently becomes a private definition (#20044), so a status
+        # word "shared" between two files would be two words.
+        warnings = [line for line in done.stderr.splitlines() if "warning" in line.lower()]
+        if any("20044" in line for line in warnings):
+            raise RuntimeError(f"{source.name}: extern device variable without relocatable device code:\n"
+                               + done.stderr)
         if verbose:
             sys.stderr.write(done.stderr)
+        elif warnings:
+            sys.stderr.write(f"[{source.name}]\n" + "\n".join(warnings) + "\n")
         return source
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:

@@ -32,6 +32,7 @@ extern "C" const char* intent_b200_status_string(int status) {
     case INTENT_B200_ERR_WORKSPACE: return "workspace missing or too small";
     case INTENT_B200_ERR_NULL: return "null pointer";
     case INTENT_B200_ERR_SCRATCH_LIMIT: return "problem exceeds the built-in scratch of the no-allocation entry";
+    case INTENT_B200_ERR_INDEX: return "an index read from device memory was out of range";
     default: break;
   }
   if (status >= INTENT_B200_ERR_CUDA) return cudaGetErrorString(static_cast<cudaError_t>(status - INTENT_B200_ERR_CUDA));

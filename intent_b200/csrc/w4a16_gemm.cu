@@ -50,6 +50,7 @@ __device__ int g_w4a16_gemm_status = 0;
 template <typename T>
 int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
                     int group_size, int zero_point, cudaStream_t stream);
+int w4a16_gemm_pair_take_status(int* value);
 
 namespace {
 
@@ -89,6 +90,8 @@ struct GemmParams {
   const int* tile_expert;    // grouped modes: expert of each (MT*128)-row block; of each 128-row block with pair_blocks
   int pair_blocks;           // grouped modes, MT = 2: rows are padded to 128 per expert and the kernel pairs
                              // neighbouring blocks of one expert itself (an odd last block runs as half a tile)
+  int experts;               // grouped modes: E; a block whose expert id is outside [0, E) is computed with zero
+                             // weights and recorded as INTENT_B200_ERR_INDEX
 };
 
 constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
@@ -383,10 +386,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
         tile_coords(f_tile, m_tiles, p.n_tiles, m_tile, n_tile);
         int first_block, halves;
         tile_blocks(m_tile, first_block, halves);
-        const int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[(CAN_PAIR && paired) ? first_block : m_tile];
+        int expert = MODE == MODE_DENSE ? 0 : p.tile_expert[(CAN_PAIR && paired) ? first_block : m_tile];
         const int col = (MODE == MODE_UPGATE_SILU ? n_tile * 128 : n_tile * BN) +
                         (n < 128 ? n : p.second_half_offset + (n - 128));
         f_col_ok = col < p.WN;
+        if (MODE != MODE_DENSE && unsigned(expert) >= unsigned(p.experts)) {
+          // an id that names no expert (a stale or sentinel table entry): never used as an index
+          if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_INDEX);
+          f_col_ok = false;
+          expert = 0;
+        }
         f_w = p.packed + size_t(expert) * packed_rows * p.WN + (f_col_ok ? col : 0);
         f_s = p.scales + size_t(expert) * scale_rows * p.WN + (f_col_ok ? col : 0);
       }
@@ -478,7 +487,7 @@ int device_sms() {
 template <typename T, int MODE, int MT>
 int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t WN, void* out,
                 int64_t out_cols, int group_size, int zero_point, const int* total_rows, const int* tile_expert,
-                cudaStream_t stream, bool pair_blocks = false) {
+                cudaStream_t stream, bool pair_blocks = false, int64_t experts = 1) {
   const int sms = device_sms();
   if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
   const CUtensorMapDataType type =
@@ -500,6 +509,7 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
   p.total_rows = total_rows;
   p.tile_expert = tile_expert;
   p.pair_blocks = pair_blocks ? 1 : 0;
+  p.experts = int(experts);
 
   CUtensorMap map_x;
   if (!make_tensor_map_2d(&map_x, type, x, uint64_t(rows), uint64_t(K), uint64_t(K) * 2, BM, BK,
@@ -565,9 +575,10 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
   if (block_rows == 2 * BM || (P + BM - 1) / BM <= PAIR_LIST_BLOCKS)   // 128-row blocks are paired by the kernel
     return launch_gemm<T, MODE, 2>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
                                    static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream,
-                                   block_rows == BM);
+                                   block_rows == BM, E);
   return launch_gemm<T, MODE, 1>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
-                                 static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream);
+                                 static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream,
+                                 false, E);
 }
 
 }  // namespace
@@ -582,15 +593,18 @@ int w4a16_gemm_bf16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStrea
 }
 }  // namespace ib200
 
-// Reads (and clears) the status word of the tensor-core W4A16 kernel; synchronises the device.
+// Reads (and clears) the status words of the tensor-core W4A16 kernels - the single-CTA kernel of this
+// file and the CTA-pair kernel, which keeps its own word - and synchronises the device.
 extern "C" int intent_b200_w4a16_gemm_device_status(void) {
-  int value = 0, zero = 0;
+  int value = 0, pair_value = 0, zero = 0;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return ib200::cuda_status(e);
   e = cudaMemcpyFromSymbol(&value, ib200::g_w4a16_gemm_status, sizeof(int));
   if (e != cudaSuccess) return ib200::cuda_status(e);
   if (value != 0) cudaMemcpyToSymbol(ib200::g_w4a16_gemm_status, &zero, sizeof(int));
-  return value;
+  const int status = ib200::w4a16_gemm_pair_take_status(&pair_value);
+  if (status != INTENT_B200_OK) return status;
+  return value != 0 ? value : pair_value;
 }
 
 #define IB200_GROUPED_ENTRY(NAME, TYPE, MODE)                                                                   \

@@ -26,7 +26,10 @@
 
 namespace ib200 {
 
-extern __device__ int g_w4a16_gemm_status;
+// Status word of this translation unit's kernel (device variables are private to the file they are
+// defined in unless the library is built with relocatable device code, which it is not); read and
+// cleared by w4a16_gemm_pair_take_status below.
+__device__ int g_w4a16_pair_status = 0;
 
 namespace {
 
@@ -178,7 +181,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
             tma_load_2d_pair(smem_a + (s * MT + mt) * A_BYTES, &map_x, kb * BK, row0 + mt * BM, leader_bar);
         }
       }
-      if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+      if (!ok) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) --------------------------
@@ -194,7 +197,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
         if (!mbar_wait(full_b + 8 * t, (it / B_STAGES) & 1)) { ok = false; break; }
         mbar_arrive_cluster(leader_full_b + 8 * t);
       }
-      if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+      if (!ok) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
     }
     if (lane == 0 && rank == 0) {
       constexpr uint32_t fmt = std::is_same<T, __half>::value ? 0u : 1u;
@@ -223,7 +226,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
         }
         if (ok) umma_commit_pair(tmem_full);
       }
-      if (!ok) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+      if (!ok) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
     }
   } else if (warp < 6) {
     // ------------------------------ epilogue (both CTAs, own TMEM) -------------------------
@@ -235,7 +238,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       int m_tile, n_tile;
       pair_tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
       if (!__all_sync(0xffffffffu, mbar_wait(tmem_full, local & 1))) {
-        if (lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+        if (lane == 0) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
         break;
       }
       tcgen05_fence_after();
@@ -368,7 +371,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       consume(i + 2, b2);
       fetch(b2);
     }
-    if (!ok && lane == 0) atomicExch(&g_w4a16_gemm_status, INTENT_B200_ERR_TIMEOUT);
+    if (!ok && lane == 0) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
   }
 
   tcgen05_fence_before();
@@ -421,6 +424,19 @@ int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const vo
   kernel<<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(map_x, p);
   note_launch();
   return launch_status();
+}
+
+// Reads the pair kernel's status word into *value and clears it when it was set (the caller has
+// synchronised the device).
+int w4a16_gemm_pair_take_status(int* value) {
+  const int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(value, g_w4a16_pair_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e);
+  if (*value != 0) {
+    e = cudaMemcpyToSymbol(g_w4a16_pair_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e);
+  }
+  return INTENT_B200_OK;
 }
 
 template int w4a16_gemm_pair<__half>(const void*, int64_t, int64_t, const void*, const void*, int64_t, void*, int, int,

@@ -123,7 +123,6 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // then every K chunk of the column tiles it owns whole, which are reduced in shared memory.
   const int grid = int(gridDim.x);
   const int left_base = p.own_tiles * int(grid) * p.chunks;   // first unit of the K-split tiles
-  const int left_total = p.units - left_base;
   // quotient and remainder come from the host: no division on the way to the first load
   const int l0 = int(blockIdx.x) * p.left_each + min(int(blockIdx.x), p.left_extra);
   const int l1 = l0 + p.left_each + (int(blockIdx.x) < p.left_extra ? 1 : 0);
@@ -738,6 +737,30 @@ extern "C" int intent_b200_w4a16_gemv_warps(int32_t warps) {
   return INTENT_B200_OK;
 }
 
+// Reads the status word at the head of a bandwidth-kernel workspace after synchronising `stream`.  When a
+// launch gave up on a bounded wait its warps stopped early: tickets were left untaken and parts of Y
+// unwritten, so the workspace is no longer zero-filled.  In that case the whole workspace is cleared
+// again (and the stream synchronised once more) before the code is returned, so the next launch starts
+// from a clean one.
+static int take_workspace_status(void* workspace, int64_t bytes, cudaStream_t stream) {
+  if (!workspace || bytes < 4) return INTENT_B200_ERR_WORKSPACE;
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return ib200::cuda_status(e);
+  int value = 0;
+  e = cudaMemcpy(&value, workspace, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return ib200::cuda_status(e);
+  if (value != 0) {
+    e = cudaMemsetAsync(workspace, 0, size_t(bytes), stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return ib200::cuda_status(e);
+  }
+  return value;
+}
+
+extern "C" int intent_b200_w4a16_gemv_workspace_status(void* workspace, int64_t workspace_bytes, void* stream) {
+  return take_workspace_status(workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 // ---------------------------------------------------------------------------------
 // Entry point that performs no allocation at all.
 //
@@ -775,6 +798,15 @@ static int builtin_scratch_address(void** address) {
 }
 
 }  // namespace ib200
+
+// Status of the latest call of the no-allocation entry on the current device (see the header): must be read
+// before the next call of that entry, which clears the word.
+extern "C" int intent_b200_w4a16_gemv_builtin_scratch_status(void* stream) {
+  void* scratch = nullptr;
+  const int status = ib200::builtin_scratch_address(&scratch);
+  if (status != INTENT_B200_OK) return status;
+  return take_workspace_status(scratch, int64_t(ib200::kBuiltinScratchBytes), static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int intent_b200_w4a16_gemv_f16_builtin_scratch(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
                                                           INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),

@@ -134,16 +134,34 @@ class PeerSignals:
     ``peer_flags`` the int64 table of every rank's array, ``peer_tables`` the table of every rank's count
     matrix.  Channel 0 carries the per-expert counts, channels 1 and 2 are plain barriers.  The waits are
     bounded (``max_polls`` polls about a microsecond apart: the default rides out a rank that is still loading
-    its kernels, roughly 20 s); ``status`` holds a timeout code if one gave up."""
+    its kernels, roughly 20 s); ``status`` holds a timeout code if one gave up.
+
+    The sequence counters must live exactly as long as the flag arrays they are compared with: flags keep the
+    numbers of every earlier step, so counters that restart at zero would be behind the flags and every wait
+    would pass without waiting.  Whoever owns the flag arrays therefore owns one ``sequence`` (and ``status``)
+    tensor and hands the same one to every ``PeerSignals`` built on those flags; a ``PeerSignals`` only binds a
+    step's payload (its per-expert counts) to them."""
 
     CHANNELS = 3
 
-    def __init__(self, *, rank, world, flags, peer_flags, peer_tables, counts, target=None, max_polls=1 << 24):
+    @classmethod
+    def counters(cls, device):
+        """(sequence, status) for one flag array: zero exactly when the flags are zero."""
+        import torch
+
+        return (torch.zeros((2 * cls.CHANNELS,), dtype=torch.int32, device=device),
+                torch.zeros((1,), dtype=torch.int32, device=device))
+
+    def __init__(self, *, rank, world, flags, peer_flags, peer_tables, counts, target=None, max_polls=1 << 24,
+                 sequence=None, status=None):
         import torch
 
         device = flags.device
-        self.flags, self.status = flags, torch.zeros((1,), dtype=torch.int32, device=device)
-        self.sequence = torch.zeros((2 * self.CHANNELS,), dtype=torch.int32, device=device)
+        if (sequence is None) != (status is None):
+            raise ValueError("pass both sequence and status (PeerSignals.counters) or neither")
+        if sequence is None:      # a flag array used by this object alone (it must still be all zero)
+            sequence, status = self.counters(device)
+        self.flags, self.status, self.sequence = flags, status, sequence
         none = torch.empty((0,), dtype=torch.int64, device=device)
         self.posts, self.waits = [], []
         for channel in range(self.CHANNELS):
@@ -175,7 +193,7 @@ class PeerExpertParallelMoE:
     ``signals='nccl'``: an all-gather and two one-word all-reduces."""
 
     def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
-                 act_dtype="bf16", block_rows=128, target=None, group=None, signals="peer"):
+                 act_dtype="bf16", block_rows=128, target=None, group=None, signals="peer", max_polls=1 << 24):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symmetric
@@ -221,6 +239,10 @@ class PeerExpertParallelMoE:
                                             device=device)
             self.peer_flags = torch.tensor([t.data_ptr() for t in self._peer_flags], dtype=torch.int64,
                                            device=device)
+            # one pair of counters for the life of the flag arrays: every prepared step continues the same
+            # sequence, so a second prepare() (or every __call__) still waits for the other ranks
+            self._sequence, self._status = PeerSignals.counters(device)
+            self._max_polls = max_polls
         # every rank's buffers are cleared before any rank may write into them
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
@@ -239,7 +261,8 @@ class PeerExpertParallelMoE:
         signals = None
         if self.signals == "peer":
             signals = PeerSignals(rank=self.rank, world=self.world, flags=self.flags, peer_flags=self.peer_flags,
-                                  peer_tables=self.peer_counts, counts=step.counts, target=self._target)
+                                  peer_tables=self.peer_counts, counts=step.counts, target=self._target,
+                                  max_polls=self._max_polls, sequence=self._sequence, status=self._status)
         return PreparedPeerStep(self, step, signals)
 
     def __call__(self, logits, x, up_gate_packed, up_gate_scales, down_packed, down_scales):

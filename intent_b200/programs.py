@@ -79,7 +79,9 @@ def _lower_w4a16(constants, device):
 
     return NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
                          constants=(group, zp), device=device, workspace=workspace_bytes,
-                         empty=lambda d: d["M"] == 0 or d["N"] == 0)
+                         empty=lambda d: d["M"] == 0 or d["N"] == 0,
+                         workspace_status="intent_b200_w4a16_gemv_workspace_status",
+                         device_status=() if kernel == "gemv" else ("intent_b200_w4a16_gemm_device_status",))
 
 
 weight_only_int4_matmul = KernelDefinition(

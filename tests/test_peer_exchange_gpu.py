@@ -127,6 +127,46 @@ def test_peer_wait_gives_up(cuda_device):
     assert torch.equal(torch.ones(1, device=cuda_device), torch.ones(1, device=cuda_device))   # context is usable
 
 
+def test_second_prepared_step_still_waits(cuda_device):
+    """Two steps bound one after the other to the same flag array must continue one sequence: the flags keep
+    the first step's numbers, so counters that restarted at zero would let every wait of the second step pass
+    at once.  With the shared counters the second step's wait runs out when the other rank has not posted
+    again (bounded wait, a flag that nothing sets)."""
+    from intent_b200.peer import PeerSignals
+
+    world = 2
+    flags = torch.zeros((PeerSignals.CHANNELS, world), dtype=torch.int32, device=cuda_device)
+    other = torch.zeros_like(flags)
+    peer_flags = torch.tensor([flags.data_ptr(), other.data_ptr()], dtype=torch.int64, device=cuda_device)
+    table = torch.zeros((world, 8), dtype=torch.int32, device=cuda_device)
+    peer_tables = torch.tensor([table.data_ptr(), table.data_ptr()], dtype=torch.int64, device=cuda_device)
+    counts = torch.arange(8, dtype=torch.int32, device=cuda_device)
+    sequence, status = PeerSignals.counters(cuda_device)
+    common = dict(rank=0, world=world, flags=flags, peer_flags=peer_flags, peer_tables=peer_tables, counts=counts,
+                  target=ib.B200Target(0), max_polls=2000, sequence=sequence, status=status)
+    first = PeerSignals(**common)
+    flags[:, 1] = 1                      # "rank 1" posts its first step on every channel
+    for channel in range(PeerSignals.CHANNELS):
+        first.post(channel)
+        first.wait(channel)
+    torch.cuda.synchronize()
+    first.check()
+    second = PeerSignals(**common)       # what a second prepare() on the same exchange builds
+    assert second.sequence.data_ptr() == first.sequence.data_ptr()
+    second.post(1)
+    second.wait(1)                       # rank 1 has not posted its second step
+    torch.cuda.synchronize()
+    assert sequence.tolist() == [1, 1, 2, 2, 1, 1]
+    with pytest.raises(RuntimeError, match="expired"):
+        second.check()
+    flags[1, 1] = 2                      # now it has
+    second.post(1)                       # (a retry after the failure: number 3 here, rank 1 must follow)
+    flags[1, 1] = 3
+    second.wait(1)
+    torch.cuda.synchronize()
+    second.check()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -163,6 +203,16 @@ def _peer_worker(rank, world, port, results):
                 call.check()
                 t_local = tokens // world
                 ok = ok and bool(torch.equal(call.y, expected[rank * t_local:(rank + 1) * t_local]))
+            # a second bound step and the unprepared call share the exchange's flags and counters
+            again = ep.prepare(logits, x, *w)
+            again.launch()
+            torch.cuda.synchronize()
+            again.check()
+            ok = ok and bool(torch.equal(again.y, expected[rank * t_local:(rank + 1) * t_local]))
+            for _ in range(2):
+                y = ep(logits, x, *w)
+                torch.cuda.synchronize()
+                ok = ok and bool(torch.equal(y, expected[rank * t_local:(rank + 1) * t_local]))
         results[rank] = ok
         dist.barrier()
     finally:

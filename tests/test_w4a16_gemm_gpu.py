@@ -73,11 +73,50 @@ def test_gemm_full_size_prefill_rows(cuda_device):
     torch.cuda.synchronize()
     assert _device_status() == 0
     assert torch.equal(doubled, out * 2)
-    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 6000, 8191])
+    # 80 rows: five in each of the 16 pair tiles of 512 rows - first and last row of the tile, and rows of
+    # both CTAs of the pair (each owns 256 rows) and of both of their 128-row blocks
+    rows = torch.cat([torch.tensor([0, 130, 255, 300, 511]) + 512 * tile for tile in range(16)])
     ref = oracle.weight_only_int4_matmul(x[rows], p, s, group_size=128, zero_point=8)
     assert max_abs_rel(out[rows.to(cuda_device)].cpu(), ref) <= 2e-2
+    # a column checksum over ALL rows: sum_m y[m, :] = (sum_m x[m, :]) @ W', W' being the dequantised weight
+    # rounded to bf16 as the kernel rounds it.  What remains is the rounding of the 8192 outputs of a column
+    # (each about 4 in magnitude, 2^-9 relative: 0.4 rms in the sum); a 512-row tile that was skipped or
+    # doubled would move its columns' sums by about 100.
+    column_sum = out.float().sum(dim=0).cpu()
+    signed = (oracle.unpack_int4(p) - 8).to(torch.bfloat16)
+    weight = (signed * s.repeat_interleave(128, dim=0)).float()
+    expected_sum = x.float().sum(dim=0) @ weight
+    assert (column_sum - expected_sum).abs().max() <= 5.0
     # every tile was written: no element is left at the fill value
     assert torch.isfinite(out).all()
+
+
+def test_reference_case_on_cta_pairs(cuda_device):
+    """The reference's own W4A16 case at its own size (M512 K2048 N4096, group 64, signed nibbles, f16;
+    experiments/cpu/providers/mojo/contraction.py:190-198): this is the CTA-pair kernel in two's-complement
+    mode.  Checked against stored rows of the reference module's output at the reference's atol = 4e-2,
+    against the oracle on every row, and at the benchmark's 2e-2 * max|ref|."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("golden_generate", Path(__file__).parent / "golden" / "generate.py")
+    generate = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(generate)
+    g = load_golden("w4a16_reference_case_rows")
+    activation, packed, scales = generate.reference_case_inputs()
+    assert torch.equal(generate.digest(packed), g["packed_digest"])
+    for kernel in ("auto", "gemm"):
+        artifact = _compile("f16", 64, "twos_complement", kernel)
+        out = artifact.run(activation.to(cuda_device), packed.to(cuda_device), scales.to(cuda_device))
+        torch.cuda.synchronize()
+        assert _device_status() == 0
+        out = out.cpu()
+        rows = g["rows"].long()
+        assert (out[rows].float() - g["output_rows"].float()).abs().max() <= 4e-2
+        ref = oracle.weight_only_int4_matmul(activation, packed, scales)          # reference defaults
+        assert (out.float() - ref.float()).abs().max() <= 4e-2
+        assert max_abs_rel(out, ref) <= 2e-2
+        assert max_abs_rel(out, ref) <= 2e-3          # what the kernel really achieves on f16
 
 
 @pytest.mark.parametrize("M,K,N", [(512, 512, 256), (1100, 1024, 776), (2048, 2048, 2048)])

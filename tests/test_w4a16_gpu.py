@@ -105,6 +105,43 @@ def test_workspace_stays_clean_and_status_word_is_zero(cuda_device):
     assert not header.any()                                         # ticket counters are back at zero
 
 
+def test_timeout_status_is_reported_and_the_workspace_recovered(cuda_device):
+    """What the host sees after a launch whose bounded wait expired, made on the host: the status word and
+    a ticket counter of a prepared call's workspace are set by hand (no kernel is made to time out).
+    ``check()`` must raise with the timeout status and leave the workspace zero-filled, and the next launch
+    must give the right result again."""
+    x, p, s = ib.workloads.w4a16_inputs(4, 4096, 256, dtype=torch.float16, seed=6)
+    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
+    artifact = _compile("f16", 128, 8, "gemv")
+    call = artifact.prepare(xd, pd, sd)
+    call.launch()
+    call.check()                                                  # a clean launch: nothing to report
+    expected = call.result().clone()
+    (workspace,) = call._workspace
+    words = workspace.view(torch.int32)
+    words[0] = 4                                                  # INTENT_B200_ERR_TIMEOUT
+    words[64 + 1] = 3                                             # an abandoned ticket counter (offset 256 bytes)
+    with pytest.raises(ib.CompilationStageError) as info:
+        call.check()
+    assert info.value.stage == "provider_invocation" and info.value.status == 4
+    assert not workspace.any()                                    # cleared for reuse
+    call.check()
+    call.result().zero_()
+    call.launch()
+    call.check()
+    assert torch.equal(call.result(), expected)
+    # the unprepared path reuses one workspace per stream: artifact.check() covers it
+    y = artifact.run(xd, pd, sd)
+    artifact.check()
+    assert torch.equal(y, expected)
+    cached = next(iter(artifact.runtime._stream_workspaces.values()))
+    cached.view(torch.int32)[0] = 4
+    with pytest.raises(ib.CompilationStageError):
+        artifact.check()
+    assert not cached.any()
+    assert torch.equal(artifact.run(xd, pd, sd), expected)
+
+
 def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
     x, p, s = ib.workloads.w4a16_inputs(4, 1024, 256, dtype=torch.float16, seed=2)
     xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)

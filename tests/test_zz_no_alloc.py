@@ -62,6 +62,11 @@ def test_builtin_scratch_matches_workspace_entry_twice(cuda_device, M, K, N):
         # same kernel, same summation order: the benchmark tolerance holds trivially, the bits agree
         assert max_abs_rel(got.cpu(), expected.cpu()) <= 2e-2
         assert torch.equal(got, expected)
+        # no bounded wait gave up inside the call (the word lives in the built-in array and is only valid
+        # until the next call of the entry clears it)
+        reader = native.library().intent_b200_w4a16_gemv_builtin_scratch_status
+        reader.restype, reader.argtypes = ctypes.c_int, [ctypes.c_void_p]
+        assert reader(stream) == 0
         outputs.append(got)
     assert not torch.equal(outputs[0], outputs[1])      # the two calls really had different inputs
 
