@@ -6,16 +6,17 @@
 // examples/kernels/contraction/weight_only_int4.py:18-51 (the dequantised weight is
 // rounded to the activation type before the f32-accumulated product, as at :42-47).
 //
-// One persistent CTA per SM walks output tiles of (MT * 128) rows x 256 columns; 14 warps in
+// One persistent CTA per SM walks output tiles of (MT * 128) rows x 256 columns; 22 warps in
 // four roles:
 //   warp 0        TMA producer: per 64-wide k block MT 128B-swizzled boxes of X (128 rows x 64 k).
-//   warps 6..13   dequantisers: thread n owns weight column n of the tile.  It reads its packed
-//                 words straight from global memory (a warp reads 128 contiguous bytes per packed
-//                 row; three k blocks are kept in flight in registers), expands the 8 words of a
-//                 k block to 64 values of T with the magic-number trick (prmt + lop3, exact
-//                 subtract, one rounding multiply by the scale) and writes them as the 128-byte
-//                 row n of the K-major, 128B-swizzled B operand tile.  Shared memory therefore
-//                 carries each weight once (the operand tile), not twice.
+//   warps 6..21   dequantisers: two threads per weight column of the tile, each expanding half of
+//                 the k block (four packed words).  A thread reads its packed words straight from
+//                 global memory (a warp reads 128 contiguous bytes per packed row; three k blocks
+//                 are kept in flight in registers), expands them to values of T with the
+//                 magic-number trick (prmt + lop3, exact subtract, one rounding multiply by the
+//                 scale) and writes them into the 128-byte row n of the K-major, 128B-swizzled B
+//                 operand tile.  Shared memory therefore carries each weight once (the operand
+//                 tile), not twice.
 //   warp 1        MMA issuer: one thread issues, per k block, four tcgen05.mma (M128 N256 K16,
 //                 kind::f16, f32 accumulation in TMEM) for each of the MT row blocks - the row
 //                 blocks share the dequantised B tile - and commits to the mbarriers that free

@@ -12,8 +12,8 @@
 // CTAs.  Per flop each CTA therefore expands a quarter of the int4 weights that a lone
 // 128 x 256 CTA would, which is what bounded the single-CTA kernel.
 //
-// Roles per CTA (14 warps): warp 0 TMA producer (its own rows of X; the transaction bytes of
-// both CTAs complete on the leader's mbarrier), warps 6..13 dequantisers (thread = weight column
+// Roles per CTA (22 warps): warp 0 TMA producer (its own rows of X; the transaction bytes of
+// both CTAs complete on the leader's mbarrier), warps 6..21 dequantisers (thread = weight column
 // x half of the k block; packed words straight from global memory, three k blocks ahead), warps
 // 2..5 epilogue (own TMEM lanes).  Only the leader CTA (cluster rank 0) issues MMAs (one thread
 // of warp 1); its commits arrive on the stage barriers of both CTAs.

@@ -28,12 +28,15 @@
 // (which removes the magic bias and the zero point), one FMA with the group
 // scale per accumulator and group.
 //
-// Reduction over K: inside the MMA and the warp's registers for one unit; across
-// units through a global scratch buffer: a warp stores the unit's partial
-// [M x 32] f32, fences, and takes a ticket on the column tile's counter; the
-// warp that takes the last ticket adds the tile's partials in chunk order and
-// writes Y.  No CTA-wide barrier after start-up, no spin waits between CTAs, a
-// fixed summation order => bitwise reproducible.
+// Reduction over K: inside the MMA and the warp's registers for one unit.  Across
+// units: column tiles a CTA owns whole are summed in its shared memory (per-unit
+// partials [M x 32] f32, a shared ticket counter, the warp with the last ticket adds
+// them in chunk order and writes Y).  A tile that is split over K between CTAs is
+// first summed per CTA in shared memory the same way; each CTA then publishes ONE
+// partial of the tile to global scratch, fences and takes a ticket on the tile's
+// global counter, and the warp that takes the last ticket adds those two or three
+// partials in CTA order and writes Y.  No CTA-wide barrier after start-up, no spin
+// waits between CTAs, a fixed summation order => bitwise reproducible.
 #include <mutex>
 #include <type_traits>
 

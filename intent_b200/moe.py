@@ -20,54 +20,53 @@ from .compiler import compile as _compile
 from .targets import B200Target
 
 
-@dataclass
+_ALIGN_STAGES = ("moe_count_routes", "moe_prefix_routes", "moe_scatter_routes", "moe_mark_expert_blocks")
+
+
 class MoEAlignmentCall:
-    count: object
-    prefix: object
-    scatter: object
-    mark: object
-    sorted_routes: object
-    expert_blocks: object
-    total_padded: object
-    counts: object
-    cursors: object
-    routes: int
+    """The four alignment launches bound to fixed buffers.  ``launch()`` clears the per-expert counters,
+    refills the route list with the padding sentinel and replays the launches; ``result()`` is
+    ``(sorted_route_ids, expert_blocks, total_padded)`` like the unbound forms."""
+
+    def __init__(self, stages, counters, sorted_routes, expert_blocks, total_padded, sentinel):
+        self.stages = tuple(stages)
+        self._counters = counters                      # counts | cursors in one buffer: one clear per launch
+        half = counters.numel() // 2
+        self.counts, self.cursors = counters[:half], counters[half:]
+        self.sorted_routes, self.expert_blocks, self.total_padded = sorted_routes, expert_blocks, total_padded
+        self.routes = sentinel
 
     def compile(self):
-        for call in (self.count, self.prefix, self.scatter, self.mark):
-            call.compile()
+        for stage in self.stages:
+            stage.compile()
 
     def launch(self):
-        self.counts.zero_()
-        self.cursors.zero_()
+        self._counters.zero_()
         self.sorted_routes.fill_(self.routes)
-        self.count.launch()
-        self.prefix.launch()
-        self.scatter.launch()
-        self.mark.launch()
+        for stage in self.stages:
+            stage.launch()
 
     def result(self):
         return self.sorted_routes, self.expert_blocks, self.total_padded
 
 
-@dataclass
 class MoEAlignment:
-    count: object
-    prefix: object
-    scatter: object
-    mark: object
-    tokens: int = 4096
-    top_k: int = 2
-    experts: int = 64
-    block_size: int = 128
+    """Host composition of the route alignment, with the reference's surface
+    (examples/programs/composition.py:98-174: ``build`` / ``run`` / ``run_into`` / ``prepare``, results
+    ``(sorted_route_ids, expert_blocks, total_padded)``, padding sentinel = number of routes).  The stages
+    are the four alignment programs compiled with this object's token / top-k / expert / block constants
+    (the reference fixes them at module level; here they are constructor arguments)."""
+
+    def __init__(self, count, prefix, scatter, mark, tokens=4096, top_k=2, experts=64, block_size=128):
+        self.count, self.prefix, self.scatter, self.mark = count, prefix, scatter, mark
+        self.tokens, self.top_k, self.experts, self.block_size = tokens, top_k, experts, block_size
 
     @classmethod
     def build(cls, *, tokens=4096, top_k=2, experts=64, block_size=128, target=None, resolve_target=True):
-        constexprs = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": block_size}
-        artifacts = [_compile(definition, target=target, constexprs=constexprs, resolve_target=resolve_target)
-                     for definition in (programs.moe_count_routes, programs.moe_prefix_routes,
-                                        programs.moe_scatter_routes, programs.moe_mark_expert_blocks)]
-        return cls(*artifacts, tokens=tokens, top_k=top_k, experts=experts, block_size=block_size)
+        constants = {"TOKENS": tokens, "TOP_K": top_k, "EXPERTS": experts, "BLOCK_SIZE": block_size}
+        stages = [_compile(getattr(programs, name), target=target, constexprs=constants,
+                           resolve_target=resolve_target) for name in _ALIGN_STAGES]
+        return cls(*stages, tokens=tokens, top_k=top_k, experts=experts, block_size=block_size)
 
     @property
     def routes(self) -> int:
@@ -75,44 +74,45 @@ class MoEAlignment:
 
     @property
     def padded_routes(self) -> int:
+        # every expert span may need up to block_size - 1 padding entries
         return self.routes + self.experts * (self.block_size - 1)
 
-    def _validate_ids(self, ids):
-        if len(ids.shape) != 2 or ids.shape[1] != self.top_k or ids.shape[0] > self.tokens:
+    def _check(self, ids):
+        if ids.dim() != 2 or ids.shape[1] != self.top_k or ids.shape[0] > self.tokens:
             raise ValueError(f"MoEAlignment requires at most {self.tokens} tokens with top-k {self.top_k}")
 
-    def _workspace(self, ids):
+    def _buffers(self, device):
         import torch
 
-        counts = torch.empty((self.experts,), dtype=torch.int32, device=ids.device)
-        cursors = torch.empty((self.experts,), dtype=torch.int32, device=ids.device)
-        sorted_routes = torch.empty((self.padded_routes,), dtype=torch.int32, device=ids.device)
-        return counts, cursors, sorted_routes
+        counters = torch.empty((2 * self.experts,), dtype=torch.int32, device=device)
+        return counters, torch.empty((self.padded_routes,), dtype=torch.int32, device=device)
 
     def run_into(self, ids, counts, cursors, sorted_routes):
-        self._validate_ids(ids)
-        counts.zero_()
-        cursors.zero_()
-        sorted_routes.fill_(self.routes)          # padding sentinel (composition.py:98-101)
+        """Alignment into caller-owned ``counts`` / ``cursors`` [experts] and ``sorted_routes``
+        [padded_routes]; all three are reset first."""
+        self._check(ids)
+        for buffer, value in ((counts, 0), (cursors, 0), (sorted_routes, self.routes)):
+            buffer.fill_(value)
         self.count.run(ids, counts)
         offsets, total_padded = self.prefix.run(counts)
         self.scatter.run(ids, offsets, cursors, sorted_routes)
-        expert_blocks = self.mark.run(offsets)
-        return sorted_routes, expert_blocks, total_padded
+        return sorted_routes, self.mark.run(offsets), total_padded
 
     def run(self, ids):
-        return self.run_into(ids, *self._workspace(ids))
+        counters, sorted_routes = self._buffers(ids.device)
+        return self.run_into(ids, counters[:self.experts], counters[self.experts:], sorted_routes)
 
     def prepare(self, ids):
-        self._validate_ids(ids)
-        counts, cursors, sorted_routes = self._workspace(ids)
+        self._check(ids)
+        counters, sorted_routes = self._buffers(ids.device)
+        counts, cursors = counters[:self.experts], counters[self.experts:]
         count = self.count.prepare(ids, counts)
         prefix = self.prefix.prepare(counts)
         offsets, total_padded = prefix.result()
         scatter = self.scatter.prepare(ids, offsets, cursors, sorted_routes)
         mark = self.mark.prepare(offsets)
-        return MoEAlignmentCall(count, prefix, scatter, mark, sorted_routes, mark.result(), total_padded,
-                                counts, cursors, self.routes)
+        return MoEAlignmentCall((count, prefix, scatter, mark), counters, sorted_routes, mark.result(),
+                                total_padded, self.routes)
 
 
 class MoEW4A16FFN:

@@ -1,78 +1,112 @@
-"""PyTorch custom-operator registration of an artifact.
+"""``artifact.as_torch_op("ns::name")``: the artifact as a ``torch.library`` custom operator.
 
-Mirrors python/intent/runtime/torch.py:27-93: the schema is built from the
-public inputs (``Tensor``, ``Tensor(aN!)`` for writable views, ``SymInt`` /
-``float`` / ``bool`` scalars), declared Out buffers become fresh return values,
-InOut parameters are declared as mutated, and the fake implementation runs the
-same binder without pointers or launches.  Autograd is never inferred.
+Contract taken from the reference (python/intent/runtime/torch.py:27-93): the operator's arguments are
+the artifact's public inputs in declaration order; a writable tensor is declared as mutated; declared
+``Out`` buffers come back as fresh return values; the fake (meta) implementation infers output shapes
+with the same binder and launches nothing; autograd is not registered.
+
+The schema text is assembled from two small tables (scalar category -> schema type, number of outputs ->
+return clause); the operator body is one closure that first applies the aliasing rule for mutated
+arguments and then forwards to ``run`` (real tensors) or to shape inference (fake tensors).
 """
 from __future__ import annotations
 
-from inspect import Parameter, Signature
+from dataclasses import dataclass
 
 from .interface import ScalarParameter, ViewParameter
+
+# schema type of a scalar parameter by dtype category
+_SCALAR_SCHEMA = {"bool": "bool", "int": "SymInt", "uint": "SymInt", "float": "float", "bfloat": "float"}
+
+
+@dataclass(frozen=True)
+class _Slot:
+    """One operator argument: its schema declaration and what the aliasing rule needs to know."""
+
+    name: str
+    declaration: str
+    tensor: bool
+    mutated: bool
+    label: str
+
+
+def _slots(interface) -> tuple:
+    slots = []
+    for position, parameter in enumerate(interface.inputs):
+        name = f"arg{position}"
+        if isinstance(parameter, ViewParameter):
+            kind = f"Tensor(a{position}!)" if parameter.writable else "Tensor"
+            slots.append(_Slot(name, f"{kind} {name}", True, parameter.writable, parameter.name))
+        elif isinstance(parameter, ScalarParameter):
+            kind = _SCALAR_SCHEMA.get(parameter.dtype.category)
+            if kind is None:
+                raise NotImplementedError(f"no operator schema type for scalar {parameter.name}: {parameter.dtype}")
+            slots.append(_Slot(name, f"{kind} {name}", False, False, parameter.name))
+        else:
+            raise NotImplementedError(f"parameter {position} is neither a view nor a scalar")
+    return tuple(slots)
+
+
+def _returns(count: int) -> str:
+    if count == 0:
+        return "()"
+    if count == 1:
+        return "Tensor"
+    return "(" + ", ".join(["Tensor"] * count) + ")"
+
+
+def _qualified(name: str) -> None:
+    namespace, separator, operator = name.partition("::")
+    if not separator or "::" in operator or not namespace.isidentifier() or not operator.isidentifier():
+        raise ValueError(f"{name!r} is not an operator name of the form 'namespace::operator'")
 
 
 def register_operator(artifact, name: str):
     import torch
 
-    interface = artifact.interface
     if artifact.device_type != "cuda" or not hasattr(artifact.runtime, "infer_outputs"):
-        raise NotImplementedError("PyTorch registration requires a CUDA tensor runtime with output inference")
-    inputs = interface.inputs
-    views = tuple((index, parameter) for index, parameter in enumerate(inputs)
-                  if isinstance(parameter, ViewParameter))
-    if not views:
-        raise NotImplementedError("PyTorch registration requires an input tensor to determine device dispatch")
+        raise NotImplementedError("as_torch_op needs a CUDA artifact whose runtime can infer output shapes")
+    interface = artifact.interface
+    slots = _slots(interface)
+    tensors = [index for index, slot in enumerate(slots) if slot.tensor]
+    if not tensors:
+        raise NotImplementedError("as_torch_op needs at least one tensor input: the dispatcher picks the "
+                                  "device from it")
     interface.require_output_allocation()
-    pieces = name.split("::")
-    if len(pieces) != 2 or not all(piece.isidentifier() for piece in pieces):
-        raise ValueError("operator name must be 'your_namespace::your_operator'")
+    _qualified(name)
+    schema = f"({', '.join(slot.declaration for slot in slots)}) -> {_returns(len(interface.outputs))}"
+    # a mutated tensor may not share storage with any other tensor argument of the same call
+    guarded = [(a, b) for i, a in enumerate(tensors) for b in tensors[i + 1:]
+               if slots[a].mutated or slots[b].mutated]
+    names = [slot.name for slot in slots]
 
-    mutable_names = tuple(f"arg{index}" for index, parameter in views if parameter.writable)
-    alias_pairs = tuple((li, ri, left.name, right.name)
-                        for position, (li, left) in enumerate(views)
-                        for ri, right in views[position + 1:]
-                        if left.writable or right.writable)
-    declared = []
-    for index, parameter in enumerate(inputs):
-        if isinstance(parameter, ViewParameter):
-            kind = f"Tensor(a{index}!)" if parameter.writable else "Tensor"
-        elif isinstance(parameter, ScalarParameter):
-            category = parameter.dtype.category
-            if category == "bool":
-                kind = "bool"
-            elif category in ("int", "uint"):
-                kind = "SymInt"
-            elif category in ("float", "bfloat"):
-                kind = "float"
-            else:
-                raise NotImplementedError(f"PyTorch scalar schema for {parameter.dtype}")
-        declared.append(f"{kind} arg{index}")
-    outputs = interface.outputs
-    if not outputs:
-        returns = "()"
-    elif len(outputs) == 1:
-        returns = "Tensor"
-    else:
-        returns = "(" + ", ".join("Tensor" for _ in outputs) + ")"
-    schema = f"({', '.join(declared)}) -> {returns}"
-    signature = Signature(Parameter(f"arg{index}", Parameter.POSITIONAL_OR_KEYWORD)
-                          for index in range(len(declared)))
+    def positional(arguments, keywords):
+        if len(arguments) > len(names):
+            raise TypeError(f"{name} takes {len(names)} arguments, got {len(arguments)}")
+        values = list(arguments)
+        for slot_name in names[len(arguments):]:
+            if slot_name not in keywords:
+                raise TypeError(f"{name} is missing argument {slot_name}")
+            values.append(keywords[slot_name])
+        unknown = set(keywords) - set(names[len(arguments):])
+        if unknown:
+            raise TypeError(f"{name} got unexpected arguments {sorted(unknown)}")
+        return values
 
-    def wrap(invoke):
-        def operator(*arguments, **keywords):
-            arguments = signature.bind(*arguments, **keywords).args
-            for left, right, left_name, right_name in alias_pairs:
-                if torch._C._is_alias_of(arguments[left], arguments[right]):
+    def body(target):
+        def call(*arguments, **keywords):
+            values = positional(arguments, keywords)
+            for a, b in guarded:
+                if torch._C._is_alias_of(values[a], values[b]):
                     raise NotImplementedError(
-                        "PyTorch mutable calls require independent input storage: "
-                        f"{left_name} and {right_name} share storage; use ordinary artifact calls for this binding")
-            return invoke(*arguments)
+                        f"{name}: {slots[a].label} and {slots[b].label} share storage, and one of them is "
+                        "written by the operator; call the artifact directly for such a binding")
+            return target(*values)
 
-        return operator
+        return call
 
-    operator = torch.library.custom_op(name, wrap(artifact.run), mutates_args=mutable_names,
-                                       device_types=artifact.device_type, schema=schema)
-    operator.register_fake(wrap(lambda *arguments: artifact.runtime.infer_outputs(arguments)))
+    operator = torch.library.custom_op(name, body(artifact.run), schema=schema,
+                                       mutates_args=tuple(slot.name for slot in slots if slot.mutated),
+                                       device_types=artifact.device_type)
+    operator.register_fake(body(lambda *values: artifact.runtime.infer_outputs(values)))
     return operator

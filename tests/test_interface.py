@@ -181,3 +181,28 @@ def test_artifact_save_and_load(tmp_path):
     assert error.value.stage == "generated_program_loading"
     with pytest.raises(ib.CompilationStageError):
         ib.load(tmp_path / "missing", resolve_target=False)
+
+
+def test_torch_operator_schema_and_fake_inference_without_a_device():
+    """as_torch_op: schema from the public inputs, mutated InOut views, fresh Out returns, and shape inference
+    under fake tensors - none of which needs a GPU."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import intent_b200 as ib
+
+    artifact = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(0), resolve_target=False,
+                          constexprs={"GROUP_SIZE": 128, "ZERO_POINT": 8})
+    operator = artifact.as_torch_op("intent_b200_cpu_test::w4a16")
+    assert str(operator._schema) == "(Tensor arg0, Tensor arg1, Tensor arg2) -> Tensor"
+    with FakeTensorMode():
+        fake = operator(torch.empty((4, 1024), dtype=torch.float16, device="cuda"),
+                        torch.empty((128, 256), dtype=torch.int32, device="cuda"),
+                        arg2=torch.empty((8, 256), dtype=torch.float16, device="cuda"))
+        assert fake.shape == (4, 256) and fake.dtype == torch.float16
+    combine = ib.compile(ib.programs.moe_combine, target=ib.B200Target(0), resolve_target=False)
+    schema = str(combine.as_torch_op("intent_b200_cpu_test::combine")._schema)
+    assert schema == "(Tensor arg0, Tensor arg1, Tensor arg2, Tensor(a3!) arg3) -> ()"
+    for bad in ("no_namespace", "a::b::c", "9a::b", "a::"):
+        with pytest.raises(ValueError):
+            artifact.as_torch_op(bad)
