@@ -30,6 +30,113 @@ def column_shard(columns: int, world: int, rank: int, multiple: int = 256) -> sl
 
 
 @dataclass
+class RowAligned:
+    """Marks a resident operand of :class:`ColumnShardedRows` that has one entry per activation row (the
+    per-token scales of W8A8): every piece gets the entries of its own rows."""
+
+    tensor: object
+
+
+class ColumnShardedRows:
+    """End-to-end form of a column-sharded dense program (W4A16 prefill, W8A8): the activation rows start in
+    pinned HOST memory and the result block ends there, with the copies overlapped with the contraction.
+
+    ``artifact`` is a compiled dense program whose first parameter is the row operand ``[M, K]`` and whose
+    single Out is ``[M, n_local]``; ``resident`` are its remaining inputs, already on the device (this rank's
+    column shard of the weights; an operand with one entry per row is wrapped in :class:`RowAligned`).  One call of :meth:`run` computes ``Y[:, shard] = program(X, resident)``:
+
+      * rank r uploads only ITS rows ``[r*M/world, (r+1)*M/world)`` of X, in ``chunks`` pieces on a copy
+        stream (plain ``cudaMemcpyAsync`` from pinned memory);
+      * with more than one rank every piece is all-gathered over NVLink (NCCL) into a local buffer, so each
+        row crosses PCIe once on the whole node and the contraction reads local memory only;
+      * the contraction of piece i runs on the compute stream while piece i+1 uploads and the result of
+        piece i-1 downloads on a third stream (PCIe is full duplex).
+
+    Gathered pieces hold rows ``{r*M/world + i*piece .. }`` of every rank r; the result rows are copied back
+    to exactly those rows of the pinned output.  Every buffer and prepared call is built once here; ``run``
+    neither allocates nor validates.  Nothing here runs on one GPU only: no load is a multicast load.
+    """
+
+    def __init__(self, artifact, resident: tuple, *, rows: int, width: int, n_local: int, in_dtype, out_dtype,
+                 device, chunks: int = 8, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.group, self._dist = group, dist
+        if rows % self.world:
+            raise ValueError("the row count must be a multiple of the number of ranks")
+        self.rows, self.width, self.n_local = rows, width, n_local
+        self.local_rows = rows // self.world
+        chunks = max(1, min(chunks, self.local_rows // 128 or 1))
+        while self.local_rows % chunks:
+            chunks -= 1
+        self.chunks, self.piece = chunks, self.local_rows // chunks
+        self.device = device
+        gathered = self.piece * self.world
+        self._mine = [torch.empty((self.piece, width), dtype=in_dtype, device=device) for _ in range(chunks)]
+        self._x = (self._mine if self.world == 1 else
+                   [torch.empty((gathered, width), dtype=in_dtype, device=device) for _ in range(chunks)])
+        self._y = [torch.empty((gathered, n_local), dtype=out_dtype, device=device) for _ in range(chunks)]
+        self._calls = []
+        for i, (x, y) in enumerate(zip(self._x, self._y)):
+            # rows of piece i, in the order the gathered buffer holds them: rank 0's rows first
+            index = torch.cat([torch.arange(r * self.local_rows + i * self.piece,
+                                            r * self.local_rows + (i + 1) * self.piece) for r in range(self.world)])
+            operands = [o.tensor[index.to(o.tensor.device)].contiguous() if isinstance(o, RowAligned) else o
+                        for o in resident]
+            self._calls.append(artifact.prepare(x, *operands, outputs=(y,)))
+        self._upload, self._download = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self._uploaded = [torch.cuda.Event() for _ in range(chunks)]
+        self._computed = [torch.cuda.Event() for _ in range(chunks)]
+        self._released = [torch.cuda.Event() for _ in range(chunks)]     # result buffer i may be overwritten
+        self._used = [torch.cuda.Event() for _ in range(chunks)]         # upload buffer i may be overwritten
+        self._first = True
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.local_rows * self.width * self._mine[0].element_size()
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.rows * self.n_local * self._y[0].element_size()
+
+    def run(self, host_x, host_y) -> None:
+        """``host_x`` [M, K] and ``host_y`` [M, n_local]: pinned host tensors.  Returns after queueing; the
+        caller synchronises (``torch.cuda.synchronize``) before reading ``host_y``."""
+        import torch
+
+        compute = torch.cuda.current_stream(self.device)
+        first_row = self.rank * self.local_rows
+        self._upload.wait_stream(compute)
+        for i in range(self.chunks):
+            begin = first_row + i * self.piece
+            with torch.cuda.stream(self._upload):
+                if not self._first:
+                    self._upload.wait_event(self._used[i])
+                self._mine[i].copy_(host_x[begin:begin + self.piece], non_blocking=True)
+                self._uploaded[i].record(self._upload)
+            compute.wait_event(self._uploaded[i])
+            if self.world > 1:
+                self._dist.all_gather_into_tensor(self._x[i], self._mine[i], group=self.group)
+            if not self._first:
+                compute.wait_event(self._released[i])
+            self._calls[i].launch()
+            self._computed[i].record(compute)
+            self._used[i].record(compute)
+            with torch.cuda.stream(self._download):
+                self._download.wait_event(self._computed[i])
+                for r in range(self.world):
+                    row = r * self.local_rows + i * self.piece
+                    host_y[row:row + self.piece].copy_(self._y[i][r * self.piece:(r + 1) * self.piece],
+                                                       non_blocking=True)
+                self._released[i].record(self._download)
+        compute.wait_stream(self._download)
+        self._first = False
+
+
+@dataclass
 class ExchangePlan:
     """Row counts of one all-to-all: what this rank sends to / receives from every rank."""
 

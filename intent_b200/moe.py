@@ -212,13 +212,31 @@ class PreparedFFN:
     y: object
     clear_positions: bool
 
-    def launch(self, accumulate: bool = False):
+    PHASES = ("align", "gather", "up_gate", "down", "combine")
+
+    def launch(self, accumulate: bool = False, marks=None):
+        """``marks``: an empty list that receives one timing event before the first phase and one after each
+        phase of :attr:`PHASES` (for per-phase device times; leave it None otherwise)."""
+        def mark():
+            if marks is not None:
+                import torch
+
+                event = torch.cuda.Event(enable_timing=True)
+                event.record()
+                marks.append(event)
+
+        mark()
         self.align.launch()
         if self.clear_positions:
             self.positions.zero_()
         self.position_call.launch()
+        mark()
         self.gather_call.launch()
+        mark()
         self.up_call.launch()
+        mark()
         self.down_call.launch()
+        mark()
         (self.combine_call if accumulate else self.overwrite_call).launch()   # overwrite: y is not read or cleared
+        mark()
         return self.y

@@ -284,15 +284,38 @@ class PreparedPeerStep:
         else:
             self.ep.barrier()
 
-    def launch(self, accumulate=False):
+    PHASES = ("route", "sync_counts", "dispatch", "sync_rows", "up_gate", "down", "sync_results", "combine")
+
+    def launch(self, accumulate=False, marks=None):
+        """``marks``: an empty list that receives one timing event before the first phase and one after each
+        phase of :attr:`PHASES` (for per-phase device times; leave it None otherwise)."""
         step = self.step
+
+        def mark():
+            if marks is not None:
+                import torch
+
+                event = torch.cuda.Event(enable_timing=True)
+                event.record()
+                marks.append(event)
+
+        mark()
         step.route()
+        mark()
         self._sync(0)         # every rank's per-expert counts are in every rank's count matrix
+        mark()
         step.dispatch_rows()
+        mark()
         self._sync(1)         # every row of this step is in its owner's buffer
-        step.experts()
+        mark()
+        step._up.launch()
+        mark()
+        step._down.launch()
+        mark()
         self._sync(2)         # every result row is written; also fences the row buffers for the next step
+        mark()
         step.combine(accumulate)
+        mark()
 
     def check(self):
         if self.signals is not None:

@@ -80,3 +80,34 @@ def moe_inputs(tokens: int, hidden: int, experts: int, intermediate: int, *,
     down_packed, down_scales = quantised(intermediate, hidden)
     return dict(logits=logits, x=x, up_gate_packed=up_gate_packed, up_gate_scales=up_gate_scales,
                 down_packed=down_packed, down_scales=down_scales)
+
+
+def moe_activations(tokens: int, hidden: int, experts: int, *, dtype=torch.bfloat16, seed: int = 0):
+    """Router logits ~ N(0,1) f32 [T,E] and x ~ N(0,1)/sqrt(H) [T,H]: the first two draws of
+    :func:`moe_inputs`, so both functions give the same activations for one seed."""
+    g = _generator(seed)
+    logits = torch.randn((tokens, experts), generator=g, dtype=torch.float32)
+    x = (torch.randn((tokens, hidden), generator=g, dtype=torch.float32) / hidden ** 0.5).to(dtype)
+    return logits, x
+
+
+def moe_expert_weights(first: int, count: int, hidden: int, intermediate: int, *, dtype=torch.bfloat16,
+                       group_size: int = 128, seed: int = 0):
+    """Int4 weights of experts ``first .. first+count-1``, each expert from its own generator (seeded with
+    ``seed`` and the expert's global id), so any rank can draw exactly its own experts.
+
+    The packed words are drawn directly as uniform 32-bit integers: eight independent nibbles uniform on
+    0..15, i.e. the same distribution as packing ``q ~ U{0..15}``, at an eighth of the draws (64 experts
+    of the benchmark shape take about a second instead of half a minute).  Scales are
+    0.002 + 0.01|N(0,1)|.  Returns (up_gate_packed [n,H/8,2I], up_gate_scales [n,H/G,2I],
+    down_packed [n,I/8,H], down_scales [n,I/G,H]).
+    """
+    out = [[], [], [], []]
+    for expert in range(first, first + count):
+        g = _generator(seed * 1000003 + 7919 * (expert + 1))
+        for slot, (K, N) in ((0, (hidden, 2 * intermediate)), (2, (intermediate, hidden))):
+            out[slot].append(torch.randint(-2 ** 31, 2 ** 31, (K // PACK_FACTOR, N), generator=g,
+                                           dtype=torch.int64).to(torch.int32))
+            out[slot + 1].append((0.002 + 0.01 * torch.randn((K // group_size, N), generator=g,
+                                                             dtype=torch.float32).abs()).to(dtype))
+    return tuple(torch.stack(parts) for parts in out)
