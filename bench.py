@@ -305,87 +305,127 @@ class DecodeWeights:
 
 def run_decode(args, rank: int, world: int, device, M: int | None = None, weights: DecodeWeights | None = None,
                steps: int | None = None, load_seconds: float | None = None):
+    """One decode step = up projection + down projection.  Measured three ways, all with cold weights and
+    the K timed steps captured in one CUDA graph:
+      table      (headline) one launch per step: both projections as a table of the persistent table kernel;
+      long table eight steps' projections (16 problems) per call: what a whole layer stack per launch gives;
+      per projection  one launch per projection through the single-problem artifact (the reference's
+                 call shape), programmatic dependent launch between consecutive launches."""
     import torch
 
     import intent_b200 as ib
+    from intent_b200 import table as table_module
     from intent_b200.runtime import native
 
     M = args.batch if M is None else M
     steps = args.steps if steps is None else steps
+    steps = max(8, steps // 8 * 8)
     load_seconds = args.load_seconds if load_seconds is None else load_seconds
     weights = weights or DecodeWeights(device)
-    artifact = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(device.index),
-                          constexprs={"GROUP_SIZE": GROUP, "ZERO_POINT": 8, "ACT_DTYPE": "f16"})
-    # decode loop: the packed weights are static model state, so a GEMV may start fetching them while
-    # the previous kernel on the stream drains (programmatic dependent launch)
-    native.set_gemv_launch_overlap(True)
+    table = table_module.W4A16Table(group_size=GROUP, zero_point=8, act_dtype="f16", target=ib.B200Target(device.index))
+    artifact = table.artifact
     host_x = [x for x, _, _ in decode_inputs(M)]
     xs = [x.to(device) for x in host_x]
     step_bytes = decode_bytes(M)
     copies = weights.copies
+    warm = max(args.warmup, 3)
+
+    def graph_time(step, hold_seconds: float):
+        """Capture `steps` steps in one graph, warm it, hold the load, time one replay (ms, launches, clocks)."""
+        for i in range(warm):
+            step(i)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(device)
+        stream.wait_stream(torch.cuda.current_stream())
+        before = native.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(steps):
+                step(i)
+        launches = native.launch_count() - before
+        with torch.cuda.stream(stream):
+            for _ in range(warm):
+                graph.replay()
+        stream.synchronize()
+        sampler = ClockSampler(device.index)
+        if rank == 0:
+            sampler.start()
+        with torch.cuda.stream(stream):       # keep the GPU under the same load so the clock samples mean something
+            spin_until = time.perf_counter() + hold_seconds
+            while time.perf_counter() < spin_until:
+                graph.replay()
+                stream.synchronize()
+        barrier(world)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            graph.replay()
+            stop.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        barrier(world)
+        clocks = sampler.stop() if rank == 0 else None
+        return reduce_max(start.elapsed_time(stop), world, device), launches, clocks
+
+    # ---- one launch per step: the two projections as one table ----------------------------------
+    table_module.set_launch_overlap(True)     # static weights: a launch may request them while its predecessor drains
+    step_calls = [table.prepare([(xs[j], p, s) for j, (p, s) in enumerate(group)]) for group in weights.sets]
+    single_launch = all(call.single_launch for call in step_calls)
+
+    def table_step(i: int) -> None:
+        step_calls[i % copies].launch()
+
+    elapsed_ms, launches, clocks = graph_time(table_step, load_seconds)
+    for call in step_calls:
+        call.check()                          # no bounded wait gave up inside the timed launches
+
+    # ---- eight steps per call ---------------------------------------------------------------------
+    long_calls = []
+    for first in range(0, copies, 1):
+        problems = []
+        for k in range(8):
+            group = weights.sets[(first + k) % copies]
+            problems += [(xs[j], p, s) for j, (p, s) in enumerate(group)]
+        long_calls.append(table.prepare(problems))
+
+    def long_step(i: int) -> None:
+        if i % 8 == 0:
+            long_calls[(i // 8) % len(long_calls)].launch()
+
+    long_ms, long_launches, _ = graph_time(long_step, 0.2)
+    for call in long_calls:
+        call.check()
+    table_module.set_launch_overlap(False)
+    del long_calls
+
+    # ---- one launch per projection (single-problem artifact) ----------------------------------------
+    native.set_gemv_launch_overlap(True)
     calls = [[artifact.prepare(xs[j], p, s) for j, (p, s) in enumerate(group)] for group in weights.sets]
 
-    def step(i: int) -> None:
+    def projection_step(i: int) -> None:
         for call in calls[i % copies]:
             call.launch()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    torch.cuda.synchronize()
-
-    # capture exactly K steps in one graph
-    stream = torch.cuda.Stream(device)
-    stream.wait_stream(torch.cuda.current_stream())
-    before = native.launch_count()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        for i in range(steps):
-            step(i)
-    launches = native.launch_count() - before
-    with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
-    stream.synchronize()
-
-    sampler = ClockSampler(device.index)
-    if rank == 0:
-        sampler.start()
-    # keep the GPU under the same load for a moment so the clock samples mean something
-    with torch.cuda.stream(stream):
-        spin_until = time.perf_counter() + load_seconds
-        while time.perf_counter() < spin_until:
-            graph.replay()
-            stream.synchronize()
-    barrier(world)
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        start.record(stream)
-        graph.replay()
-        stop.record(stream)
-    stream.synchronize()
-    torch.cuda.synchronize()
-    barrier(world)
-    elapsed_ms = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
-    elapsed_ms = reduce_max(elapsed_ms, world, device)
-    for group in calls:                      # no bounded wait gave up inside the timed launches
+    single_ms, single_launches, _ = graph_time(projection_step, 0.2)
+    for group in calls:
         for call in group:
             call.check()
+    native.set_gemv_launch_overlap(False)
 
-    # ---- end to end: host activations, artifact.run, result read back ----------------
+    # ---- end to end: host activations in, results back, one table launch per step --------------------
     pinned_in = [x.pin_memory() for x in host_x]
     pinned_out = [torch.empty((M, N), dtype=torch.float16).pin_memory() for _, N in DECODE_SHAPES]
 
     def e2e_step(i: int) -> None:
-        group = weights.sets[i % copies]
         for j in range(len(DECODE_SHAPES)):
-            xd = pinned_in[j].to(device, non_blocking=True)
-            y = artifact.run(xd, group[j][0], group[j][1])
+            xs[j].copy_(pinned_in[j], non_blocking=True)
+        step_calls[i % copies].launch()
+        for j, y in enumerate(step_calls[i % copies].results()):
             pinned_out[j].copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(max(args.warmup, 3)):
+    for i in range(warm):
         e2e_step(i)
     barrier(world)
     torch.cuda.synchronize()
@@ -397,31 +437,43 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
     e2e_s = time.perf_counter() - t0
     e2e_s = reduce_max(e2e_s, world, device)
 
-    native.set_gemv_launch_overlap(False)
     ms_per_step = elapsed_ms / steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     peaks = measured_peaks()
-    per_launch_bytes = step_bytes / len(DECODE_SHAPES)
+    per_launch_bytes = step_bytes * steps / max(1, launches)
     per_launch_s = elapsed_ms * 1e-3 / max(1, launches)
     achieved = per_launch_bytes / per_launch_s / 1e9
     config = workload_config("decode", world, M)
     notes = {"l2": f"weights rotated through {copies} resident copies ({copies * weights.bytes >> 20} MiB > L2)",
              "timing": "K steps in one CUDA graph, CUDA events on the replay stream",
-             "launch": "one kernel launch per projection, programmatic dependent launch between "
-                       "consecutive GEMVs (static weights)"}
+             "launch": ("one launch per step: both projections as a table of intent_b200.table.W4A16Table "
+                        "(persistent kernel, the second projection's weights stream while the first is reduced)"
+                        if single_launch else "table fell back to one launch per projection") +
+                       "; programmatic dependent launch between consecutive steps (static weights)"}
+
+    def mode(ms_total, n_launches):
+        per_step = ms_total / steps
+        return {"ms_per_step": round(per_step, 6), "GBps": round(step_bytes / (per_step * 1e-3) / 1e9, 1),
+                "frac_of_hbm_peak": round(step_bytes / (per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "launches_per_step": round(n_launches / steps, 3),
+                "us_per_projection": round(per_step * 1e3 / len(DECODE_SHAPES), 3)}
+
     line = {
         "metric": "w4a16_decode_weight_GBps", "value": round(value, 2), "unit": "GB/s",
-        "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
+        "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": round(ms_per_step, 6), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config, "notes": notes,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4),
-                     "traffic": NCU_TRAFFIC_BYTES_1GPU["decode"] if M == 1 else None,
-                     "traffic_note": "ncu capture of the M=1 launch (replicas: every GPU runs the same problem)"
-                                     if M == 1 else "not captured for this batch size",
+                     "traffic": None, "traffic_note": "see profiles/ for the ncu capture of this kernel",
                      "peak_source": peaks["source"], "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "algorithmic_bytes_per_launch": per_launch_bytes,
-                     "kernel": "w4a16_stream_kernel", "us_per_launch": round(per_launch_s * 1e6, 3)},
+                     "kernel": "w4a16_table_kernel" if single_launch else "w4a16_stream_kernel",
+                     "us_per_launch": round(per_launch_s * 1e6, 3),
+                     "us_per_projection": round(ms_per_step * 1e3 / len(DECODE_SHAPES), 3)},
+        "modes": {"table_one_launch_per_step": mode(elapsed_ms, launches),
+                  "table_eight_steps_per_call": mode(long_ms, long_launches),
+                  "one_launch_per_projection": mode(single_ms, single_launches)},
         "e2e": {"value": round(world * step_bytes / (e2e_s / e2e_steps) / 1e9, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in pinned_in),
                 "d2h_bytes_per_step": sum(y.numel() * 2 for y in pinned_out),
@@ -1183,7 +1235,7 @@ def run_triton(args) -> dict:
                     "(tl.dot / multiply-and-sum with in-loop unpack), eager launches, device-resident inputs"}
 
 
-ATTACHED_KEYS = ("metric", "value", "unit", "ms_per_step", "steps", "config", "notes", "roofline", "kernels", "e2e",
+ATTACHED_KEYS = ("metric", "value", "unit", "ms_per_step", "steps", "config", "notes", "roofline", "modes", "kernels", "e2e",
                  "gpu_launches", "scaling", "dtype")
 
 

@@ -124,6 +124,39 @@ INTENT_B200_API int intent_b200_w4a16_gemv_grid(int32_t ctas);
 INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
 
 /* ------------------------------------------------------------------------
+ * weight_only_int4_matmul over a TABLE of independent problems in one persistent launch
+ * (same program and numerics as intent_b200_w4a16_gemv_*, M <= 16 per problem).  The
+ * reference launches one kernel per contraction (python/intent/runtime/artifact.py:130-136);
+ * a decode step's projections are small enough that launch ramp and drain cost as much as
+ * the weight stream itself, so several of them can share one launch here: the weight stream
+ * of problem i+1 starts while problem i is still being reduced.
+ *   problems: HOST array of `count` entries; x [M,K], packed [K/8,N] i32, scales [K/G,N],
+ *             y [M,N] are contiguous DEVICE buffers, 16-byte aligned; x, scales, y of type T.
+ *   The problems must be independent: no problem may read (as x) what another problem of
+ *   the same call writes (as y).  Tables longer than 8 problems run as several launches.
+ *   workspace: ..._table_workspace_bytes(problems, count, group_size) bytes, zero-filled
+ *   once, 16-byte aligned; same reuse and status-word rules as the single-problem entries
+ *   (intent_b200_w4a16_gemv_workspace_status reads and recovers it).
+ * ------------------------------------------------------------------------ */
+typedef struct intent_b200_w4a16_problem {
+  const void* x;
+  const void* packed;
+  const void* scales;
+  void* y;
+  int64_t M, K, N;
+} intent_b200_w4a16_problem;
+INTENT_B200_API int64_t intent_b200_w4a16_gemv_table_workspace_bytes(const intent_b200_w4a16_problem* problems,
+                                                                     int32_t count, int32_t group_size);
+INTENT_B200_API int intent_b200_w4a16_gemv_table_f16(const intent_b200_w4a16_problem* problems, int32_t count,
+                                                     int32_t group_size, int32_t zero_point, void* workspace,
+                                                     int64_t workspace_bytes, void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_problem* problems, int32_t count,
+                                                      int32_t group_size, int32_t zero_point, void* workspace,
+                                                      int64_t workspace_bytes, void* stream);
+/* Programmatic dependent launch for the table entries (see intent_b200_w4a16_gemv_overlap); process-global. */
+INTENT_B200_API int intent_b200_w4a16_gemv_table_overlap(int32_t enable);
+
+/* ------------------------------------------------------------------------
  * gemm_i8: C[m,n] = i32(sum_k A[m,k] * B[k,n]) + bias[n], wrapping int32.
  * Replaces the provider lowering of examples/kernels/contraction/gemm.py:29-39.
  *   a0 A [M,K] i8 (K contiguous)   a1 B [K,N] i8 (N contiguous)

@@ -1,0 +1,763 @@
+// W4A16 decode GEMV over a TABLE of independent problems in one persistent launch.
+//
+//   for every problem p of the table:  Y_p[m, n] = T( sum_k f32(X_p[m, k]) * (q_p[k, n] - 8) * f32(S_p[k / G, n]) )
+//
+// Program: weight_only_int4_matmul (reference kernel body
+// examples/kernels/contraction/weight_only_int4.py:18-51), M <= 16 per problem.  The reference has no
+// decode-specific lowering and launches one kernel per contraction; a single 30 MB GEMV per launch
+// spends as long ramping up and draining as it spends streaming, so here the projections of a decode
+// step (or of several layers) share one launch and the weight stream never stops at a problem boundary.
+//
+// One CTA per SM.  Every problem's packed weight [K/8, N] is cut into units of 32 columns x 32 packed
+// rows (256 k, 4 KiB) and the units of a problem are split evenly over the CTAs (+-1).  A CTA owns a
+// ring of 32 shared-memory slots; unit number g of the CTA's sequence - the concatenation of its shares
+// of all problems - lands in slot g % 32 through one 128B-swizzled TMA box (plus a box of its scales)
+// on the slot's mbarrier, is consumed by warp g % WARPS, and that warp then requests unit g + 32 into
+// the same slot, whichever problem it belongs to.
+//
+// Unit order inside a problem.  K is cut into chunk blocks of `cb` chunks (cb = all chunks when the
+// activations of the whole K range fit in shared memory, smaller for larger M); units are numbered
+// block-major, then column tile, then chunk.  A CTA's share is therefore a run of whole "spans"
+// (one column tile x one chunk block) plus a partial span at either end, and the activations it needs
+// are those of at most a few neighbouring chunk blocks: they are staged once per problem, permuted to
+// the nibble-pair order (w4a16_expand.cuh), together with the per-group correction sums.
+//
+// Reduction over K, fixed order (bitwise reproducible):
+//   1. units of one span inside one CTA: per-unit partials [M x 32] f32 in shared memory, a shared
+//      ticket per span, the warp with the last ticket adds them in chunk order;
+//   2. a span shared by neighbouring CTAs: each publishes ONE partial to global scratch and takes a
+//      ticket on the span's global counter; the last one adds the partials in CTA order;
+//   3. several chunk blocks: the block sums of a column tile meet the same way on the tile's counter
+//      and are added in block order.
+// Counters are left at zero for the next launch.  Partial spans at the ends of a CTA's share are
+// processed first, so their global round trips overlap the rest of the share.
+//
+// Every mbarrier wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the
+// workspace's status word, the CTA skips its remaining units (still meeting its barriers) and exits.
+#include <type_traits>
+
+#include "common.cuh"
+#include "tma.cuh"
+#include "w4a16_expand.cuh"
+
+namespace ib200 {
+namespace {
+
+constexpr int kCols = 32;            // columns of a unit
+constexpr int kRows = 32;            // packed rows of a unit (8 k each)
+constexpr int kWeightBytes = kCols * kRows * 4;
+constexpr int kScaleBytes = 512;     // up to 8 groups x 32 columns of 16-bit scales
+constexpr int kSlots = 32;
+constexpr int kMaxProblems = 8;
+constexpr int kMaxSpans = 64;        // spans a CTA may touch in one problem
+constexpr int kSmemLimit = 227 * 1024;
+
+struct TableProblem {
+  const void* x;
+  void* y;
+  int M, K, N;
+  int groups;          // K / G
+  int chunks, tiles;   // ceil(K / 256), ceil(N / 32)
+  int cb, nblocks;     // chunks per chunk block, number of chunk blocks
+  int units;           // tiles * chunks
+  int each, extra;     // units per CTA: the first `extra` CTAs get each + 1
+  int maxp;            // partial slots per span in scratch1
+  int* counters1;      // [nblocks * tiles] span tickets
+  int* counters2;      // [tiles] tile tickets (nblocks > 1)
+  float* scratch1;     // [nblocks * tiles][maxp][M][32]
+  float* scratch2;     // [tiles][nblocks][M][32]
+};
+
+struct TableParams {
+  TableProblem problem[kMaxProblems];
+  int count;
+  int twos_complement;
+  int overlap;
+  int* status;
+  // shared-memory layout behind the slot ring, sized for the largest problem of the table
+  int corr_offset, xs_offset, span_offset, part_offset;
+};
+
+struct TableMaps {
+  CUtensorMap w[kMaxProblems];
+  CUtensorMap s[kMaxProblems];
+};
+
+// What a CTA knows about its share of one problem (kept in shared memory).
+struct Share {
+  int u0, u1;        // unit range
+  int head, tail;    // partial spans at the ends: units u0 .. u0+head-1 and u1-tail .. u1-1
+  int first;         // position of the share's first unit in the CTA's whole sequence
+  int row0;          // first staged packed row (start of the first chunk block touched)
+  int rows;          // staged packed rows
+  int span0;         // span index (block * tiles + tile) of unit u0
+};
+
+struct Unit {
+  int block, tile, chunk;
+  int span_first, span_len;   // first unit and length of the span (tile x chunk block)
+};
+
+__device__ __forceinline__ Unit decode_unit(const TableProblem& q, int u) {
+  Unit r;
+  const int full = q.tiles * q.cb;                       // units of a full chunk block
+  r.block = min(u / full, q.nblocks - 1);
+  const int rest = u - r.block * full;
+  r.span_len = min(q.cb, q.chunks - r.block * q.cb);     // only the last block can be shorter
+  r.tile = rest / r.span_len;
+  r.chunk = r.block * q.cb + (rest - r.tile * r.span_len);
+  r.span_first = r.block * full + r.tile * r.span_len;
+  return r;
+}
+
+__device__ __forceinline__ int cta_of(const TableProblem& q, int u) {
+  const int boundary = q.extra * (q.each + 1);
+  return u < boundary ? u / (q.each + 1) : q.extra + (u - boundary) / q.each;   // each > 0 past the boundary
+}
+
+// j-th unit of a share in processing order: the partial span at the end, the one at the start, the rest
+__device__ __forceinline__ int unit_at(const Share& s, int j) {
+  if (j < s.tail) return s.u1 - s.tail + j;
+  if (j < s.tail + s.head) return s.u0 + (j - s.tail);
+  return s.u0 + s.head + (j - s.tail - s.head);
+}
+
+template <typename T, int MB, int STEPS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
+  constexpr int THREADS = WARPS * 32;
+  constexpr int RPG = 4 * STEPS;        // packed rows per quantisation group
+  constexpr int GPC = kRows / RPG;      // groups per unit
+  constexpr int CP = 8 * MB;            // row pitch of the correction table
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Share shares[kMaxProblems];
+  __shared__ int total_units;
+  __shared__ int abort_flag;
+
+  if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int cta = int(blockIdx.x);
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t scale_base = base + kSlots * kWeightBytes;
+  const uint32_t bars = scale_base + kSlots * kScaleBytes;
+  float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
+  uint4* xs = reinterpret_cast<uint4*>(base_ptr + p.xs_offset);
+  const uint32_t xs_addr = base + uint32_t(p.xs_offset);
+  int* span_count = reinterpret_cast<int*>(base_ptr + p.span_offset);
+  float* part = reinterpret_cast<float*>(base_ptr + p.part_offset);
+
+  // ---- this CTA's share of every problem ---------------------------------------------------
+  if (tid < p.count) {
+    const TableProblem& q = p.problem[tid];
+    Share s;
+    s.u0 = cta * q.each + min(cta, q.extra);
+    s.u1 = s.u0 + q.each + (cta < q.extra ? 1 : 0);
+    s.head = s.tail = 0;
+    s.row0 = s.rows = s.span0 = 0;
+    if (s.u1 > s.u0) {
+      const Unit a = decode_unit(q, s.u0), b = decode_unit(q, s.u1 - 1);
+      if (a.span_first < s.u0) s.head = min(s.u1, a.span_first + a.span_len) - s.u0;
+      if (b.span_first + b.span_len > s.u1 && b.span_first >= s.u0 + s.head) s.tail = s.u1 - max(b.span_first, s.u0);
+      if (s.head == s.u1 - s.u0) s.tail = 0;
+      s.row0 = a.block * q.cb * kRows;
+      s.rows = min(q.chunks, (b.block + 1) * q.cb) * kRows - s.row0;
+      s.span0 = a.block * q.tiles + a.tile;
+    }
+    shares[tid] = s;
+  }
+  if (tid == 0) abort_flag = 0;
+  __syncthreads();
+  if (tid == 0) {
+    int first = 0;
+    for (int i = 0; i < p.count; ++i) {
+      shares[i].first = first;
+      first += shares[i].u1 - shares[i].u0;
+    }
+    total_units = first;
+  }
+  if (tid < kSlots) mbar_init(bars + uint32_t(tid) * 8u, 1);
+  if (tid == 0) fence_mbar_init();
+  __syncthreads();
+  const int total = total_units;
+
+  // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).
+  auto issue = [&](int seq) {
+    int i = 0;
+    while (i + 1 < p.count && seq >= shares[i + 1].first) ++i;
+    const TableProblem& q = p.problem[i];
+    const Unit u = decode_unit(q, unit_at(shares[i], seq - shares[i].first));
+    const uint32_t slot = uint32_t(seq % kSlots);
+    const uint32_t bar = bars + slot * 8u;
+    mbar_expect_tx(bar, kWeightBytes + GPC * 64);
+    tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
+    tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
+  };
+  // first wave: slot s is owned by warp s % WARPS
+  if (lane == 0)
+    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq);
+  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  uint32_t magic_a, magic_b;
+  Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
+  int row_of[STEPS];
+  uint32_t off_of[STEPS];
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    row_of[i] = STEPS >= 2 ? 8 * (i >> 1) + 2 * t + (i & 1) : t;
+    off_of[i] = uint32_t(row_of[i]) * 128u + (uint32_t(g ^ (row_of[i] & 7)) << 4);
+  }
+  const int q4 = lane >> 3, v8 = lane & 7;   // reduction lanes: quarter q4 takes partials q4, q4+4, ...; columns 4*v8..+3
+
+  for (int pi = 0; pi < p.count; ++pi) {
+    const TableProblem& q = p.problem[pi];
+    const Share sh = shares[pi];
+    const int n_units = sh.u1 - sh.u0;
+    const int M = q.M;
+    const int part_floats = M * kCols;
+
+    // ---- stage this problem's activations and correction sums -------------------------------
+    // corr[group][m] = - sum over the group's k of x[m,k] * (bias_k + 8); rows of one group sit in RPG
+    // adjacent lanes and are added by a fixed-order butterfly.
+    {
+      const uint4* xg = reinterpret_cast<const uint4*>(q.x);
+      const int k8 = q.K >> 3;
+      const int items = sh.rows * M;
+      constexpr int BATCH = 4;
+      for (int start = 0; start < items; start += THREADS * BATCH) {
+        uint4 val[BATCH];
+        int ms[BATCH], lr[BATCH];
+        bool in_range[BATCH], real[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+          const int i = start + b * THREADS + tid;
+          in_range[b] = i < items;
+          ms[b] = in_range[b] ? i / sh.rows : 0;
+          lr[b] = in_range[b] ? i - ms[b] * sh.rows : 0;
+          real[b] = in_range[b] && sh.row0 + lr[b] < k8;
+          val[b] = real[b] ? xg[size_t(ms[b]) * k8 + sh.row0 + lr[b]] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+          float partial = 0.f;
+          uint4 o = make_uint4(0, 0, 0, 0);   // rows past K/8 (last chunk) are staged as zeros
+          if (real[b]) {
+            o.x = prmt(val[b].x, val[b].z, 0x5410);                        // (k0, k4)
+            o.y = Expand<T>::scale_odd(prmt(val[b].x, val[b].z, 0x7632));  // (k1, k5)
+            o.z = prmt(val[b].y, val[b].w, 0x5410);                        // (k2, k6)
+            o.w = Expand<T>::scale_odd(prmt(val[b].y, val[b].w, 0x7632));  // (k3, k7)
+            partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
+                      Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
+          }
+          if (in_range[b]) xs[lr[b] * M + ms[b]] = o;
+#pragma unroll
+          for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+          if (in_range[b] && (lr[b] % RPG) == 0) corr[(lr[b] / RPG) * CP + ms[b]] = real[b] ? -partial : 0.f;
+        }
+      }
+      for (int i = tid; i < kMaxSpans; i += THREADS) span_count[i] = 0;
+    }
+    __syncthreads();   // staged data visible; nobody is still reading the previous problem's (see the barrier below)
+
+    uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
+    const int group0 = sh.row0 / RPG;   // first staged group
+
+    // this warp's units of the problem: sequence numbers congruent to the warp modulo WARPS
+    int j = ((warp - sh.first) % WARPS + WARPS) % WARPS;
+    for (; j < n_units; j += WARPS) {
+      if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+      const int seq = sh.first + j;
+      const int unit = unit_at(sh, j);
+      const Unit u = decode_unit(q, unit);
+      const uint32_t slot = uint32_t(seq % kSlots);
+      const uint32_t bar = bars + slot * 8u;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar, uint32_t(seq / kSlots) & 1u))) {
+        if (lane == 0) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // this unit's loads never completed
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        break;
+      }
+      const uint32_t wslot = base + slot * kWeightBytes;
+      const uint32_t sslot = scale_base + slot * kScaleBytes;
+      float facc[MB][8];
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) facc[mb][i] = 0.f;
+
+      const int staged_row = u.chunk * kRows - sh.row0;   // first staged row of this unit
+#pragma unroll
+      for (int gi = 0; gi < GPC; ++gi) {
+        const int group = u.chunk * GPC + gi;
+        float gacc[MB][8];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          float2 c = make_float2(0.f, 0.f);
+          if (group < q.groups) c = *reinterpret_cast<const float2*>(&corr[(group - group0) * CP + mb * 8 + 2 * t]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gacc[mb][i] = (i & 1) ? c.y : c.x;
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+          const int row = gi * RPG + row_of[i];
+          const uint32_t off = STEPS >= 2 ? off_of[i] + uint32_t(gi * RPG * 128)
+                                          : uint32_t(row) * 128u + (uint32_t(g ^ (row & 7)) << 4);
+          const uint4 w = lds128(wslot + off);
+          uint32_t c0[4], c1[4], c2[4], c3[4];
+          Expand<T>::word(w.x, magic_a, magic_b, c0);
+          Expand<T>::word(w.y, magic_a, magic_b, c1);
+          Expand<T>::word(w.z, magic_a, magic_b, c2);
+          Expand<T>::word(w.w, magic_a, magic_b, c3);
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            uint4 b = make_uint4(0, 0, 0, 0);
+            const int m = mb * 8 + g;
+            if (m < M) b = lds128(xs_addr + uint32_t((staged_row + row) * M + m) * 16u);
+            float(&a01)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][0]);
+            float(&a23)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][4]);
+            Elem<T>::mma16816(a01, c0[0], c1[0], c0[1], c1[1], b.x, b.y);
+            Elem<T>::mma16816(a23, c2[0], c3[0], c2[1], c3[1], b.x, b.y);
+            Elem<T>::mma16816(a01, c0[2], c1[2], c0[3], c1[3], b.z, b.w);
+            Elem<T>::mma16816(a23, c2[2], c3[2], c2[3], c3[3], b.z, b.w);
+          }
+        }
+        uint2 s;  // this lane's four column scales of the group (zero outside the matrix)
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(s.x), "=r"(s.y) : "r"(sslot + gi * 64 + g * 8));
+        const float s0 = Elem<T>::to_float(uint16_t(s.x & 0xFFFF)), s1 = Elem<T>::to_float(uint16_t(s.x >> 16));
+        const float s2 = Elem<T>::to_float(uint16_t(s.y & 0xFFFF)), s3 = Elem<T>::to_float(uint16_t(s.y >> 16));
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          facc[mb][0] = fmaf(gacc[mb][0], s0, facc[mb][0]);
+          facc[mb][1] = fmaf(gacc[mb][1], s0, facc[mb][1]);
+          facc[mb][2] = fmaf(gacc[mb][2], s1, facc[mb][2]);
+          facc[mb][3] = fmaf(gacc[mb][3], s1, facc[mb][3]);
+          facc[mb][4] = fmaf(gacc[mb][4], s2, facc[mb][4]);
+          facc[mb][5] = fmaf(gacc[mb][5], s2, facc[mb][5]);
+          facc[mb][6] = fmaf(gacc[mb][6], s3, facc[mb][6]);
+          facc[mb][7] = fmaf(gacc[mb][7], s3, facc[mb][7]);
+        }
+      }
+      // the slot is free: request the unit that maps to it next, whichever problem that is
+      if (seq + kSlots < total) {
+        __syncwarp();
+        fence_proxy_async();
+        if (lane == 0) issue(seq + kSlots);
+      }
+
+      // ---- level 1: the unit's partial joins its span's partials in shared memory --------------
+      // accumulator element (mb, i): row m = 8*mb + 2t + (i & 1), column 4g + (i >> 1)
+      const int seg_begin = max(u.span_first, sh.u0), seg_end = min(u.span_first + u.span_len, sh.u1);
+      const int seg_len = seg_end - seg_begin;
+      const int span = u.block * q.tiles + u.tile;
+      const int seg = span - sh.span0;           // < kMaxSpans, checked on the host
+      float* mine = part + size_t(unit - sh.u0) * part_floats;
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int m = mb * 8 + 2 * t + hh;
+          if (m < M)
+            *reinterpret_cast<float4*>(mine + m * kCols + 4 * g) =
+                make_float4(facc[mb][0 + hh], facc[mb][2 + hh], facc[mb][4 + hh], facc[mb][6 + hh]);
+        }
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) {
+        __threadfence_block();
+        last = atomicAdd(span_count + seg, 1) == seg_len - 1;
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (!last) continue;
+      __threadfence_block();
+
+      // sum of `count` partials spaced `stride` floats apart, for row m: quarter q4 adds partials q4, q4+4, ...
+      // (four loads in flight), then the quarters are added in a fixed order
+      auto sum_partials = [&](const float* first, int count, int stride, bool global, int m) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = q4; c < count; c += 16) {
+          float4 a[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int cc = c + 4 * k;
+            a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (cc < count) {
+              const float4* src = reinterpret_cast<const float4*>(first + size_t(cc) * stride + m * kCols + 4 * v8);
+              a[k] = global ? __ldcg(src) : *src;
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            sum.x += a[k].x; sum.y += a[k].y; sum.z += a[k].z; sum.w += a[k].w;
+          }
+        }
+#pragma unroll
+        for (int d = 16; d >= 8; d >>= 1) {
+          sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
+          sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
+          sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
+          sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+        }
+        return sum;
+      };
+      auto write_y = [&](int m, float4 sum) {
+        const int n = u.tile * kCols + 4 * v8;
+        if (q4 == 0 && n < q.N) {  // N is a multiple of 8, so the four columns are inside together
+          uint2 out;
+          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
+          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+          *reinterpret_cast<uint2*>(y + size_t(m) * q.N + n) = out;
+        }
+      };
+      auto store_rows = [&](float* dst, float4 sum, int m) {
+        if (q4 == 0) *reinterpret_cast<float4*>(dst + m * kCols + 4 * v8) = sum;
+      };
+      auto take_ticket = [&](int* counter, int arrivals) {   // true for the last of `arrivals`
+        __syncwarp();
+        int final_one = 0;
+        if (lane == 0) {
+          int old;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+          final_one = old == arrivals - 1;
+        }
+        return __shfl_sync(0xffffffffu, final_one, 0) != 0;
+      };
+
+      const float* seg_first = part + size_t(seg_begin - sh.u0) * part_floats;
+      const bool whole = seg_len == u.span_len;     // the whole span was added here: this is the block sum
+      float* block_dst = q.nblocks > 1 ? q.scratch2 + (size_t(u.tile) * q.nblocks + u.block) * part_floats : nullptr;
+      if (whole) {
+        for (int m = 0; m < M; ++m) {
+          const float4 sum = sum_partials(seg_first, seg_len, part_floats, false, m);
+          if (block_dst) store_rows(block_dst, sum, m); else write_y(m, sum);
+        }
+      } else {
+        // ---- level 2: a span shared with neighbouring CTAs ------------------------------------
+        const int first_cta = cta_of(q, u.span_first), last_cta = cta_of(q, u.span_first + u.span_len - 1);
+        float* span_scratch = q.scratch1 + size_t(span) * q.maxp * part_floats;
+        float* slot_dst = span_scratch + size_t(cta - first_cta) * part_floats;
+        for (int m = 0; m < M; ++m) store_rows(slot_dst, sum_partials(seg_first, seg_len, part_floats, false, m), m);
+        if (!take_ticket(q.counters1 + span, last_cta - first_cta + 1)) continue;
+        for (int m = 0; m < M; ++m) {
+          const float4 sum = sum_partials(span_scratch, last_cta - first_cta + 1, part_floats, true, m);
+          if (block_dst) store_rows(block_dst, sum, m); else write_y(m, sum);
+        }
+        if (lane == 0) q.counters1[span] = 0;   // ready for the next launch
+      }
+      if (block_dst) {
+        // ---- level 3: the chunk blocks of a column tile -----------------------------------------
+        if (!take_ticket(q.counters2 + u.tile, q.nblocks)) continue;
+        const float* tile_first = q.scratch2 + size_t(u.tile) * q.nblocks * part_floats;
+        for (int m = 0; m < M; ++m) write_y(m, sum_partials(tile_first, q.nblocks, part_floats, true, m));
+        if (lane == 0) q.counters2[u.tile] = 0;
+      }
+    }
+    // everybody is done with this problem's staged activations and partials before the next problem
+    // overwrites them (the weight ring keeps streaming meanwhile)
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct HostProblem {
+  const void* x;
+  const void* w;
+  const void* s;
+  void* y;
+  int64_t M, K, N;
+};
+
+struct ProblemPlan {
+  int chunks, tiles, cb, nblocks, units, each, extra, maxp;
+  size_t xs_bytes, corr_bytes, part_bytes;       // shared memory this problem needs (worst CTA)
+  size_t counters1, counters2, scratch1, scratch2, bytes;   // workspace layout (offsets) and size
+};
+
+// Spans a CTA may touch and rows it must stage, worst case over CTAs, for a chunk-block size.
+void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched, int* spans_touched) {
+  const long long block_units = (long long)tiles * cb;
+  const int nblocks = (chunks + cb - 1) / cb;
+  long long touched = n_max <= 0 ? 0 : (n_max + block_units - 2) / block_units + 1;
+  if (touched > nblocks) touched = nblocks;
+  *blocks_touched = int(touched);
+  const int shortest = chunks - (nblocks - 1) * cb;      // the last block's spans may be shorter
+  *spans_touched = n_max <= 0 ? 0 : (n_max - 1) / (shortest < cb ? shortest : cb) + 2;
+}
+
+bool plan_problem(int M, int K, int N, int group_size, int mb, int grid, size_t smem_budget, ProblemPlan* out) {
+  ProblemPlan q{};
+  q.tiles = (N + kCols - 1) / kCols;
+  q.chunks = (K / 8 + kRows - 1) / kRows;
+  q.units = q.tiles * q.chunks;
+  q.each = q.units / grid;
+  q.extra = q.units % grid;
+  const int n_max = q.each + (q.extra ? 1 : 0);
+  q.part_bytes = size_t(n_max) * M * kCols * 4;
+  const int rpg = group_size / 8;
+  // the largest chunk block whose staged activations (all blocks a CTA can touch) fit beside the rest
+  int cb = q.chunks;
+  for (;;) {
+    int blocks, spans;
+    share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
+    const size_t rows = size_t(blocks) * cb * kRows;
+    q.xs_bytes = rows * M * 16;
+    q.corr_bytes = (rows / rpg + 1) * 16 * 4;   // sized for the wider correction pitch (M > 8 in the same launch)
+    if (spans <= kMaxSpans && q.xs_bytes + q.corr_bytes + q.part_bytes <= smem_budget) break;
+    if (cb == 1) return false;
+    cb = (cb + 1) / 2;
+  }
+  q.cb = cb;
+  q.nblocks = (q.chunks + cb - 1) / cb;
+  q.maxp = q.each == 0 ? cb : ((cb + q.each - 2) / q.each + 1 < cb ? (cb + q.each - 2) / q.each + 1 : cb);
+  if (q.maxp < 1) q.maxp = 1;
+  const size_t spans = size_t(q.nblocks) * q.tiles;
+  size_t offset = 0;
+  q.counters1 = offset;
+  offset += (spans * 4 + 255) / 256 * 256;
+  q.counters2 = offset;
+  offset += (size_t(q.tiles) * 4 + 255) / 256 * 256;
+  q.scratch1 = offset;
+  offset += (spans * q.maxp * M * kCols * 4 + 255) / 256 * 256;
+  q.scratch2 = offset;
+  if (q.nblocks > 1) offset += (size_t(q.tiles) * q.nblocks * M * kCols * 4 + 255) / 256 * 256;
+  q.bytes = offset;
+  *out = q;
+  return true;
+}
+
+int table_sms() {
+  static int sms = [] {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return value;
+  }();
+  return sms;
+}
+
+int g_table_overlap = 0;
+
+constexpr size_t kRingBytes = size_t(kSlots) * (kWeightBytes + kScaleBytes + 8);
+constexpr size_t kFixedBytes = 1024 + kRingBytes + 16 + kMaxSpans * 4 + 64;   // alignment slack, ring, span tickets
+
+int validate(const HostProblem& h, int group_size) {
+  if (h.M < 0 || h.K < 0 || h.N < 0) return INTENT_B200_ERR_SHAPE;
+  if (h.M == 0 || h.N == 0) return INTENT_B200_OK;
+  if (!h.x || !h.w || !h.s || !h.y) return INTENT_B200_ERR_NULL;
+  if (!aligned16(h.x) || !aligned16(h.w) || !aligned16(h.s) || !aligned16(h.y)) return INTENT_B200_ERR_LAYOUT;
+  if (h.K == 0 || h.K % group_size != 0 || h.N % 8 != 0 || h.M > 16 || h.K > (1 << 24) || h.N > (1 << 24))
+    return INTENT_B200_ERR_UNSUPPORTED;
+  return INTENT_B200_OK;
+}
+
+template <typename T, int MB, int STEPS>
+int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
+  constexpr int WARPS = MB == 1 ? 32 : 16;
+  auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (e != cudaSuccess) return cuda_status(e);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid, 1, 1);
+  config.blockDim = dim3(WARPS * 32, 1, 1);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = p.overlap ? 1 : 0;
+  e = cudaLaunchKernelEx(&config, kernel, maps, p);
+  if (e != cudaSuccess) return cuda_status(e);
+  note_launch();
+  return launch_status();
+}
+
+// Lays out the workspace of a whole table: a 256-byte header (status word), then every problem's part.
+int64_t table_workspace(const HostProblem* problems, int count, int group_size, int grid, ProblemPlan* plans,
+                        size_t* offsets) {
+  size_t offset = 256;
+  for (int begin = 0; begin < count; begin += kMaxProblems) {
+    const int n = count - begin < kMaxProblems ? count - begin : kMaxProblems;
+    // the problems of one launch share the space behind the ring: every one must fit next to the others' maximum,
+    // which the per-problem budget below guarantees without a second pass
+    for (int i = begin; i < begin + n; ++i) {
+      const HostProblem& h = problems[i];
+      if (h.M <= 0 || h.N <= 0) {
+        plans[i] = ProblemPlan{};
+        offsets[i] = offset;
+        continue;
+      }
+      const int mb = h.M <= 8 ? 1 : 2;
+      if (!plan_problem(int(h.M), int(h.K), int(h.N), group_size, mb, grid, size_t(kSmemLimit) - kFixedBytes, &plans[i]))
+        return -1;
+      offsets[i] = offset;
+      offset += plans[i].bytes;
+    }
+  }
+  return int64_t(offset);
+}
+
+template <typename T>
+int run_table(const HostProblem* problems, int count, int group_size, int zero_point, void* workspace,
+              int64_t workspace_bytes, cudaStream_t stream) {
+  if (count < 0) return INTENT_B200_ERR_SHAPE;
+  if (count == 0) return INTENT_B200_OK;
+  if (!problems) return INTENT_B200_ERR_NULL;
+  if (count > 4096) return INTENT_B200_ERR_UNSUPPORTED;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
+  if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
+  for (int i = 0; i < count; ++i) {
+    const int status = validate(problems[i], group_size);
+    if (status != INTENT_B200_OK) return status;
+  }
+  const int grid = table_sms();
+  if (grid <= 0) return INTENT_B200_ERR_UNSUPPORTED;
+  ProblemPlan* plans = new ProblemPlan[count];
+  size_t* offsets = new size_t[count];
+  struct Cleanup {
+    ProblemPlan* a;
+    size_t* b;
+    ~Cleanup() { delete[] a; delete[] b; }
+  } cleanup{plans, offsets};
+  const int64_t need = table_workspace(problems, count, group_size, grid, plans, offsets);
+  if (need < 0) return INTENT_B200_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < need || !aligned16(workspace)) return INTENT_B200_ERR_WORKSPACE;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  const CUtensorMapDataType xt =
+      std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int steps = group_size / 32;
+
+  // Problems that share a launch share the space behind the slot ring, each region sized for the largest of
+  // them: a launch takes as many consecutive problems (at most kMaxProblems) as fit together.
+  const size_t behind_ring = size_t(kSmemLimit) - kFixedBytes;
+  for (int begin = 0; begin < count;) {
+    TableMaps maps;
+    TableParams p{};
+    size_t xs_max = 0, corr_max = 0, part_max = 0;
+    int n = 0, mb = 1, i = begin;
+    for (; i < count && n < kMaxProblems; ++i) {
+      const HostProblem& h = problems[i];
+      if (h.M <= 0 || h.N <= 0) continue;   // nothing to compute
+      const ProblemPlan& q = plans[i];
+      {
+        const size_t xs = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
+        const size_t corr_b = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
+        const size_t part_b = q.part_bytes > part_max ? q.part_bytes : part_max;
+        if (n > 0 && xs + corr_b + part_b > behind_ring) break;
+      }
+      TableProblem& d = p.problem[n];
+      d.x = h.x;
+      d.y = h.y;
+      d.M = int(h.M);
+      d.K = int(h.K);
+      d.N = int(h.N);
+      d.groups = int(h.K / group_size);
+      d.chunks = q.chunks;
+      d.tiles = q.tiles;
+      d.cb = q.cb;
+      d.nblocks = q.nblocks;
+      d.units = q.units;
+      d.each = q.each;
+      d.extra = q.extra;
+      d.maxp = q.maxp;
+      d.counters1 = reinterpret_cast<int*>(ws + offsets[i] + q.counters1);
+      d.counters2 = reinterpret_cast<int*>(ws + offsets[i] + q.counters2);
+      d.scratch1 = reinterpret_cast<float*>(ws + offsets[i] + q.scratch1);
+      d.scratch2 = reinterpret_cast<float*>(ws + offsets[i] + q.scratch2);
+      if (!make_tensor_map_2d(&maps.w[n], CU_TENSOR_MAP_DATA_TYPE_INT32, h.w, uint64_t(h.K / 8), uint64_t(h.N),
+                              uint64_t(h.N) * 4, kRows, kCols, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
+          !make_tensor_map_2d(&maps.s[n], xt, h.s, uint64_t(h.K / group_size), uint64_t(h.N), uint64_t(h.N) * 2,
+                              uint32_t(256 / group_size), kCols, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INTENT_B200_ERR_UNSUPPORTED;
+      xs_max = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
+      corr_max = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
+      part_max = q.part_bytes > part_max ? q.part_bytes : part_max;
+      if (h.M > 8) mb = 2;
+      ++n;
+    }
+    begin = i;
+    if (n == 0) continue;
+    for (int i = n; i < kMaxProblems; ++i) {   // unused descriptors must still be valid objects
+      maps.w[i] = maps.w[0];
+      maps.s[i] = maps.s[0];
+    }
+    p.count = n;
+    p.twos_complement = zero_point == -1 ? 1 : 0;
+    p.overlap = g_table_overlap;
+    p.status = reinterpret_cast<int*>(ws);
+    size_t offset = kRingBytes;
+    offset = (offset + 15) & ~size_t(15);
+    p.span_offset = int(offset);
+    offset += kMaxSpans * 4;
+    p.corr_offset = int(offset);
+    offset += (corr_max + 15) & ~size_t(15);
+    p.xs_offset = int(offset);
+    offset += (xs_max + 15) & ~size_t(15);
+    p.part_offset = int(offset);
+    offset += (part_max + 15) & ~size_t(15);
+    const size_t smem = 1024 + offset;
+    if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // the mix of problems does not fit together
+    int status;
+#define IB200_TABLE_STEPS(MB_)                                                                  \
+  status = steps == 4   ? launch_table<T, MB_, 4>(maps, p, grid, smem, stream)                  \
+           : steps == 2 ? launch_table<T, MB_, 2>(maps, p, grid, smem, stream)                  \
+                        : launch_table<T, MB_, 1>(maps, p, grid, smem, stream);
+    if (mb == 1) {
+      IB200_TABLE_STEPS(1)
+    } else {
+      IB200_TABLE_STEPS(2)
+    }
+#undef IB200_TABLE_STEPS
+    if (status != INTENT_B200_OK) return status;
+  }
+  return INTENT_B200_OK;
+}
+
+}  // namespace
+}  // namespace ib200
+
+static_assert(sizeof(intent_b200_w4a16_problem) == sizeof(ib200::HostProblem), "table entry layout");
+
+extern "C" int64_t intent_b200_w4a16_gemv_table_workspace_bytes(const intent_b200_w4a16_problem* problems,
+                                                                int32_t count, int32_t group_size) {
+  using namespace ib200;
+  if (!problems || count <= 0 || count > 4096) return 0;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return 0;
+  for (int i = 0; i < count; ++i)
+    if (problems[i].M > 16 || problems[i].M < 0 || problems[i].K <= 0 || problems[i].N < 0 ||
+        problems[i].K > (1 << 24) || problems[i].N > (1 << 24))
+      return 0;
+  const int sms = table_sms();
+  ProblemPlan* plans = new ProblemPlan[count];
+  size_t* offsets = new size_t[count];
+  // without a visible device the size is computed for the 148-SM part this library targets
+  const int64_t need = table_workspace(reinterpret_cast<const HostProblem*>(problems), count, group_size,
+                                       sms > 0 ? sms : 148, plans, offsets);
+  delete[] plans;
+  delete[] offsets;
+  return need < 0 ? 0 : need;
+}
+
+extern "C" int intent_b200_w4a16_gemv_table_f16(const intent_b200_w4a16_problem* problems, int32_t count,
+                                                int32_t group_size, int32_t zero_point, void* workspace,
+                                                int64_t workspace_bytes, void* stream) {
+  return ib200::run_table<__half>(reinterpret_cast<const ib200::HostProblem*>(problems), count, group_size, zero_point,
+                                  workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_problem* problems, int32_t count,
+                                                 int32_t group_size, int32_t zero_point, void* workspace,
+                                                 int64_t workspace_bytes, void* stream) {
+  return ib200::run_table<__nv_bfloat16>(reinterpret_cast<const ib200::HostProblem*>(problems), count, group_size,
+                                         zero_point, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
+  ib200::g_table_overlap = enable ? 1 : 0;
+  return INTENT_B200_OK;
+}
