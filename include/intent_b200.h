@@ -155,6 +155,10 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_pr
                                                       int64_t workspace_bytes, void* stream);
 /* Programmatic dependent launch for the table entries (see intent_b200_w4a16_gemv_overlap); process-global. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_overlap(int32_t enable);
+/* Problems of at most two rows use the form of the table kernel in which every unit brings its own
+ * activations and no CTA-wide barrier separates the problems; 0 forces the staged form for them too.
+ * For measurement and tests; process-global; set it before querying the workspace size. */
+INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
 
 /* ------------------------------------------------------------------------
  * gemm_i8: C[m,n] = i32(sum_k A[m,k] * B[k,n]) + bias[n], wrapping int32.

@@ -32,6 +32,14 @@
 // Counters are left at zero for the next launch.  Partial spans at the ends of a CTA's share are
 // processed first, so their global round trips overlap the rest of the share.
 //
+// Two forms of the kernel.  STAGED (above): a CTA-wide barrier on either side of the staging of every
+// problem.  RIDE (problems of at most two rows): every unit's TMA transaction also brings the 256
+// activations per row it needs, the consuming warp derives the correction sums of its unit from them, and
+// nothing is staged - so there is no CTA-wide barrier after start-up and the warps drift apart instead of
+// re-synchronising at every problem (a ring whose slots are all requested and consumed in lock-step leaves
+// HBM idle while it computes).  Per-problem partial areas alternate between two buffers; a warp enters
+// problem i + 2 only after every warp has left problem i (a bounded wait on a shared counter).
+//
 // Every mbarrier wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the
 // workspace's status word, the CTA skips its remaining units (still meeting its barriers) and exits.
 #include <type_traits>
@@ -62,6 +70,7 @@ struct TableProblem {
   int units;           // tiles * chunks
   int each, extra;     // units per CTA: the first `extra` CTAs get each + 1
   int maxp;            // partial slots per span in scratch1
+  uint32_t magic_full, magic_cb, magic_last;   // ceil(2^32 / d) for d = tiles * cb, cb, chunks of the last block
   int* counters1;      // [nblocks * tiles] span tickets
   int* counters2;      // [tiles] tile tickets (nblocks > 1)
   float* scratch1;     // [nblocks * tiles][maxp][M][32]
@@ -76,11 +85,14 @@ struct TableParams {
   int* status;
   // shared-memory layout behind the slot ring, sized for the largest problem of the table
   int corr_offset, xs_offset, span_offset, part_offset;
+  // ride-along form: every unit brings its own activations (box of M x 256 values behind the scales)
+  int xbox_offset, xbox_bytes, finished_offset, part_stride;
 };
 
 struct TableMaps {
   CUtensorMap w[kMaxProblems];
   CUtensorMap s[kMaxProblems];
+  CUtensorMap x[kMaxProblems];   // ride-along form only
 };
 
 // What a CTA knows about its share of one problem (kept in shared memory).
@@ -98,13 +110,29 @@ struct Unit {
   int span_first, span_len;   // first unit and length of the span (tile x chunk block)
 };
 
+// u / d for 0 <= u < 2^31 with magic = ceil(2^32 / d): the product can overestimate by one, never underestimate
+__device__ __forceinline__ int fast_div(int u, int d, uint32_t magic) {
+  if (d == 1) return u;                                  // 2^32 does not fit the magic word
+  const int q = int(__umulhi(uint32_t(u), magic));
+  return q - (u - q * d < 0 ? 1 : 0);
+}
+
 __device__ __forceinline__ Unit decode_unit(const TableProblem& q, int u) {
   Unit r;
+  if (q.nblocks == 1) {                                  // one chunk block: a span is a whole column tile
+    r.block = 0;
+    r.span_len = q.chunks;
+    r.tile = fast_div(u, q.chunks, q.magic_cb);
+    r.chunk = u - r.tile * q.chunks;
+    r.span_first = u - r.chunk;
+    return r;
+  }
   const int full = q.tiles * q.cb;                       // units of a full chunk block
-  r.block = min(u / full, q.nblocks - 1);
+  r.block = min(fast_div(u, full, q.magic_full), q.nblocks - 1);
   const int rest = u - r.block * full;
-  r.span_len = min(q.cb, q.chunks - r.block * q.cb);     // only the last block can be shorter
-  r.tile = rest / r.span_len;
+  const bool last = r.block == q.nblocks - 1;            // only the last block can be shorter
+  r.span_len = last ? q.chunks - r.block * q.cb : q.cb;
+  r.tile = fast_div(rest, r.span_len, last ? q.magic_last : q.magic_cb);
   r.chunk = r.block * q.cb + (rest - r.tile * r.span_len);
   r.span_first = r.block * full + r.tile * r.span_len;
   return r;
@@ -122,7 +150,7 @@ __device__ __forceinline__ int unit_at(const Share& s, int j) {
   return s.u0 + s.head + (j - s.tail - s.head);
 }
 
-template <typename T, int MB, int STEPS, int WARPS>
+template <typename T, int MB, int STEPS, int WARPS, bool RIDE>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
   constexpr int THREADS = WARPS * 32;
@@ -146,8 +174,10 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
   uint4* xs = reinterpret_cast<uint4*>(base_ptr + p.xs_offset);
   const uint32_t xs_addr = base + uint32_t(p.xs_offset);
-  int* span_count = reinterpret_cast<int*>(base_ptr + p.span_offset);
-  float* part = reinterpret_cast<float*>(base_ptr + p.part_offset);
+  int* span_counts = reinterpret_cast<int*>(base_ptr + p.span_offset);   // RIDE: one row of tickets per problem
+  float* parts = reinterpret_cast<float*>(base_ptr + p.part_offset);
+  const uint32_t xbox_base = base + uint32_t(p.xbox_offset);
+  volatile int* finished = reinterpret_cast<volatile int*>(base_ptr + p.finished_offset);   // RIDE: warps done per problem
 
   // ---- this CTA's share of every problem ---------------------------------------------------
   if (tid < p.count) {
@@ -169,6 +199,10 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     shares[tid] = s;
   }
   if (tid == 0) abort_flag = 0;
+  if (RIDE) {
+    for (int i = tid; i < kMaxProblems * kMaxSpans; i += THREADS) span_counts[i] = 0;
+    if (tid < kMaxProblems) finished[tid] = 0;
+  }
   __syncthreads();
   if (tid == 0) {
     int first = 0;
@@ -191,14 +225,17 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const Unit u = decode_unit(q, unit_at(shares[i], seq - shares[i].first));
     const uint32_t slot = uint32_t(seq % kSlots);
     const uint32_t bar = bars + slot * 8u;
-    mbar_expect_tx(bar, kWeightBytes + GPC * 64);
+    mbar_expect_tx(bar, kWeightBytes + GPC * 64 + (RIDE ? uint32_t(q.M) * 512u : 0u));
     tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
     tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
+    if (RIDE) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], u.chunk * 256, 0, bar);
   };
-  // first wave: slot s is owned by warp s % WARPS
+  // first wave: slot s is owned by warp s % WARPS.  The ride-along form reads activations in the same
+  // transaction, so with launch overlap it has to wait for the kernel before it first.
+  if (RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (lane == 0)
     for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq);
-  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   uint32_t magic_a, magic_b;
   Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
@@ -218,10 +255,29 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const int M = q.M;
     const int part_floats = M * kCols;
 
+    int* span_count = RIDE ? span_counts + pi * kMaxSpans : span_counts;
+    float* part = RIDE ? parts + size_t(pi & 1) * p.part_stride : parts;
+    if (RIDE && pi >= 2) {
+      // the partial area of this parity was last used by problem pi - 2: every warp must have left it
+      bool ok = false;
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (finished[pi - 2] >= WARPS) { ok = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(64);
+      }
+      __threadfence_block();
+      if (!ok) {
+        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        return;
+      }
+    }
     // ---- stage this problem's activations and correction sums -------------------------------
     // corr[group][m] = - sum over the group's k of x[m,k] * (bias_k + 8); rows of one group sit in RPG
     // adjacent lanes and are added by a fixed-order butterfly.
-    {
+    if (!RIDE) {
       const uint4* xg = reinterpret_cast<const uint4*>(q.x);
       const int k8 = q.K >> 3;
       const int items = sh.rows * M;
@@ -259,7 +315,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       }
       for (int i = tid; i < kMaxSpans; i += THREADS) span_count[i] = 0;
     }
-    __syncthreads();   // staged data visible; nobody is still reading the previous problem's (see the barrier below)
+    if (!RIDE) __syncthreads();   // staged data visible; nobody still reads the previous problem's (barrier below)
 
     uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
     const int group0 = sh.row0 / RPG;   // first staged group
@@ -289,14 +345,43 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         for (int i = 0; i < 8; ++i) facc[mb][i] = 0.f;
 
       const int staged_row = u.chunk * kRows - sh.row0;   // first staged row of this unit
+      const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
+      float* my_corr = corr + warp * (GPC * CP);            // RIDE: this warp's correction sums of the unit
+      if (RIDE) {
+        // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
+        // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
+        // their share of the correction sum with the same fixed-order butterfly as the staged form
+        for (int m = 0; m < M; ++m) {
+          const uint32_t addr = xslot + uint32_t(m) * 512u + uint32_t(lane) * 16u;
+          const uint4 val = lds128(addr);
+          uint4 o;
+          o.x = prmt(val.x, val.z, 0x5410);
+          o.y = Expand<T>::scale_odd(prmt(val.x, val.z, 0x7632));
+          o.z = prmt(val.y, val.w, 0x5410);
+          o.w = Expand<T>::scale_odd(prmt(val.y, val.w, 0x7632));
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                       : "memory");
+          float partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
+                          Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
+#pragma unroll
+          for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+          if ((lane % RPG) == 0) my_corr[(lane / RPG) * CP + m] = -partial;
+        }
+        __syncwarp();
+      }
+      // Rows of X beyond M: the lanes that would hold them read row M - 1 instead.  An MMA output column depends
+      // only on its own column of the activation fragment, and output columns >= M are never stored.
+      const int m_lane = min(g, M - 1);
 #pragma unroll
       for (int gi = 0; gi < GPC; ++gi) {
         const int group = u.chunk * GPC + gi;
         float gacc[MB][8];
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
+          // (entries of rows >= M hold stale values: they only reach accumulator rows that are never stored)
           float2 c = make_float2(0.f, 0.f);
-          if (group < q.groups) c = *reinterpret_cast<const float2*>(&corr[(group - group0) * CP + mb * 8 + 2 * t]);
+          if (RIDE) c = *reinterpret_cast<const float2*>(&my_corr[gi * CP + mb * 8 + 2 * t]);
+          else if (group < q.groups) c = *reinterpret_cast<const float2*>(&corr[(group - group0) * CP + mb * 8 + 2 * t]);
 #pragma unroll
           for (int i = 0; i < 8; ++i) gacc[mb][i] = (i & 1) ? c.y : c.x;
         }
@@ -313,9 +398,9 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
           Expand<T>::word(w.w, magic_a, magic_b, c3);
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
-            uint4 b = make_uint4(0, 0, 0, 0);
-            const int m = mb * 8 + g;
-            if (m < M) b = lds128(xs_addr + uint32_t((staged_row + row) * M + m) * 16u);
+            const int m = MB == 1 ? m_lane : min(mb * 8 + g, M - 1);
+            const uint4 b = RIDE ? lds128(xslot + uint32_t(m) * 512u + uint32_t(row) * 16u)
+                                 : lds128(xs_addr + uint32_t((staged_row + row) * M + m) * 16u);
             float(&a01)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][0]);
             float(&a23)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][4]);
             Elem<T>::mma16816(a01, c0[0], c1[0], c0[1], c1[1], b.x, b.y);
@@ -454,9 +539,19 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         if (lane == 0) q.counters2[u.tile] = 0;
       }
     }
-    // everybody is done with this problem's staged activations and partials before the next problem
-    // overwrites them (the weight ring keeps streaming meanwhile)
-    __syncthreads();
+    if (RIDE) {
+      // this warp has left the problem (its partial area may be reused two problems later)
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(const_cast<int*>(&finished[pi]), 1);
+      }
+      if (*reinterpret_cast<volatile int*>(&abort_flag)) return;
+    } else {
+      // everybody is done with this problem's staged activations and partials before the next problem
+      // overwrites them (the weight ring keeps streaming meanwhile)
+      __syncthreads();
+    }
   }
 }
 
@@ -473,9 +568,15 @@ struct HostProblem {
 
 struct ProblemPlan {
   int chunks, tiles, cb, nblocks, units, each, extra, maxp;
+  bool ride;                                     // the ride-along form (no staging, no CTA barriers)
   size_t xs_bytes, corr_bytes, part_bytes;       // shared memory this problem needs (worst CTA)
   size_t counters1, counters2, scratch1, scratch2, bytes;   // workspace layout (offsets) and size
 };
+
+constexpr size_t kRingBytes = size_t(kSlots) * (kWeightBytes + kScaleBytes + 8);
+// alignment slack + ring + span tickets (one row per problem) + finished counters + rounding of the regions
+constexpr size_t kFixedBytes = 1024 + kRingBytes + 128 + kMaxProblems * kMaxSpans * 4 + 64 + 64;
+constexpr size_t kRideCorrBytes = 32 * 8 * 16 * 4;   // per-warp correction sums, widest case
 
 // Spans a CTA may touch and rows it must stage, worst case over CTAs, for a chunk-block size.
 void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched, int* spans_touched) {
@@ -488,27 +589,41 @@ void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched,
   *spans_touched = n_max <= 0 ? 0 : (n_max - 1) / (shortest < cb ? shortest : cb) + 2;
 }
 
-bool plan_problem(int M, int K, int N, int group_size, int mb, int grid, size_t smem_budget, ProblemPlan* out) {
+bool plan_problem(int M, int K, int N, int group_size, int grid, ProblemPlan* out) {
   ProblemPlan q{};
+  const size_t smem_budget = size_t(kSmemLimit) - kFixedBytes;
   q.tiles = (N + kCols - 1) / kCols;
   q.chunks = (K / 8 + kRows - 1) / kRows;
+  if ((long long)q.tiles * q.chunks > (1ll << 30)) return false;   // unit numbers are 32-bit
   q.units = q.tiles * q.chunks;
   q.each = q.units / grid;
   q.extra = q.units % grid;
   const int n_max = q.each + (q.extra ? 1 : 0);
   q.part_bytes = size_t(n_max) * M * kCols * 4;
   const int rpg = group_size / 8;
-  // the largest chunk block whose staged activations (all blocks a CTA can touch) fit beside the rest
   int cb = q.chunks;
-  for (;;) {
+  {
+    // ride-along form: the activations travel with every unit, the whole K range is one chunk block
     int blocks, spans;
     share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
-    const size_t rows = size_t(blocks) * cb * kRows;
-    q.xs_bytes = rows * M * 16;
-    q.corr_bytes = (rows / rpg + 1) * 16 * 4;   // sized for the wider correction pitch (M > 8 in the same launch)
-    if (spans <= kMaxSpans && q.xs_bytes + q.corr_bytes + q.part_bytes <= smem_budget) break;
-    if (cb == 1) return false;
-    cb = (cb + 1) / 2;
+    q.ride = M <= 2 && spans <= kMaxSpans &&
+             size_t(kSlots) * M * 512 + kRideCorrBytes + 2 * q.part_bytes <= smem_budget;
+  }
+  if (q.ride) {
+    q.xs_bytes = 0;
+    q.corr_bytes = kRideCorrBytes;
+  } else {
+    // the largest chunk block whose staged activations (all blocks a CTA can touch) fit beside the rest
+    for (;;) {
+      int blocks, spans;
+      share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
+      const size_t rows = size_t(blocks) * cb * kRows;
+      q.xs_bytes = rows * M * 16;
+      q.corr_bytes = (rows / rpg + 1) * 16 * 4;   // sized for the wider correction pitch (M > 8 in the same launch)
+      if (spans <= kMaxSpans && q.xs_bytes + q.corr_bytes + q.part_bytes <= smem_budget) break;
+      if (cb == 1) return false;
+      cb = (cb + 1) / 2;
+    }
   }
   q.cb = cb;
   q.nblocks = (q.chunks + cb - 1) / cb;
@@ -540,9 +655,7 @@ int table_sms() {
 }
 
 int g_table_overlap = 0;
-
-constexpr size_t kRingBytes = size_t(kSlots) * (kWeightBytes + kScaleBytes + 8);
-constexpr size_t kFixedBytes = 1024 + kRingBytes + 16 + kMaxSpans * 4 + 64;   // alignment slack, ring, span tickets
+int g_table_ride = 1;     // 0 forces the staged form (measurement and tests)
 
 int validate(const HostProblem& h, int group_size) {
   if (h.M < 0 || h.K < 0 || h.N < 0) return INTENT_B200_ERR_SHAPE;
@@ -554,10 +667,10 @@ int validate(const HostProblem& h, int group_size) {
   return INTENT_B200_OK;
 }
 
-template <typename T, int MB, int STEPS>
+template <typename T, int MB, int STEPS, bool RIDE>
 int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
   constexpr int WARPS = MB == 1 ? 32 : 16;
-  auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS>;
+  auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS, RIDE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return cuda_status(e);
   cudaLaunchConfig_t config = {};
@@ -591,9 +704,14 @@ int64_t table_workspace(const HostProblem* problems, int count, int group_size, 
         offsets[i] = offset;
         continue;
       }
-      const int mb = h.M <= 8 ? 1 : 2;
-      if (!plan_problem(int(h.M), int(h.K), int(h.N), group_size, mb, grid, size_t(kSmemLimit) - kFixedBytes, &plans[i]))
-        return -1;
+      if (!plan_problem(int(h.M), int(h.K), int(h.N), group_size, grid, &plans[i])) return -1;
+      if (!g_table_ride && plans[i].ride) {
+        plans[i].ride = false;     // staged form forced: the whole K range staged (it fits for M <= 2)
+        const size_t rows = size_t(plans[i].chunks) * kRows;
+        plans[i].xs_bytes = rows * size_t(h.M) * 16;
+        plans[i].corr_bytes = (rows / (group_size / 8) + 1) * 16 * 4;
+        if (plans[i].xs_bytes + plans[i].corr_bytes + plans[i].part_bytes > size_t(kSmemLimit) - kFixedBytes) return -1;
+      }
       offsets[i] = offset;
       offset += plans[i].bytes;
     }
@@ -632,22 +750,40 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   const int steps = group_size / 32;
 
   // Problems that share a launch share the space behind the slot ring, each region sized for the largest of
-  // them: a launch takes as many consecutive problems (at most kMaxProblems) as fit together.
+  // them: a launch takes as many problems (at most kMaxProblems) of one form as fit together.  The problems are
+  // independent, so they may run in any order: the ride-along ones first, then the staged ones.
   const size_t behind_ring = size_t(kSmemLimit) - kFixedBytes;
+  int* order = new int[count];
+  struct OrderCleanup {
+    int* a;
+    ~OrderCleanup() { delete[] a; }
+  } order_cleanup{order};
+  {
+    int k = 0;
+    for (int pass = 0; pass < 2; ++pass)
+      for (int i = 0; i < count; ++i)
+        if ((pass == 0) == plans[i].ride) order[k++] = i;
+  }
   for (int begin = 0; begin < count;) {
     TableMaps maps;
     TableParams p{};
     size_t xs_max = 0, corr_max = 0, part_max = 0;
-    int n = 0, mb = 1, i = begin;
+    int n = 0, mb = 1, i = begin, rows_max = 0;
+    bool ride = false;
     for (; i < count && n < kMaxProblems; ++i) {
-      const HostProblem& h = problems[i];
+      const int index = order[i];
+      const HostProblem& h = problems[index];
       if (h.M <= 0 || h.N <= 0) continue;   // nothing to compute
-      const ProblemPlan& q = plans[i];
+      const ProblemPlan& q = plans[index];
+      if (n == 0) ride = q.ride;
+      if (q.ride != ride) break;            // a launch is one form of the kernel
       {
         const size_t xs = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
         const size_t corr_b = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
         const size_t part_b = q.part_bytes > part_max ? q.part_bytes : part_max;
-        if (n > 0 && xs + corr_b + part_b > behind_ring) break;
+        const int rows = int(h.M) > rows_max ? int(h.M) : rows_max;
+        const size_t together = ride ? size_t(kSlots) * rows * 512 + corr_b + 2 * part_b : xs + corr_b + part_b;
+        if (n > 0 && together > behind_ring) break;
       }
       TableProblem& d = p.problem[n];
       d.x = h.x;
@@ -664,16 +800,27 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
       d.each = q.each;
       d.extra = q.extra;
       d.maxp = q.maxp;
-      d.counters1 = reinterpret_cast<int*>(ws + offsets[i] + q.counters1);
-      d.counters2 = reinterpret_cast<int*>(ws + offsets[i] + q.counters2);
-      d.scratch1 = reinterpret_cast<float*>(ws + offsets[i] + q.scratch1);
-      d.scratch2 = reinterpret_cast<float*>(ws + offsets[i] + q.scratch2);
+      {
+        auto magic = [](long long divisor) { return uint32_t(((1ll << 32) + divisor - 1) / divisor); };
+        const int last_len = q.chunks - (q.nblocks - 1) * q.cb;
+        d.magic_full = magic((long long)q.tiles * q.cb);
+        d.magic_cb = magic(q.cb);
+        d.magic_last = magic(last_len);
+      }
+      d.counters1 = reinterpret_cast<int*>(ws + offsets[index] + q.counters1);
+      d.counters2 = reinterpret_cast<int*>(ws + offsets[index] + q.counters2);
+      d.scratch1 = reinterpret_cast<float*>(ws + offsets[index] + q.scratch1);
+      d.scratch2 = reinterpret_cast<float*>(ws + offsets[index] + q.scratch2);
       if (!make_tensor_map_2d(&maps.w[n], CU_TENSOR_MAP_DATA_TYPE_INT32, h.w, uint64_t(h.K / 8), uint64_t(h.N),
                               uint64_t(h.N) * 4, kRows, kCols, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
           !make_tensor_map_2d(&maps.s[n], xt, h.s, uint64_t(h.K / group_size), uint64_t(h.N), uint64_t(h.N) * 2,
                               uint32_t(256 / group_size), kCols, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INTENT_B200_ERR_UNSUPPORTED;
+      if (ride && !make_tensor_map_2d(&maps.x[n], xt, h.x, uint64_t(h.M), uint64_t(h.K), uint64_t(h.K) * 2,
+                                      uint32_t(h.M), 256, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INTENT_B200_ERR_UNSUPPORTED;
+      if (int(h.M) > rows_max) rows_max = int(h.M);
       xs_max = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
       corr_max = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
       part_max = q.part_bytes > part_max ? q.part_bytes : part_max;
@@ -682,35 +829,45 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     }
     begin = i;
     if (n == 0) continue;
-    for (int i = n; i < kMaxProblems; ++i) {   // unused descriptors must still be valid objects
-      maps.w[i] = maps.w[0];
-      maps.s[i] = maps.s[0];
+    for (int k = 0; k < kMaxProblems; ++k) {   // unused descriptors must still be valid objects
+      if (k >= n) {
+        maps.w[k] = maps.w[0];
+        maps.s[k] = maps.s[0];
+      }
+      if (k >= n || !ride) maps.x[k] = maps.w[0];
     }
     p.count = n;
     p.twos_complement = zero_point == -1 ? 1 : 0;
     p.overlap = g_table_overlap;
     p.status = reinterpret_cast<int*>(ws);
-    size_t offset = kRingBytes;
-    offset = (offset + 15) & ~size_t(15);
+    size_t offset = (kRingBytes + 127) & ~size_t(127);
+    p.xbox_offset = int(offset);
+    p.xbox_bytes = ride ? rows_max * 512 : 0;
+    offset += size_t(kSlots) * p.xbox_bytes;
     p.span_offset = int(offset);
-    offset += kMaxSpans * 4;
+    offset += size_t(ride ? kMaxProblems : 1) * kMaxSpans * 4;
+    p.finished_offset = int(offset);
+    offset += 64;
     p.corr_offset = int(offset);
     offset += (corr_max + 15) & ~size_t(15);
     p.xs_offset = int(offset);
     offset += (xs_max + 15) & ~size_t(15);
     p.part_offset = int(offset);
-    offset += (part_max + 15) & ~size_t(15);
+    p.part_stride = int(((part_max + 15) & ~size_t(15)) / 4);      // in floats
+    offset += ((part_max + 15) & ~size_t(15)) * (ride ? 2 : 1);
     const size_t smem = 1024 + offset;
-    if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // the mix of problems does not fit together
+    if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned to fit
     int status;
-#define IB200_TABLE_STEPS(MB_)                                                                  \
-  status = steps == 4   ? launch_table<T, MB_, 4>(maps, p, grid, smem, stream)                  \
-           : steps == 2 ? launch_table<T, MB_, 2>(maps, p, grid, smem, stream)                  \
-                        : launch_table<T, MB_, 1>(maps, p, grid, smem, stream);
-    if (mb == 1) {
-      IB200_TABLE_STEPS(1)
+#define IB200_TABLE_STEPS(MB_, RIDE_)                                                           \
+  status = steps == 4   ? launch_table<T, MB_, 4, RIDE_>(maps, p, grid, smem, stream)           \
+           : steps == 2 ? launch_table<T, MB_, 2, RIDE_>(maps, p, grid, smem, stream)           \
+                        : launch_table<T, MB_, 1, RIDE_>(maps, p, grid, smem, stream);
+    if (ride) {
+      IB200_TABLE_STEPS(1, true)        // the ride-along form is only planned for M <= 2
+    } else if (mb == 1) {
+      IB200_TABLE_STEPS(1, false)
     } else {
-      IB200_TABLE_STEPS(2)
+      IB200_TABLE_STEPS(2, false)
     }
 #undef IB200_TABLE_STEPS
     if (status != INTENT_B200_OK) return status;
@@ -759,5 +916,10 @@ extern "C" int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_problem
 
 extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
   ib200::g_table_overlap = enable ? 1 : 0;
+  return INTENT_B200_OK;
+}
+
+extern "C" int intent_b200_w4a16_gemv_table_ride(int32_t enable) {
+  ib200::g_table_ride = enable ? 1 : 0;
   return INTENT_B200_OK;
 }

@@ -73,8 +73,30 @@ def test_mixed_table_matches_oracle(cuda_device, dtype, group):
     assert call.single_launch
     before = native.launch_count()
     call.launch()
-    assert native.launch_count() - before == 2                    # ten problems: eight and two
+    assert native.launch_count() - before == 2                    # ten problems: the one- and two-row ones, the rest
     _check(call, host, group, 8, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_both_forms_of_the_table_kernel(cuda_device, dtype):
+    """Problems of one or two rows run in the barrier-free form (every unit brings its activations); the
+    staged form can be forced for them.  Both must meet the oracle, and a long table must keep the per-problem
+    partial areas apart (eight problems per launch alternate between two buffers)."""
+    from intent_b200 import table as table_module
+
+    shapes = [(1, 4096, 14336), (2, 14336, 4096), (1, 4096, 4096), (2, 256, 72), (1, 14336, 4096), (1, 1024, 64),
+              (2, 4096, 14336), (1, 128, 8), (1, 11008, 4096)]
+    host, dev = _problems(shapes, dtype, 128, cuda_device, seed=40)
+    table = W4A16Table(group_size=128, zero_point=8, act_dtype="f16" if dtype == torch.float16 else "bf16",
+                       target=ib.B200Target(0))
+    try:
+        table_module.set_ride_along(False)
+        staged = _check(table.prepare(dev), host, 128, 8, dtype)
+    finally:
+        table_module.set_ride_along(True)
+    riding = _check(table.prepare(dev), host, 128, 8, dtype)
+    for a, b in zip(staged, riding):
+        assert max_abs_rel(a.cpu(), b.cpu()) <= (2e-3 if dtype == torch.float16 else 1.6e-2)
 
 
 def test_table_agrees_with_single_problem_entry(cuda_device):
