@@ -58,6 +58,16 @@ INTENT_B200_API const char* intent_b200_status_string(int status);
  * entries, all streams).  Used by the benchmark to report its launch count. */
 INTENT_B200_API int64_t intent_b200_launch_count(void);
 
+/* Dry-run observation (the reference's NativeObservation reports registers, spills, shared memory and the
+ * selected configuration of the latest native call, python/intent/runtime/diagnostics.py:119-137).  Between
+ * begin and end, on the calling thread, the entries of the bandwidth / dense / grouped kernels launch nothing
+ * and record what they would launch into `facts`: eight int32 (valid, registers per thread, local-memory bytes
+ * per thread = spills, static shared bytes, dynamic shared bytes, threads per CTA, CTAs, CTAs per cluster)
+ * followed by 64 bytes holding the kernel family and the plan's choice.  The small routing kernels do not
+ * take part (they launch as usual). */
+INTENT_B200_API int intent_b200_observe_begin(void* facts);
+INTENT_B200_API int intent_b200_observe_end(void);
+
 /* ------------------------------------------------------------------------
  * weight_only_int4_matmul  (W4A16)
  * Replaces the provider lowering of
@@ -360,6 +370,28 @@ INTENT_B200_API int intent_b200_dequant_bf16_fp4_matmul(INTENT_B200_VIEW2(a0), I
 INTENT_B200_API int intent_b200_quantized_projection(INTENT_B200_VIEW3(a0), INTENT_B200_VIEW2(a1),
                                                      INTENT_B200_VIEW1(a2), void* workspace,
                                                      int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * entry_benchmark counterparts of the reference's native ABI, which exports
+ * `double entry_benchmark(slots..., int64 repetitions)` beside every `entry(slots...)`
+ * (python/intent/runtime/mojo/compilation.py:54-96, python/intent/runtime/mojo/program.py:253-257).
+ * Same slots as the entry, then `repetitions`, then the stream.  One untimed call first, then
+ * `repetitions` calls between two CUDA events on `stream` (the events are the only synchronisation).
+ * Returns the mean milliseconds per call, or minus the status code of a failed call.
+ * ------------------------------------------------------------------------ */
+#define INTENT_B200_W4A16_BENCHMARK_SLOTS                                                         \
+  INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),     \
+      int32_t group_size, int32_t zero_point, void *workspace, int64_t workspace_bytes,          \
+      int64_t repetitions, void *stream
+INTENT_B200_API double intent_b200_weight_only_int4_matmul_f16_benchmark(INTENT_B200_W4A16_BENCHMARK_SLOTS);
+INTENT_B200_API double intent_b200_weight_only_int4_matmul_bf16_benchmark(INTENT_B200_W4A16_BENCHMARK_SLOTS);
+INTENT_B200_API double intent_b200_gemm_i8_benchmark(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                     INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3),
+                                                     int64_t repetitions, void* stream);
+INTENT_B200_API double intent_b200_w8a8_gemm_bf16_benchmark(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1),
+                                                            INTENT_B200_VIEW1(a2), INTENT_B200_VIEW1(a3),
+                                                            INTENT_B200_VIEW2(a4), int64_t repetitions,
+                                                            void* stream);
 
 /* ------------------------------------------------------------------------
  * W4A16 bandwidth kernel (f16) without any workspace argument.

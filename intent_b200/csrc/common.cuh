@@ -23,6 +23,24 @@ inline int cuda_status(cudaError_t error) {
 // would also see sticky errors of unrelated work; cudaGetLastError clears ours).
 inline int launch_status() { return cuda_status(cudaGetLastError()); }
 
+// Dry-run observation of a launch: while a sink is installed on the calling thread (intent_b200_observe_begin),
+// the main compute kernels' launch sites fill it with what they WOULD launch - the kernel instance's resource
+// usage from cudaFuncGetAttributes and the launch plan - and launch nothing.
+struct LaunchFacts {
+  int valid;
+  int registers;        // per thread
+  int local_bytes;      // per-thread local memory (register spills land here)
+  int static_smem;      // bytes
+  int dynamic_smem;     // bytes requested by this launch
+  int threads;          // per CTA
+  int grid;             // CTAs
+  int cluster;          // CTAs per cluster (1 = none)
+  char kernel[64];      // kernel family and the plan's distinguishing choice
+};
+LaunchFacts* observe_sink();
+int record_launch(LaunchFacts* sink, const void* kernel, const char* name, int grid, int threads, int dynamic_smem,
+                  int cluster);
+
 struct View2 {
   void* p;
   int64_t d0, d1, s0, s1;

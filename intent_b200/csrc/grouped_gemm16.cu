@@ -400,6 +400,9 @@ int launch(const Problem& q, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_status(e);
   const int grid = int(tile_bound < sms ? (tile_bound > 0 ? tile_bound : 1) : sms);
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "grouped_gemm16_kernel 128x256 tiles", grid,
+                         THREADS, SMEM_BYTES, 1);
   kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   note_launch();
   return launch_status();
@@ -410,6 +413,7 @@ int gather(const void* x, int64_t tokens, int64_t width, const int32_t* members,
            const int32_t* route_token, int64_t routes, void* out, cudaStream_t stream) {
   if (count == 0 || width == 0) return INTENT_B200_OK;
   const int64_t blocks = count < 148 * 16 ? count : 148 * 16;
+  if (observe_sink()) return INTENT_B200_OK;      // the contraction behind this gather is what gets observed
   gather16_kernel<BY_TABLE><<<int(blocks), 256, 0, stream>>>(static_cast<const uint4*>(x), tokens, int(width / 8),
                                                             members, int(count), top_k, route_token, routes,
                                                             static_cast<uint4*>(out));

@@ -523,6 +523,10 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel),
+                         MT == 2 ? "w4a16_gemm_kernel single CTA, 256x256 tiles" : "w4a16_gemm_kernel single CTA, 128x256 tiles",
+                         grid, THREADS, smem, 1);
   kernel<<<grid, THREADS, smem, stream>>>(map_x, p);
   note_launch();
   return launch_status();

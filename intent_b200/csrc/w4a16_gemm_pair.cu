@@ -421,6 +421,9 @@ int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const vo
   const int tiles = p.m_tiles * p.n_tiles;
   int pairs = sms / 2;
   if (pairs > tiles) pairs = tiles;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "w4a16_gemm_pair_kernel CTA pairs, 512x256 tiles",
+                         2 * pairs, THREADS, SMEM_BYTES, 2);
   kernel<<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(map_x, p);
   note_launch();
   return launch_status();

@@ -591,6 +591,11 @@ int launch_kernel(const CUtensorMap& map_w, const CUtensorMap& map_s, const CUte
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = p.overlap ? 1 : 0;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel),
+                         XSTAGED ? (RING ? "w4a16_stream_kernel staged activations, slot ring" : "w4a16_stream_kernel staged activations")
+                                 : (RING ? "w4a16_stream_kernel activations per unit, slot ring" : "w4a16_stream_kernel activations per unit"),
+                         plan.grid, WARPS * 32, int(plan.smem_bytes), 1);
   e = cudaLaunchKernelEx(&config, kernel, map_w, map_s, map_x, p);
   if (e != cudaSuccess) return cuda_status(e);
   note_launch();

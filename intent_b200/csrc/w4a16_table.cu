@@ -683,6 +683,10 @@ int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t s
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = p.overlap ? 1 : 0;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel),
+                         RIDE ? "w4a16_table_kernel activations ride with the units" : "w4a16_table_kernel staged activations",
+                         grid, WARPS * 32, int(smem), 1);
   e = cudaLaunchKernelEx(&config, kernel, maps, p);
   if (e != cudaSuccess) return cuda_status(e);
   note_launch();

@@ -254,6 +254,9 @@ int run(View2 a, View2 b, void* out, const int32_t* bias, const float* sa, const
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "i8_gemm_kernel 128x256 tiles, two accumulators",
+                         tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, 1);
   kernel<<<tiles < sms ? tiles : sms, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   note_launch();
   return launch_status();

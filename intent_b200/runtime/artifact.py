@@ -25,7 +25,10 @@ from .interface import BoundArguments, PublicInterface, ScalarParameter, ViewPar
 
 @dataclass(frozen=True, slots=True)
 class NativeObservation:
-    """Facts about the latest invocation of an entry (never an estimate)."""
+    """Facts about the latest invocation of an entry (never an estimate).  The resource fields are what the
+    reference's observation reports for a native call (registers, spills, shared memory, the selected
+    configuration: python/intent/runtime/diagnostics.py:119-137); they come from the library's dry-run
+    observation of the same slots and are None for entries whose kernels do not take part in it."""
 
     provider: str
     entry: str
@@ -34,6 +37,27 @@ class NativeObservation:
     arguments: tuple          # per view: (name, shape, strides)
     workspace_bytes: int
     status: int
+    kernel: str | None = None            # kernel family and the launch plan's choice
+    registers: int | None = None         # per thread
+    spill_bytes: int | None = None       # per-thread local memory
+    shared_static: int | None = None     # bytes
+    shared_dynamic: int | None = None    # bytes
+    threads: int | None = None           # per CTA
+    grid: int | None = None              # CTAs
+    cluster: int | None = None           # CTAs per cluster
+
+
+class _LaunchFacts(ctypes.Structure):
+    _fields_ = [("valid", ctypes.c_int32), ("registers", ctypes.c_int32), ("local_bytes", ctypes.c_int32),
+                ("static_smem", ctypes.c_int32), ("dynamic_smem", ctypes.c_int32), ("threads", ctypes.c_int32),
+                ("grid", ctypes.c_int32), ("cluster", ctypes.c_int32), ("kernel", ctypes.c_char * 64)]
+
+
+# entries made only of kernels that honour the dry-run observation
+_OBSERVABLE = ("intent_b200_weight_only_int4_matmul", "intent_b200_w4a16_gemv", "intent_b200_w4a16_gemm",
+               "intent_b200_gemm_i8", "intent_b200_w8a8_gemm", "intent_b200_ragged_grouped_gemm",
+               "intent_b200_routed_expert_projection", "intent_b200_moe_expert_ffn", "intent_b200_gemm_f16",
+               "intent_b200_bf16_gemm", "intent_b200_quantized_gemm", "intent_b200_moe_grouped_w4a16")
 
 
 class PreparedCall:
@@ -46,6 +70,7 @@ class PreparedCall:
         self._slots = program.marshal(bound, self._workspace)
         self._observation: NativeObservation | None = None
         self._skip = program.is_empty(bound)
+        self._facts: dict | None = None     # resource facts of this binding, observed once
 
     @property
     def outputs(self) -> tuple:
@@ -85,17 +110,39 @@ class PreparedCall:
 
     __call__ = launch
 
+    def _observe(self, stream: int) -> dict:
+        """The same slots once more in the library's dry-run mode: nothing is launched, the entry reports the
+        kernel instance it selects for them and that instance's resource usage."""
+        program = self.program
+        if not program.entry_name.startswith(_OBSERVABLE):
+            return {}
+        library = native.library()
+        facts = _LaunchFacts()
+        if library.intent_b200_observe_begin(ctypes.byref(facts)) != 0:
+            return {}
+        try:
+            status = program.function()(*self._slots, ctypes.c_void_p(stream))
+        finally:
+            library.intent_b200_observe_end()
+        if status != 0 or not facts.valid:
+            return {}
+        return {"kernel": facts.kernel.decode(), "registers": facts.registers, "spill_bytes": facts.local_bytes,
+                "shared_static": facts.static_smem, "shared_dynamic": facts.dynamic_smem, "threads": facts.threads,
+                "grid": facts.grid, "cluster": facts.cluster}
+
     def _invoke(self) -> None:
         import torch
 
         program = self.program
         stream = torch.cuda.current_stream(program.device).cuda_stream
         status = program.function()(*self._slots, ctypes.c_void_p(stream))
+        if self._facts is None:
+            self._facts = self._observe(stream) if status == 0 else {}
         observation = NativeObservation(
             "b200", program.entry_name, "launched" if status == 0 else "failed", program.constants,
             tuple((p.name, f.shape, f.strides) for p, f in zip(program.interface.parameters, self.invocation.views)
                   if f is not None),
-            sum(w.numel() * w.element_size() for w in self._workspace), int(status))
+            sum(w.numel() * w.element_size() for w in self._workspace), int(status), **self._facts)
         self._observation = observation
         program._observation = observation
         native.check(status, program.entry_name, observation)

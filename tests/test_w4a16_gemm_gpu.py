@@ -73,6 +73,9 @@ def test_gemm_full_size_prefill_rows(cuda_device):
     torch.cuda.synchronize()
     assert _device_status() == 0
     assert torch.equal(doubled, out * 2)
+    seen = artifact.observation            # the plan this shape selects: CTA pairs, one pair per two SMs
+    assert seen.kernel.startswith("w4a16_gemm_pair_kernel") and seen.cluster == 2 and seen.grid % 2 == 0
+    assert seen.registers > 0 and seen.shared_dynamic > 100 * 1024
     # 80 rows: five in each of the 16 pair tiles of 512 rows - first and last row of the tile, and rows of
     # both CTAs of the pair (each owns 256 rows) and of both of their 128-row blocks
     rows = torch.cat([torch.tensor([0, 130, 255, 300, 511]) + 512 * tile for tile in range(16)])

@@ -173,6 +173,10 @@ def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
     torch.cuda.synchronize()
     assert torch.equal(held, expected)
     assert artifact.observation is not None and artifact.observation.status == 0
+    # resource facts of the selected kernel instance (from a dry run of the same slots; nothing is launched)
+    seen = call.observation
+    assert seen.kernel.startswith("w4a16_stream_kernel") and seen.threads in (512, 1024) and seen.grid >= 1
+    assert 0 < seen.registers <= 255 and seen.spill_bytes == 0 and seen.shared_dynamic > 0 and seen.cluster == 1
     # torch custom operator with a fake implementation
     op = artifact.as_torch_op("intent_b200_test::w4a16")
     assert torch.equal(op(xd, pd, sd), expected)
