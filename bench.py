@@ -368,6 +368,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
         clocks = sampler.stop() if rank == 0 else None
         return reduce_max(start.elapsed_time(stop), world, device), launches, clocks
 
+    modes = set(args.decode_modes.split(","))
     # ---- one launch per step: the two projections as one table ----------------------------------
     table_module.set_launch_overlap(True)     # static weights: a launch may request them while its predecessor drains
     step_calls = [table.prepare([(xs[j], p, s) for j, (p, s) in enumerate(group)]) for group in weights.sets]
@@ -382,7 +383,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
 
     # ---- eight steps per call ---------------------------------------------------------------------
     long_calls = []
-    for first in range(0, copies, 1):
+    for first in range(copies if "long" in modes else 0):
         problems = []
         for k in range(8):
             group = weights.sets[(first + k) % copies]
@@ -393,25 +394,30 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
         if i % 8 == 0:
             long_calls[(i // 8) % len(long_calls)].launch()
 
-    long_ms, long_launches, _ = graph_time(long_step, 0.2)
-    for call in long_calls:
-        call.check()
+    long_ms, long_launches = None, 0
+    if long_calls:
+        long_ms, long_launches, _ = graph_time(long_step, 0.2)
+        for call in long_calls:
+            call.check()
     table_module.set_launch_overlap(False)
     del long_calls
 
     # ---- one launch per projection (single-problem artifact) ----------------------------------------
-    native.set_gemv_launch_overlap(True)
-    calls = [[artifact.prepare(xs[j], p, s) for j, (p, s) in enumerate(group)] for group in weights.sets]
+    single_ms, single_launches = None, 0
+    if "projection" in modes:
+        native.set_gemv_launch_overlap(True)
+        calls = [[artifact.prepare(xs[j], p, s) for j, (p, s) in enumerate(group)] for group in weights.sets]
 
-    def projection_step(i: int) -> None:
-        for call in calls[i % copies]:
-            call.launch()
+        def projection_step(i: int) -> None:
+            for call in calls[i % copies]:
+                call.launch()
 
-    single_ms, single_launches, _ = graph_time(projection_step, 0.2)
-    for group in calls:
-        for call in group:
-            call.check()
-    native.set_gemv_launch_overlap(False)
+        single_ms, single_launches, _ = graph_time(projection_step, 0.2)
+        for group in calls:
+            for call in group:
+                call.check()
+        native.set_gemv_launch_overlap(False)
+        del calls
 
     # ---- end to end: host activations in, results back, one table launch per step --------------------
     pinned_in = [x.pin_memory() for x in host_x]
@@ -452,6 +458,8 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
                        "; programmatic dependent launch between consecutive steps (static weights)"}
 
     def mode(ms_total, n_launches):
+        if ms_total is None:
+            return None
         per_step = ms_total / steps
         return {"ms_per_step": round(per_step, 6), "GBps": round(step_bytes / (per_step * 1e-3) / 1e9, 1),
                 "frac_of_hbm_peak": round(step_bytes / (per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
@@ -1275,6 +1283,9 @@ def main() -> int:
     parser.add_argument("--moe-graph", action="store_true",
                         help="replay the expert-parallel step (peer exchange) as one CUDA graph")
     parser.add_argument("--no-decode", action="store_true", help="same as --attach none")
+    parser.add_argument("--decode-modes", default="long,projection",
+                        help="extra decode measurements beside the one-launch-per-step table: 'long' (eight steps "
+                             "per call), 'projection' (one launch per projection); '' = none (for profiling)")
     args = parser.parse_args()
     if args.steps is None:
         args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20, "grouped": 50}[args.workload]

@@ -218,8 +218,8 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   const int total = total_units;
 
   // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).
-  auto issue = [&](int seq) {
-    int i = 0;
+  auto issue = [&](int seq, int hint) {
+    int i = hint;                        // the sequence only moves forward: start at the caller's problem
     while (i + 1 < p.count && seq >= shares[i + 1].first) ++i;
     const TableProblem& q = p.problem[i];
     const Unit u = decode_unit(q, unit_at(shares[i], seq - shares[i].first));
@@ -234,7 +234,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   // transaction, so with launch overlap it has to wait for the kernel before it first.
   if (RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (lane == 0)
-    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq);
+    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0);
   if (!RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   uint32_t magic_a, magic_b;
@@ -257,23 +257,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
 
     int* span_count = RIDE ? span_counts + pi * kMaxSpans : span_counts;
     float* part = RIDE ? parts + size_t(pi & 1) * p.part_stride : parts;
-    if (RIDE && pi >= 2) {
-      // the partial area of this parity was last used by problem pi - 2: every warp must have left it
-      bool ok = false;
-      for (int spin = 0; spin < (1 << 22); ++spin) {
-        if (finished[pi - 2] >= WARPS) { ok = true; break; }
-        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
-        __nanosleep(64);
-      }
-      __threadfence_block();
-      if (!ok) {
-        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
-          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
-          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-        }
-        return;
-      }
-    }
+    bool area_checked = !RIDE || pi < 2;   // RIDE: the partial area of this parity was last used by problem pi - 2
     // ---- stage this problem's activations and correction sums -------------------------------
     // corr[group][m] = - sum over the group's k of x[m,k] * (bias_k + 8); rows of one group sit in RPG
     // adjacent lanes and are added by a fixed-order butterfly.
@@ -429,9 +413,29 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       if (seq + kSlots < total) {
         __syncwarp();
         fence_proxy_async();
-        if (lane == 0) issue(seq + kSlots);
+        if (lane == 0) issue(seq + kSlots, pi);
       }
 
+      if (RIDE && !area_checked) {
+        // Before this warp's first write into the problem's partial area: every warp must have left problem
+        // pi - 2, which used the same area.  Checked here, after the unit's data has arrived and been
+        // multiplied, because by then it practically always holds (the wait above was the long one).
+        bool ok = false;
+        for (int spin = 0; spin < (1 << 20); ++spin) {
+          if (finished[pi - 2] >= WARPS) { ok = true; break; }
+          if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+          __nanosleep(256);
+        }
+        __threadfence_block();
+        if (!ok) {
+          if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+            atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+          }
+          break;
+        }
+        area_checked = true;
+      }
       // ---- level 1: the unit's partial joins its span's partials in shared memory --------------
       // accumulator element (mb, i): row m = 8*mb + 2t + (i & 1), column 4g + (i >> 1)
       const int seg_begin = max(u.span_first, sh.u0), seg_end = min(u.span_first + u.span_len, sh.u1);
