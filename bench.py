@@ -323,6 +323,10 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
     load_seconds = args.load_seconds if load_seconds is None else load_seconds
     weights = weights or DecodeWeights(device)
     table = table_module.W4A16Table(group_size=GROUP, zero_point=8, act_dtype="f16", target=ib.B200Target(device.index))
+    tune = native.library().intent_b200_w4a16_gemv_table_tune
+    for item in filter(None, args.table_tune.split(",")):
+        knob, _, number = item.partition("=")
+        native.check(tune(knob.encode(), int(number)), "intent_b200_w4a16_gemv_table_tune")
     artifact = table.artifact
     host_x = [x for x, _, _ in decode_inputs(M)]
     xs = [x.to(device) for x in host_x]
@@ -399,6 +403,14 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
         long_ms, long_launches, _ = graph_time(long_step, 0.2)
         for call in long_calls:
             call.check()
+    # ---- what the slot ring alone can stream: the same long table with every unit's arithmetic skipped -------
+    probe_ms, probe_launches = None, 0
+    if long_calls and "probe" in modes:
+        native.check(tune(b"probe", 1), "intent_b200_w4a16_gemv_table_tune")
+        try:
+            probe_ms, probe_launches, _ = graph_time(long_step, 0.2)
+        finally:
+            native.check(tune(b"probe", 0), "intent_b200_w4a16_gemv_table_tune")
     table_module.set_launch_overlap(False)
     del long_calls
 
@@ -481,6 +493,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
                      "us_per_projection": round(ms_per_step * 1e3 / len(DECODE_SHAPES), 3)},
         "modes": {"table_one_launch_per_step": mode(elapsed_ms, launches),
                   "table_eight_steps_per_call": mode(long_ms, long_launches),
+                  "stream_only_probe_eight_steps_per_call": mode(probe_ms, probe_launches),
                   "one_launch_per_projection": mode(single_ms, single_launches)},
         "e2e": {"value": round(world * step_bytes / (e2e_s / e2e_steps) / 1e9, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(x.numel() * 2 for x in pinned_in),
@@ -1283,9 +1296,14 @@ def main() -> int:
     parser.add_argument("--moe-graph", action="store_true",
                         help="replay the expert-parallel step (peer exchange) as one CUDA graph")
     parser.add_argument("--no-decode", action="store_true", help="same as --attach none")
-    parser.add_argument("--decode-modes", default="long,projection",
+    parser.add_argument("--table-tune", default="",
+                        help="measurement knobs of the table kernel, e.g. 'warps=16,areas=4' "
+                             "(see intent_b200_w4a16_gemv_table_tune)")
+    parser.add_argument("--decode-modes", default="long,probe,projection",
                         help="extra decode measurements beside the one-launch-per-step table: 'long' (eight steps "
-                             "per call), 'projection' (one launch per projection); '' = none (for profiling)")
+                             "per call), 'probe' (the long table with the arithmetic skipped: the ring's streaming "
+                             "ceiling; results are wrong by design and are not read), 'projection' (one launch per "
+                             "projection); '' = none (for profiling)")
     args = parser.parse_args()
     if args.steps is None:
         args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20, "grouped": 50}[args.workload]

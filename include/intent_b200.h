@@ -169,6 +169,10 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_overlap(int32_t enable);
  * activations and no CTA-wide barrier separates the problems; 0 forces the staged form for them too.
  * For measurement and tests; process-global; set it before querying the workspace size. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
+/* Measurement knobs of that form (process-global): "warps" 16 | 32 | 0 = built-in choice; "areas" 2 | 4 partial
+ * areas, 0 = built-in choice; "probe" 1 = stream-only launch (the arithmetic of every unit is skipped, so the
+ * results are WRONG by design: it shows what the slot ring alone can stream), 0 = normal. */
+INTENT_B200_API int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value);
 
 /* ------------------------------------------------------------------------
  * gemm_i8: C[m,n] = i32(sum_k A[m,k] * B[k,n]) + bias[n], wrapping int32.

@@ -37,8 +37,9 @@
 // activations per row it needs, the consuming warp derives the correction sums of its unit from them, and
 // nothing is staged - so there is no CTA-wide barrier after start-up and the warps drift apart instead of
 // re-synchronising at every problem (a ring whose slots are all requested and consumed in lock-step leaves
-// HBM idle while it computes).  Per-problem partial areas alternate between two buffers; a warp enters
-// problem i + 2 only after every warp has left problem i (a bounded wait on a shared counter).
+// HBM idle while it computes).  Per-problem partial areas rotate through four buffers (two when four do not
+// fit); a warp writes its first partial of problem i + 4 only after every warp has left problem i (a bounded
+// wait on a shared counter that practically never has to wait).
 //
 // Every mbarrier wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the
 // workspace's status word, the CTA skips its remaining units (still meeting its barriers) and exits.
@@ -87,6 +88,8 @@ struct TableParams {
   int corr_offset, xs_offset, span_offset, part_offset;
   // ride-along form: every unit brings its own activations (box of M x 256 values behind the scales)
   int xbox_offset, xbox_bytes, finished_offset, part_stride;
+  int part_depth;     // ride-along form: partial areas the problems rotate through (2 or 4)
+  int probe;          // measurement only: 1 = skip the arithmetic of every unit (stream and reduction traffic only)
 };
 
 struct TableMaps {
@@ -217,25 +220,29 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   __syncthreads();
   const int total = total_units;
 
-  // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).
-  auto issue = [&](int seq, int hint) {
+  // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).  `parts`: 1 = packed
+  // weights and scales (and the barrier's byte count for everything), 2 = the activations that ride along, 3 = both.
+  auto issue = [&](int seq, int hint, int parts) {
     int i = hint;                        // the sequence only moves forward: start at the caller's problem
     while (i + 1 < p.count && seq >= shares[i + 1].first) ++i;
     const TableProblem& q = p.problem[i];
     const Unit u = decode_unit(q, unit_at(shares[i], seq - shares[i].first));
     const uint32_t slot = uint32_t(seq % kSlots);
     const uint32_t bar = bars + slot * 8u;
-    mbar_expect_tx(bar, kWeightBytes + GPC * 64 + (RIDE ? uint32_t(q.M) * 512u : 0u));
-    tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
-    tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
-    if (RIDE) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], u.chunk * 256, 0, bar);
+    if (parts & 1) {
+      mbar_expect_tx(bar, kWeightBytes + GPC * 64 + (RIDE ? uint32_t(q.M) * 512u : 0u));
+      tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
+      tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
+    }
+    if (RIDE && (parts & 2)) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], u.chunk * 256, 0, bar);
   };
-  // first wave: slot s is owned by warp s % WARPS.  The ride-along form reads activations in the same
-  // transaction, so with launch overlap it has to wait for the kernel before it first.
-  if (RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // First wave: slot s is owned by warp s % WARPS.  With launch overlap the packed weights (static) are requested
+  // before the wait for the kernel ahead of this one; activations, which that kernel may have produced, after it.
   if (lane == 0)
-    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0);
-  if (!RIDE && p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0, 1);
+  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (RIDE && lane == 0)
+    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0, 2);
 
   uint32_t magic_a, magic_b;
   Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
@@ -256,8 +263,8 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const int part_floats = M * kCols;
 
     int* span_count = RIDE ? span_counts + pi * kMaxSpans : span_counts;
-    float* part = RIDE ? parts + size_t(pi & 1) * p.part_stride : parts;
-    bool area_checked = !RIDE || pi < 2;   // RIDE: the partial area of this parity was last used by problem pi - 2
+    float* part = RIDE ? parts + size_t(pi % p.part_depth) * p.part_stride : parts;
+    bool area_checked = !RIDE || pi < p.part_depth;   // RIDE: this partial area was last used by problem pi - depth
     // ---- stage this problem's activations and correction sums -------------------------------
     // corr[group][m] = - sum over the group's k of x[m,k] * (bias_k + 8); rows of one group sit in RPG
     // adjacent lanes and are added by a fixed-order butterfly.
@@ -331,7 +338,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       const int staged_row = u.chunk * kRows - sh.row0;   // first staged row of this unit
       const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
       float* my_corr = corr + warp * (GPC * CP);            // RIDE: this warp's correction sums of the unit
-      if (RIDE) {
+      if (RIDE && !p.probe) {
         // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
         // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
         // their share of the correction sum with the same fixed-order butterfly as the staged form
@@ -357,7 +364,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       // only on its own column of the activation fragment, and output columns >= M are never stored.
       const int m_lane = min(g, M - 1);
 #pragma unroll
-      for (int gi = 0; gi < GPC; ++gi) {
+      for (int gi = 0; gi < (p.probe ? 0 : GPC); ++gi) {
         const int group = u.chunk * GPC + gi;
         float gacc[MB][8];
 #pragma unroll
@@ -413,16 +420,16 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       if (seq + kSlots < total) {
         __syncwarp();
         fence_proxy_async();
-        if (lane == 0) issue(seq + kSlots, pi);
+        if (lane == 0) issue(seq + kSlots, pi, 3);
       }
 
       if (RIDE && !area_checked) {
         // Before this warp's first write into the problem's partial area: every warp must have left problem
-        // pi - 2, which used the same area.  Checked here, after the unit's data has arrived and been
+        // pi - depth, which used the same area.  Checked here, after the unit's data has arrived and been
         // multiplied, because by then it practically always holds (the wait above was the long one).
         bool ok = false;
         for (int spin = 0; spin < (1 << 20); ++spin) {
-          if (finished[pi - 2] >= WARPS) { ok = true; break; }
+          if (finished[pi - p.part_depth] >= WARPS) { ok = true; break; }
           if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
           __nanosleep(256);
         }
@@ -671,9 +678,21 @@ int validate(const HostProblem& h, int group_size) {
   return INTENT_B200_OK;
 }
 
+int g_table_warps = 0;     // ride-along form: 16 or 32 warps per CTA (0 = built-in choice); for measurement
+int g_table_probe = 0;
+int g_table_depth = 0;     // ride-along form: partial areas (2 or 4; 0 = as many as fit); for measurement
+
+template <typename T, int MB, int STEPS, bool RIDE, int WARPS>
+int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream);
+
 template <typename T, int MB, int STEPS, bool RIDE>
 int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
-  constexpr int WARPS = MB == 1 ? 32 : 16;
+  if (RIDE && g_table_warps == 16) return launch_table_warps<T, MB, STEPS, RIDE, 16>(maps, p, grid, smem, stream);
+  return launch_table_warps<T, MB, STEPS, RIDE, (MB == 1 ? 32 : 16)>(maps, p, grid, smem, stream);
+}
+
+template <typename T, int MB, int STEPS, bool RIDE, int WARPS>
+int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
   auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS, RIDE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return cuda_status(e);
@@ -862,7 +881,11 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     offset += (xs_max + 15) & ~size_t(15);
     p.part_offset = int(offset);
     p.part_stride = int(((part_max + 15) & ~size_t(15)) / 4);      // in floats
-    offset += ((part_max + 15) & ~size_t(15)) * (ride ? 2 : 1);
+    // four areas when they fit (a warp then practically never waits for the slowest warp of an older problem)
+    p.part_depth = ride && 1024 + offset + ((part_max + 15) & ~size_t(15)) * 4 <= size_t(kSmemLimit) ? 4 : 2;
+    p.probe = g_table_probe;
+    if (g_table_depth != 4) p.part_depth = 2;   // measured: two areas are faster than four (the warps stay closer together)
+    offset += ((part_max + 15) & ~size_t(15)) * (ride ? p.part_depth : 1);
     const size_t smem = 1024 + offset;
     if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned to fit
     int status;
@@ -925,6 +948,31 @@ extern "C" int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_problem
 extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
   ib200::g_table_overlap = enable ? 1 : 0;
   return INTENT_B200_OK;
+}
+
+// Measurement knobs of the ride-along form (process-global): "warps" 16 | 32 | 0 (built-in choice); "areas" 2 | 4
+// partial areas | 0 (built-in choice); "probe" 1 = stream-only (every unit's arithmetic is skipped: the results
+// are WRONG by design, the launch only shows what the ring alone can stream) | 0 = normal.
+extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value) {
+  if (!knob) return INTENT_B200_ERR_NULL;
+  const auto is = [&](const char* name) {
+    int i = 0;
+    for (; name[i] && knob[i] == name[i]; ++i) {}
+    return name[i] == 0 && knob[i] == 0;
+  };
+  if (is("warps") && (value == 0 || value == 16 || value == 32)) {
+    ib200::g_table_warps = value;
+    return INTENT_B200_OK;
+  }
+  if (is("areas") && (value == 0 || value == 2 || value == 4)) {
+    ib200::g_table_depth = value;
+    return INTENT_B200_OK;
+  }
+  if (is("probe") && (value == 0 || value == 1)) {
+    ib200::g_table_probe = value;
+    return INTENT_B200_OK;
+  }
+  return INTENT_B200_ERR_UNSUPPORTED;
 }
 
 extern "C" int intent_b200_w4a16_gemv_table_ride(int32_t enable) {
