@@ -734,6 +734,7 @@ def phase_times(launch, phases, steps: int, world: int, device):
     totals = [0.0] * len(phases)
     for _ in range(steps):
         marks = []
+        barrier(world)              # the ranks start a marked step together, so a sync phase shows only the wait
         launch(marks=marks)
         torch.cuda.synchronize()
         for i in range(len(phases)):
@@ -781,7 +782,23 @@ def run_moe(args, rank: int, world: int, device):
                     marks.append(event)
                 router.launch()
                 return chain.launch(marks=marks)
-            return launch
+
+            bound["marked"] = launch
+            if args.moe_eager:
+                return launch
+            # the bound step allocates nothing and reads nothing back: replayed as one CUDA graph, which takes
+            # the host's launch gaps between its dozen small kernels out of the step
+            for _ in range(3):
+                launch()
+            torch.cuda.synchronize()
+            from intent_b200.runtime import native
+
+            graph = torch.cuda.CUDAGraph()
+            before = native.launch_count()
+            with torch.cuda.graph(graph):
+                launch()
+            bound["graph"], bound["launches_per_replay"] = graph, native.launch_count() - before
+            return graph.replay
     elif args.moe_exchange == "peer":
         from intent_b200.peer import PeerExpertParallelMoE
 
@@ -834,7 +851,7 @@ def run_moe(args, rank: int, world: int, device):
     launch = prepare(lgd, xd)
     elapsed_ms, clocks, launches = timed_steps(launch, args.steps, args.warmup, world, device,
                                                rank, args.load_seconds)
-    if world > 1 and args.moe_exchange == "peer" and "launches_per_replay" in bound:
+    if "launches_per_replay" in bound:
         launches = bound["launches_per_replay"] * args.steps      # kernels inside the replayed graph
     phases = None
     if "phases" in bound:
@@ -867,6 +884,9 @@ def run_moe(args, rank: int, world: int, device):
     achieved = flops / world / (ms * 1e-3) / 1e12
     config = workload_config("moe", world)
     notes = {"expert_block_rows": args.moe_block}
+    if world == 1:
+        notes["launch"] = ("eager launches of the bound step" if args.moe_eager else
+                           "the bound step (router, alignment, gather, two grouped contractions) replayed as one CUDA graph")
     if world > 1:
         notes["exchange"] = ("rows written into the owners' buffers and results read back over NVLink peer memory; "
                               "three sync points per step as flag posts and bounded flag waits over peer memory, no "
@@ -878,10 +898,11 @@ def run_moe(args, rank: int, world: int, device):
         routes = tokens * cfg["top_k"]
         up_flops = routes * 2.0 * hidden * 2 * inter / world
         down_flops = routes * 2.0 * inter * hidden / world
+        down_us = phases.get("down", phases.get("down_combine"))
         split = {"phase_us": phases,
                  "router_align_us": round(sum(v for k, v in phases.items() if k in ("router", "align", "route")), 2),
                  "up_gate_TFLOPs": round(up_flops / (phases["up_gate"] * 1e-6) / 1e12, 1),
-                 "down_TFLOPs": round(down_flops / (phases["down"] * 1e-6) / 1e12, 1),
+                 "down_TFLOPs": round(down_flops / (down_us * 1e-6) / 1e12, 1),
                  "note": "per-phase device times from event marks inside 5 extra steps (max over ranks); the "
                          "sync phases include waiting for the slowest rank"}
         if world > 1 and "dispatch" in phases:
@@ -1303,6 +1324,8 @@ def main() -> int:
                         help="rows every expert span is padded to (= row tile of the grouped contraction)")
     parser.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores/loads, or NCCL all-to-all")
+    parser.add_argument("--moe-eager", action="store_true",
+                        help="1 GPU: launch the bound MoE step eagerly instead of replaying it as one CUDA graph")
     parser.add_argument("--moe-graph", action="store_true",
                         help="replay the expert-parallel step (peer exchange) as one CUDA graph")
     parser.add_argument("--no-decode", action="store_true", help="same as --attach none")

@@ -239,6 +239,21 @@ INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_bf16(INTENT_B200_G
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_f16(INTENT_B200_GROUPED_SLOTS);
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_bf16(INTENT_B200_GROUPED_SLOTS);
 INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_f16(INTENT_B200_GROUPED_SLOTS);
+/* Down projection with the weighted combine of examples/kernels/ragged/moe.py:43-53 in its epilogue:
+ *   a0 hidden rows [P,K] T, a1 expert_blocks [B], a2 total_padded [1], a3 packed [E,K/8,WN], a4 scales [E,K/G,WN],
+ *   a5 sorted_route_ids [>= P] i32 (route of every expert-sorted row; values outside [0, T*K) mark padding rows),
+ *   a6 route_weights [T,K] f32, a7 y [T,WN] f32 (InOut):
+ *   y[route / K, :] += route_weights[route] * (rows[r, :] . W[e]) with relaxed vector atomics, in no fixed order -
+ *   the reference's own GPU lowering of scatter_reduce(add) (lib/Target/Triton/Transforms/Access/Scatter.cpp:43-60).
+ *   With K <= 2 on a zeroed y the result is still bit-reproducible: (0 + a) + b == (0 + b) + a. */
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_scatter_bf16(
+    INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3), INTENT_B200_VIEW3(a4),
+    INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7), int32_t group_size, int32_t zero_point,
+    int32_t block_rows, void* stream);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_scatter_f16(
+    INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3), INTENT_B200_VIEW3(a4),
+    INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7), int32_t group_size, int32_t zero_point,
+    int32_t block_rows, void* stream);
 /* Weighted combine (the scatter_reduce add of moe.py:48-53, made order-fixed):
  * y[t,:] += sum over choices c in order of weights[t,c] * rows[route_positions[t*K + c], :]
  *   a0 rows [P,H] f32, a1 route_positions [T*K] i32, a2 weights [T,K] f32, a3 y [T,H] f32 (InOut);

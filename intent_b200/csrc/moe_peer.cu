@@ -98,7 +98,10 @@ __global__ void moe_peer_combine_kernel(const long long* __restrict__ peer_out, 
         if (owner < 0 || owner >= world || position < 0 || position >= capacity_rows) continue;
         const float w = weights[t * top_k + c];
         const float4 v = reinterpret_cast<const float4*>(peer_out[owner])[size_t(position) * row_vectors + i];
-        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        // product and sum are rounded separately (no fused multiply-add), so that this ordered combine and the
+        // atomic one in the down projection's epilogue give the same bits for two choices on a zeroed row
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
       }
       y[size_t(t) * row_vectors + i] = acc;
     }

@@ -176,7 +176,10 @@ __global__ void moe_combine_kernel(const float4* __restrict__ rows, const int* _
       for (int c = 0; c < top_k; ++c) {
         const float w = weights[t * top_k + c];
         const float4 v = rows[size_t(position[t * top_k + c]) * row_vectors + i];
-        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        // product and sum are rounded separately (no fused multiply-add), so that this ordered combine and the
+        // atomic one in the down projection's epilogue give the same bits for two choices on a zeroed row
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
       }
       y[size_t(t) * row_vectors + i] = acc;
     }

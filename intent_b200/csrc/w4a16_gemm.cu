@@ -38,6 +38,11 @@
 //   MODE 1  up|gate projection: the N tile is 128 gate columns + the matching 128 up columns,
 //           the epilogue writes T( silu(gate) * up ).
 //   MODE 2  down projection with f32 output rows (combined per token by a later kernel).
+//   MODE 3  down projection whose epilogue does the weighted combine itself: row r of the expert-sorted
+//           buffer belongs to route sorted_routes[r]; y[route / TOP_K, :] += weight[route] * row with
+//           red.global.add.v4.f32 (the reference's GPU lowering of scatter_reduce(add) is the same relaxed
+//           atomic, lib/Target/Triton/Transforms/Access/Scatter.cpp:43-60).  On a zeroed y with TOP_K <= 2
+//           the result does not depend on the order of the two additions: (0 + a) + b == (0 + b) + a.
 #include <type_traits>
 
 #include "common.cuh"
@@ -93,9 +98,17 @@ struct GemmParams {
                              // neighbouring blocks of one expert itself (an odd last block runs as half a tile)
   int experts;               // grouped modes: E; a block whose expert id is outside [0, E) is computed with zero
                              // weights and recorded as INTENT_B200_ERR_INDEX
+  const int* row_route;      // MODE 3: route id of every expert-sorted row (>= routes: a padding row)
+  const float* route_weight; // MODE 3: [routes]
+  int routes, top_k;         // MODE 3
 };
 
-constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2;
+constexpr int MODE_DENSE = 0, MODE_UPGATE_SILU = 1, MODE_GROUPED_F32 = 2, MODE_DOWN_SCATTER = 3;
+
+__device__ __forceinline__ void red_add_v4(float* address, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(address), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
 
 // Tile walk: bands of BAND_TILES row tiles; inside a band the row tile varies fastest.
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& m_tile, int& n_tile) {
@@ -317,13 +330,33 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
             }
           }
         } else {
+          // MODE 3: where this lane's row goes and with what weight (padding rows go nowhere)
+          float route_w = 0.f;
+          float* token_row = nullptr;
+          if (MODE == MODE_DOWN_SCATTER && row < p.M) {
+            const int route = p.row_route[row];
+            if (route >= 0 && route < p.routes) {
+              route_w = p.route_weight[route];
+              token_row = reinterpret_cast<float*>(p.y) + size_t(route / p.top_k) * p.out_cols;
+            }
+          }
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t v[32];
             tmem_load_32x32(taddr + c * 32, v);
             tmem_load_wait();
             const int col = n_tile * BN + c * 32;
-            if (row < p.M) {
+            if (MODE == MODE_DOWN_SCATTER) {
+              if (token_row != nullptr) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  if (col + q * 4 < p.out_cols)
+                    red_add_v4(token_row + col + q * 4, __fmul_rn(route_w, __uint_as_float(v[4 * q])),
+                               __fmul_rn(route_w, __uint_as_float(v[4 * q + 1])),
+                               __fmul_rn(route_w, __uint_as_float(v[4 * q + 2])),
+                               __fmul_rn(route_w, __uint_as_float(v[4 * q + 3])));
+              }
+            } else if (row < p.M) {
               if (MODE == MODE_GROUPED_F32) {
                 float* dst = reinterpret_cast<float*>(p.y) + size_t(row) * p.out_cols + col;
 #pragma unroll
@@ -488,7 +521,8 @@ int device_sms() {
 template <typename T, int MODE, int MT>
 int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t WN, void* out,
                 int64_t out_cols, int group_size, int zero_point, const int* total_rows, const int* tile_expert,
-                cudaStream_t stream, bool pair_blocks = false, int64_t experts = 1) {
+                cudaStream_t stream, bool pair_blocks = false, int64_t experts = 1, const int* row_route = nullptr,
+                const float* route_weight = nullptr, int64_t routes = 0, int top_k = 1) {
   const int sms = device_sms();
   if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
   const CUtensorMapDataType type =
@@ -511,6 +545,10 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
   p.tile_expert = tile_expert;
   p.pair_blocks = pair_blocks ? 1 : 0;
   p.experts = int(experts);
+  p.row_route = row_route;
+  p.route_weight = route_weight;
+  p.routes = int(routes);
+  p.top_k = top_k;
 
   CUtensorMap map_x;
   if (!make_tensor_map_2d(&map_x, type, x, uint64_t(rows), uint64_t(K), uint64_t(K) * 2, BM, BK,
@@ -586,6 +624,40 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
                                  false, E);
 }
 
+// Down projection with the weighted combine in the epilogue (MODE 3).
+//   x [P, K]; tile_expert; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; sorted_routes [>= P]; weights [T, TOP_K]; y [T, WN]
+template <typename T>
+int run_down_scatter(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View1 sorted_routes, View2 weights,
+                     View2 y, int group_size, int zero_point, int block_rows, cudaStream_t stream) {
+  const int64_t P = x.d0, K = x.d1, E = w.d0, WN = w.d2, tokens = weights.d0, top_k = weights.d1;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
+  if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
+  if (K % group_size != 0 || w.d1 * 8 != K || s.d0 != E || s.d1 * group_size != K || s.d2 != WN || y.d0 != tokens ||
+      y.d1 != WN || total.d0 < 1 || (block_rows != BM && block_rows != 2 * BM) || tile_expert.d0 * block_rows < P ||
+      sorted_routes.d0 < P || top_k <= 0)
+    return INTENT_B200_ERR_SHAPE;
+  if (P == 0 || WN == 0 || E == 0 || tokens == 0) return INTENT_B200_OK;
+  if (!x.p || !w.p || !s.p || !y.p || !tile_expert.p || !total.p || !sorted_routes.p || !weights.p)
+    return INTENT_B200_ERR_NULL;
+  if (!contiguous(x) || !contiguous(w) || !contiguous(s) || !contiguous(y) || !contiguous(tile_expert) ||
+      !contiguous(sorted_routes) || !contiguous(weights))
+    return INTENT_B200_ERR_LAYOUT;
+  if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
+  if (K == 0 || WN % 8 != 0 || P > (1 << 24) || K > (1 << 24) || WN > (1 << 24) || tokens * top_k > (1 << 30))
+    return INTENT_B200_ERR_UNSUPPORTED;
+  const int* routes = static_cast<const int*>(sorted_routes.p);
+  const float* route_weight = static_cast<const float*>(weights.p);
+  if (block_rows == 2 * BM || (P + BM - 1) / BM <= PAIR_LIST_BLOCKS)
+    return launch_gemm<T, MODE_DOWN_SCATTER, 2>(x.p, P, K, w.p, s.p, WN, y.p, WN, group_size, zero_point,
+                                                static_cast<const int*>(total.p),
+                                                static_cast<const int*>(tile_expert.p), stream, block_rows == BM, E,
+                                                routes, route_weight, tokens * top_k, int(top_k));
+  return launch_gemm<T, MODE_DOWN_SCATTER, 1>(x.p, P, K, w.p, s.p, WN, y.p, WN, group_size, zero_point,
+                                              static_cast<const int*>(total.p),
+                                              static_cast<const int*>(tile_expert.p), stream, false, E, routes,
+                                              route_weight, tokens * top_k, int(top_k));
+}
+
 }  // namespace
 }  // namespace ib200
 
@@ -625,3 +697,15 @@ IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_bf16, __nv_bfloat1
 IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_f16, __half, MODE_UPGATE_SILU)
 IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_bf16, __nv_bfloat16, MODE_GROUPED_F32)
 IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_f16, __half, MODE_GROUPED_F32)
+
+#define IB200_DOWN_SCATTER_ENTRY(NAME, TYPE)                                                                        \
+  extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW3(a3),     \
+                      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7),     \
+                      int32_t group_size, int32_t zero_point, int32_t block_rows, void* stream) {                    \
+    return ib200::run_down_scatter<TYPE>(IB200_VIEW2_ARG(a0), IB200_VIEW1_ARG(a1), IB200_VIEW1_ARG(a2),              \
+                                         IB200_VIEW3_ARG(a3), IB200_VIEW3_ARG(a4), IB200_VIEW1_ARG(a5),              \
+                                         IB200_VIEW2_ARG(a6), IB200_VIEW2_ARG(a7), group_size, zero_point,           \
+                                         block_rows, static_cast<cudaStream_t>(stream));                             \
+  }
+IB200_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_bf16, __nv_bfloat16)
+IB200_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_f16, __half)

@@ -141,6 +141,11 @@ class MoEW4A16FFN:
         self.down = _compile(programs.moe_grouped_down, target=target, constexprs=grouped)
         self.combine = _compile(programs.moe_combine, target=target)
         self.combine_overwrite = _compile(programs.moe_combine, target=target, constexprs={"ACCUMULATE": False})
+        # With at most two choices per token the weighted combine runs in the down projection's epilogue
+        # (relaxed vector atomics on y): on a zeroed y two additions commute exactly, so the result has the same
+        # bits as the ordered combine.  More choices keep the ordered combine kernel.
+        self.fused_combine = top_k <= 2
+        self.down_scatter = _compile(programs.moe_grouped_down_scatter, target=target, constexprs=grouped)
 
     def route(self, logits):
         """logits [T, E_total] f32 -> (ids [T,2] i32, weights [T,2] f32)."""
@@ -168,10 +173,16 @@ class MoEW4A16FFN:
         """y[t] (+)= sum_c topk_weights[t, c] * FFN_{topk_ids[t, c]}(x[t]); y f32 [T, H]."""
         import torch
 
-        rows, positions = self.experts_forward(x, topk_ids, up_gate_packed, up_gate_scales, down_packed,
-                                               down_scales)
         if y is None:
             y = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+        if self.fused_combine:
+            sorted_routes, expert_blocks, total = self.alignment.run(topk_ids)
+            rows = self.gather.run(x, sorted_routes, total)
+            hidden = self.up_gate.run(rows, expert_blocks, total, up_gate_packed, up_gate_scales)
+            self.down_scatter(hidden, expert_blocks, total, down_packed, down_scales, sorted_routes, topk_weights, y)
+            return y
+        rows, positions = self.experts_forward(x, topk_ids, up_gate_packed, up_gate_scales, down_packed,
+                                               down_scales)
         self.combine.run(rows, positions, topk_weights, y)
         return y
 
@@ -186,6 +197,12 @@ class MoEW4A16FFN:
 
         align = self.alignment.prepare(topk_ids)
         sorted_routes, expert_blocks, total = align.result()
+        if self.fused_combine and not clear_positions:
+            gather_call = self.gather.prepare(x, sorted_routes, total)
+            up_call = self.up_gate.prepare(gather_call.result(), expert_blocks, total, up_gate_packed, up_gate_scales)
+            scatter_call = self.down_scatter.prepare(up_call.result(), expert_blocks, total, down_packed, down_scales,
+                                                     sorted_routes, topk_weights, y)
+            return PreparedFusedFFN(align, gather_call, up_call, scatter_call, y)
         positions = torch.zeros((topk_ids.shape[0] * self.top_k,), dtype=torch.int32, device=x.device)
         full_positions = torch.zeros((self.tokens * self.top_k,), dtype=torch.int32, device=x.device)
         position_call = self.positions.prepare(sorted_routes, total, outputs=(full_positions,))
@@ -197,6 +214,42 @@ class MoEW4A16FFN:
         overwrite_call = self.combine_overwrite.prepare(down_call.result(), positions, topk_weights, y)
         return PreparedFFN(align, position_call, gather_call, up_call, down_call, combine_call, overwrite_call,
                            full_positions, y, clear_positions)
+
+
+@dataclass
+class PreparedFusedFFN:
+    """The chain with the weighted combine inside the down projection's epilogue (top_k <= 2)."""
+
+    align: object
+    gather_call: object
+    up_call: object
+    scatter_call: object
+    y: object
+
+    PHASES = ("align", "gather", "up_gate", "down_combine")
+
+    def launch(self, accumulate: bool = False, marks=None):
+        """Overwrites ``y`` (it is cleared first) unless ``accumulate``; ``marks`` as in :class:`PreparedFFN`."""
+        def mark():
+            if marks is not None:
+                import torch
+
+                event = torch.cuda.Event(enable_timing=True)
+                event.record()
+                marks.append(event)
+
+        mark()
+        self.align.launch()
+        mark()
+        self.gather_call.launch()
+        mark()
+        self.up_call.launch()
+        if not accumulate:
+            self.y.zero_()
+        mark()
+        self.scatter_call.launch()
+        mark()
+        return self.y
 
 
 @dataclass

@@ -312,6 +312,37 @@ moe_grouped_down = KernelDefinition(
     "out = hidden @ Wdown[e] per expert block, f32 rows")
 
 
+def _lower_down_scatter(c, device):
+    act = _act_dtype(c)
+    group, zp = _grouped_constants(c)
+    block = int(c["BLOCK_ROWS"])
+    if block not in (128, 256):
+        raise CompilationStageError("provider_native_compilation", "BLOCK_ROWS must be 128 or 256")
+    interface = PublicInterface((
+        ViewParameter(0, "rows", act, ("P", "K"), IN),
+        ViewParameter(1, "expert_blocks", dtypes.i32, ("B",), IN, alignment=4),
+        ViewParameter(2, "total_padded", dtypes.i32, (1,), IN, alignment=4),
+        ViewParameter(3, "packed_weight", dtypes.i32, ("E", "KP", "WN"), IN),
+        ViewParameter(4, "scales", act, ("E", "KG", "WN"), IN),
+        ViewParameter(5, "sorted_route_ids", dtypes.i32, ("S",), IN, alignment=4),
+        ViewParameter(6, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
+        ViewParameter(7, "y", dtypes.f32, ("T", "WN"), INOUT),
+    ), dimension_rules=(
+        _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
+              "packed_weight / scales do not match K and GROUP_SIZE"),
+        _rule(lambda d: d["B"] * block >= d["P"], f"expert_blocks must cover every {block}-row block of rows"),
+        _rule(lambda d: d["S"] >= d["P"], "sorted_route_ids must cover every row"),
+    ))
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_down_scatter_{act.name}",
+                         constants=(group, zp, block), device=device)
+
+
+moe_grouped_down_scatter = KernelDefinition(
+    "moe_grouped_down_scatter", dict(_GROUPED_CONSTEXPRS), _lower_down_scatter,
+    "examples/kernels/ragged/moe.py:43-53 (down projection + weighted scatter_reduce add)",
+    "y[route // TOP_K] += weight[route] * (hidden[r] @ Wdown[e]) per expert-sorted row r, relaxed atomics")
+
+
 def _lower_combine(c, device):
     interface = PublicInterface((
         ViewParameter(0, "rows", dtypes.f32, ("P", "H"), IN),
@@ -329,7 +360,7 @@ moe_combine = KernelDefinition("moe_combine", {"ACCUMULATE": True}, _lower_combi
 
 ALL.update({d.name: d for d in (moe_count_routes, moe_prefix_routes, moe_scatter_routes, moe_mark_expert_blocks,
                                 moe_route_positions, moe_route_top2, moe_gather_rows, moe_grouped_upgate_silu,
-                                moe_grouped_down, moe_combine)})
+                                moe_grouped_down, moe_grouped_down_scatter, moe_combine)})
 
 
 # ---------------------------------------------------------------------------------
