@@ -175,6 +175,46 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
 INTENT_B200_API int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value);
 
 /* ------------------------------------------------------------------------
+ * Tiled copy of a packed int4 weight for the tensor-core kernels.  The caller-visible format stays the
+ * reference's [K/8, N] int32 (examples/kernels/contraction/weight_only_int4.py:31-39); a weight that is static
+ * model state can be re-laid ONCE so that the four packed words a dequantiser thread needs per 64-wide k block
+ * are adjacent (one 16-byte load instead of four loads N*4 bytes apart):
+ *   tiled[n / 128][k / 64][(k % 64) / 32][n % 128][4 words], rows past K/8 and columns past N stored as zeros.
+ * The reference pays one-off costs once and persists the result in the same spirit (generated programs and
+ * native builds: python/intent/compiler/artifact.py:105-157, python/intent/runtime/native_artifact.py:151-190).
+ *   ..._words(K, N): 32-bit words of the tiled copy (0 for an invalid shape).
+ *   prelayout:         a0 packed [K/8, N] i32 -> a1 tiled [words] i32
+ *   prelayout_grouped: a0 packed [E, K/8, N] i32 -> a1 tiled [E, words] i32 (each expert on its own)
+ * The *_tiled entries are the tensor-core entries of the same name with the tiled copy in place of the
+ * packed matrix (K is taken from the activation, N from the scales).
+ * ------------------------------------------------------------------------ */
+INTENT_B200_API int64_t intent_b200_w4a16_prelayout_words(int64_t K, int64_t N);
+INTENT_B200_API int intent_b200_w4a16_prelayout(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), void* stream);
+INTENT_B200_API int intent_b200_w4a16_prelayout_grouped(INTENT_B200_VIEW3(a0), INTENT_B200_VIEW2(a1), void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemm_tiled_f16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                     INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                                     int32_t group_size, int32_t zero_point, void* stream);
+INTENT_B200_API int intent_b200_w4a16_gemm_tiled_bf16(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1),
+                                                      INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),
+                                                      int32_t group_size, int32_t zero_point, void* stream);
+#define INTENT_B200_GROUPED_TILED_SLOTS                                                                    \
+  INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3),              \
+      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point,               \
+      int32_t block_rows, void *stream
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_tiled_bf16(INTENT_B200_GROUPED_TILED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_upgate_silu_tiled_f16(INTENT_B200_GROUPED_TILED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_tiled_bf16(INTENT_B200_GROUPED_TILED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_f32_tiled_f16(INTENT_B200_GROUPED_TILED_SLOTS);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_scatter_tiled_bf16(
+    INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3), INTENT_B200_VIEW3(a4),
+    INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7), int32_t group_size, int32_t zero_point,
+    int32_t block_rows, void* stream);
+INTENT_B200_API int intent_b200_moe_grouped_w4a16_down_scatter_tiled_f16(
+    INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3), INTENT_B200_VIEW3(a4),
+    INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7), int32_t group_size, int32_t zero_point,
+    int32_t block_rows, void* stream);
+
+/* ------------------------------------------------------------------------
  * gemm_i8: C[m,n] = i32(sum_k A[m,k] * B[k,n]) + bias[n], wrapping int32.
  * Replaces the provider lowering of examples/kernels/contraction/gemm.py:29-39.
  *   a0 A [M,K] i8 (K contiguous)   a1 B [K,N] i8 (N contiguous)

@@ -105,4 +105,7 @@ def load(directory, *, target: B200Target | None = None, resolve_target: bool = 
                                     cache_directory=path) from error
     artifact = compile(definition, target=target, constexprs=constants, resolve_target=resolve_target)
     artifact.cache_directory = path
+    cache = getattr(artifact.runtime, "cache", None)
+    if cache is not None:       # tiled weight copies saved with the artifact are matched to weights by content key
+        cache.restore(path / "prelayout")
     return artifact

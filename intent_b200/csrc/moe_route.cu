@@ -97,40 +97,45 @@ __global__ void moe_prefix_kernel(const int* __restrict__ counts, int experts, i
 }
 
 // ---- scatter: CTA e compacts, in ascending route order, the routes that chose expert e ----
+// Warp w of the CTA owns the contiguous slice w of the routes.  Pass 1: every warp counts its matches;
+// one barrier; pass 2: every warp walks its slice again and writes each match at (span start + matches in
+// earlier slices + matches earlier in its own slice).  Slices are contiguous and in order, so the partition
+// is stable; the two passes read the ids from L2 and need no barrier per step.
 __global__ void __launch_bounds__(1024)
 moe_scatter_kernel(const int* __restrict__ ids, int routes, const int* __restrict__ offsets,
                    int* __restrict__ cursors, int* __restrict__ sorted, int sorted_capacity) {
   __shared__ int warp_count[32];
-  __shared__ int running;
   const int e = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int begin = offsets[e], end = offsets[e + 1];
-  if (threadIdx.x == 0) running = 0;
+  const int slice = ((routes + 31) / 32 + 31) / 32 * 32;          // per warp, a multiple of the warp size
+  const int first = min(routes, warp * slice), last = min(routes, first + slice);
+  int count = 0;
+  for (int base = first; base < last; base += 32) {
+    const int r = base + lane;
+    count += __popc(__ballot_sync(0xffffffffu, r < last && ids[r] == e));
+  }
+  if (lane == 0) warp_count[warp] = count;
   __syncthreads();
-  for (int base = 0; base < routes; base += 1024) {
-    const int r = base + threadIdx.x;
-    const bool mine = r < routes && ids[r] == e;
+  int before = 0, total = 0;
+  for (int w = 0; w < 32; ++w) {
+    if (w < warp) before += warp_count[w];
+    total += warp_count[w];
+  }
+  int position = begin + before;
+  for (int base = first; base < last; base += 32) {
+    const int r = base + lane;
+    const bool mine = r < last && ids[r] == e;
     const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-    if (lane == 0) warp_count[warp] = __popc(ballot);
-    __syncthreads();
-    int before = running;
-    for (int w = 0; w < warp; ++w) before += warp_count[w];
     if (mine) {
-      const int position = begin + before + __popc(ballot & ((1u << lane) - 1u));
-      if (position < end && position < sorted_capacity) sorted[position] = r;
+      const int at = position + __popc(ballot & ((1u << lane) - 1u));
+      if (at < end && at < sorted_capacity) sorted[at] = r;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int add = 0;
-      for (int w = 0; w < 32; ++w) add += warp_count[w];
-      running += add;
-    }
-    __syncthreads();
+    position += __popc(ballot);
   }
   // the padding of the span holds the sentinel `routes`
-  for (int position = begin + running + threadIdx.x; position < end && position < sorted_capacity; position += 1024)
-    sorted[position] = routes;
-  if (threadIdx.x == 0 && cursors) cursors[e] += running;  // final value of the reference's atomic cursor
+  for (int at = begin + total + threadIdx.x; at < end && at < sorted_capacity; at += 1024) sorted[at] = routes;
+  if (threadIdx.x == 0 && cursors) cursors[e] += total;  // final value of the reference's atomic cursor
 }
 
 // ---- mark: expert owning every block of the padded layout ----

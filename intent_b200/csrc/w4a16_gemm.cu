@@ -55,8 +55,9 @@ __device__ int g_w4a16_gemm_status = 0;
 
 template <typename T>
 int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
-                    int group_size, int zero_point, cudaStream_t stream);
+                    int group_size, int zero_point, cudaStream_t stream, bool prelaid);
 int w4a16_gemm_pair_take_status(int* value);
+int64_t w4a16_prelayout_words(int64_t K, int64_t N);
 
 namespace {
 
@@ -98,6 +99,7 @@ struct GemmParams {
                              // neighbouring blocks of one expert itself (an odd last block runs as half a tile)
   int experts;               // grouped modes: E; a block whose expert id is outside [0, E) is computed with zero
                              // weights and recorded as INTENT_B200_ERR_INDEX
+  int prelaid;               // packed points at the tiled copy (w4a16_prelayout.cu); per expert in the grouped modes
   const int* row_route;      // MODE 3: route id of every expert-sorted row (>= routes: a padding row)
   const float* route_weight; // MODE 3: [routes]
   int routes, top_k;         // MODE 3
@@ -432,9 +434,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
         }
         f_w = p.packed + size_t(expert) * packed_rows * p.WN + (f_col_ok ? col : 0);
         f_s = p.scales + size_t(expert) * scale_rows * p.WN + (f_col_ok ? col : 0);
+        if (p.prelaid) {   // per expert: [column block of 128][k block][part][column][4 words]
+          const size_t column_blocks = size_t(p.WN + 127) >> 7;
+          const size_t expert_words = column_blocks * p.k_blocks * DQ_PARTS * 128 * 4;
+          f_w = p.packed + size_t(expert) * expert_words +
+                ((size_t(col >> 7) * p.k_blocks * DQ_PARTS + part) * 128 + (col & 127)) * 4;
+          if (!f_col_ok) f_w = p.packed;   // a column past WN: any valid address, the words are not used
+        }
       }
       const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
-      if (f_col_ok && rows_left >= DQ_ROWS) {
+      if (p.prelaid) {
+        // tiled copy: this thread's four words of the k block are one 16-byte load (rows past K are zeros)
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(f_w));
+        const bool use = f_col_ok;
+        b.w[0] = use ? v.x : 0u; b.w[1] = use ? v.y : 0u; b.w[2] = use ? v.z : 0u; b.w[3] = use ? v.w : 0u;
+      } else if (f_col_ok && rows_left >= DQ_ROWS) {
         const uint32_t* q = f_w + size_t(part * DQ_ROWS) * p.WN;
 #pragma unroll
         for (int r = 0; r < DQ_ROWS; ++r, q += p.WN) b.w[r] = __ldg(q);
@@ -449,7 +463,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       const uint32_t c = g1 == g0 ? a : ((f_col_ok && g1 < scale_rows) ? __ldg(f_s + size_t(g1) * p.WN) : 0u);
       b.s_lo = a | (a << 16);
       b.s_hi = c | (c << 16);
-      f_w += size_t(BK / 8) * p.WN;
+      f_w += p.prelaid ? (f_col_ok ? size_t(DQ_PARTS) * 128 * 4 : 0) : size_t(BK / 8) * p.WN;
       if (++f_kb == p.k_blocks) {
         f_kb = 0;
         f_tile += int(gridDim.x);
@@ -522,7 +536,7 @@ template <typename T, int MODE, int MT>
 int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const void* s, int64_t WN, void* out,
                 int64_t out_cols, int group_size, int zero_point, const int* total_rows, const int* tile_expert,
                 cudaStream_t stream, bool pair_blocks = false, int64_t experts = 1, const int* row_route = nullptr,
-                const float* route_weight = nullptr, int64_t routes = 0, int top_k = 1) {
+                const float* route_weight = nullptr, int64_t routes = 0, int top_k = 1, bool prelaid = false) {
   const int sms = device_sms();
   if (sms <= 0) return INTENT_B200_ERR_UNSUPPORTED;
   const CUtensorMapDataType type =
@@ -545,6 +559,7 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
   p.tile_expert = tile_expert;
   p.pair_blocks = pair_blocks ? 1 : 0;
   p.experts = int(experts);
+  p.prelaid = prelaid ? 1 : 0;
   p.row_route = row_route;
   p.route_weight = route_weight;
   p.routes = int(routes);
@@ -571,7 +586,8 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
 }
 
 template <typename T>
-int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cudaStream_t stream) {
+int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cudaStream_t stream,
+        bool prelaid = false) {
   const int64_t M = x.d0, K = x.d1, N = w.d1;
   if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
   if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
@@ -583,14 +599,14 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
   if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
   if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
   {  // large M: CTA pairs, each CTA dequantises half of every weight tile
-    const int status = w4a16_gemm_pair<T>(x.p, M, K, w.p, s.p, N, y.p, group_size, zero_point, stream);
+    const int status = w4a16_gemm_pair<T>(x.p, M, K, w.p, s.p, N, y.p, group_size, zero_point, stream, prelaid);
     if (status != INTENT_B200_ERR_UNSUPPORTED) return status;
   }
   if (M > BM)   // two row blocks per tile share every dequantised weight tile
     return launch_gemm<T, MODE_DENSE, 2>(x.p, M, K, w.p, s.p, N, y.p, N, group_size, zero_point, nullptr, nullptr,
-                                         stream);
+                                         stream, false, 1, nullptr, nullptr, 0, 1, prelaid);
   return launch_gemm<T, MODE_DENSE, 1>(x.p, M, K, w.p, s.p, N, y.p, N, group_size, zero_point, nullptr, nullptr,
-                                       stream);
+                                       stream, false, 1, nullptr, nullptr, 0, 1, prelaid);
 }
 
 // Grouped contractions over expert-sorted rows padded to `block_rows` (128 or 256) per expert; with 256
@@ -598,7 +614,7 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
 //   x [P, K]; tile_expert [>= P/block_rows]; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; out [P, out_cols]
 template <typename T, int MODE>
 int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2 out, int group_size, int zero_point,
-                int block_rows, cudaStream_t stream) {
+                int block_rows, cudaStream_t stream, bool prelaid = false) {
   const int64_t P = x.d0, K = x.d1, E = w.d0, WN = w.d2;
   const int64_t out_cols = MODE == MODE_UPGATE_SILU ? WN / 2 : WN;
   if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
@@ -618,17 +634,18 @@ int run_grouped(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View2
   if (block_rows == 2 * BM || (P + BM - 1) / BM <= PAIR_LIST_BLOCKS)   // 128-row blocks are paired by the kernel
     return launch_gemm<T, MODE, 2>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
                                    static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream,
-                                   block_rows == BM, E);
+                                   block_rows == BM, E, nullptr, nullptr, 0, 1, prelaid);
   return launch_gemm<T, MODE, 1>(x.p, P, K, w.p, s.p, WN, out.p, out_cols, group_size, zero_point,
                                  static_cast<const int*>(total.p), static_cast<const int*>(tile_expert.p), stream,
-                                 false, E);
+                                 false, E, nullptr, nullptr, 0, 1, prelaid);
 }
 
 // Down projection with the weighted combine in the epilogue (MODE 3).
 //   x [P, K]; tile_expert; total [1]; w [E, K/8, WN]; s [E, K/G, WN]; sorted_routes [>= P]; weights [T, TOP_K]; y [T, WN]
 template <typename T>
 int run_down_scatter(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, View1 sorted_routes, View2 weights,
-                     View2 y, int group_size, int zero_point, int block_rows, cudaStream_t stream) {
+                     View2 y, int group_size, int zero_point, int block_rows, cudaStream_t stream,
+                     bool prelaid = false) {
   const int64_t P = x.d0, K = x.d1, E = w.d0, WN = w.d2, tokens = weights.d0, top_k = weights.d1;
   if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
   if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
@@ -651,11 +668,23 @@ int run_down_scatter(View2 x, View1 tile_expert, View1 total, View3 w, View3 s, 
     return launch_gemm<T, MODE_DOWN_SCATTER, 2>(x.p, P, K, w.p, s.p, WN, y.p, WN, group_size, zero_point,
                                                 static_cast<const int*>(total.p),
                                                 static_cast<const int*>(tile_expert.p), stream, block_rows == BM, E,
-                                                routes, route_weight, tokens * top_k, int(top_k));
+                                                routes, route_weight, tokens * top_k, int(top_k), prelaid);
   return launch_gemm<T, MODE_DOWN_SCATTER, 1>(x.p, P, K, w.p, s.p, WN, y.p, WN, group_size, zero_point,
                                               static_cast<const int*>(total.p),
                                               static_cast<const int*>(tile_expert.p), stream, false, E, routes,
-                                              route_weight, tokens * top_k, int(top_k));
+                                              route_weight, tokens * top_k, int(top_k), prelaid);
+}
+
+// The tiled copy stands in for the [K/8, N] matrix: K comes from the activation, N from the scales.
+inline bool tiled_as_matrix(View1 tiled, int64_t K, int64_t N, View2* w) {
+  if (K <= 0 || N <= 0 || K % 8 != 0 || tiled.d0 != w4a16_prelayout_words(K, N) || !contiguous(tiled)) return false;
+  *w = View2{tiled.p, K / 8, N, N, 1};
+  return true;
+}
+inline bool tiled_as_experts(View2 tiled, int64_t K, int64_t WN, View3* w) {
+  if (K <= 0 || WN <= 0 || K % 8 != 0 || tiled.d1 != w4a16_prelayout_words(K, WN) || !contiguous(tiled)) return false;
+  *w = View3{tiled.p, tiled.d0, K / 8, WN, (K / 8) * WN, WN, 1};
+  return true;
 }
 
 }  // namespace
@@ -709,3 +738,47 @@ IB200_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_f16, __half, MODE_GRO
   }
 IB200_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_bf16, __nv_bfloat16)
 IB200_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_f16, __half)
+
+// ---- the same entries on a tiled copy of the weight (w4a16_prelayout.cu) -------------------------------------
+#define IB200_TILED_GEMM_ENTRY(NAME, TYPE)                                                                        \
+  extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW2(a2), INTENT_B200_VIEW2(a3),   \
+                      int32_t group_size, int32_t zero_point, void* stream) {                                      \
+    ib200::View2 w;                                                                                                \
+    if (!ib200::tiled_as_matrix(IB200_VIEW1_ARG(a1), a0_d1, a2_d1, &w)) return INTENT_B200_ERR_SHAPE;              \
+    return ib200::run<TYPE>(IB200_VIEW2_ARG(a0), w, IB200_VIEW2_ARG(a2), IB200_VIEW2_ARG(a3), group_size,          \
+                            zero_point, static_cast<cudaStream_t>(stream), true);                                  \
+  }
+IB200_TILED_GEMM_ENTRY(intent_b200_w4a16_gemm_tiled_f16, __half)
+IB200_TILED_GEMM_ENTRY(intent_b200_w4a16_gemm_tiled_bf16, __nv_bfloat16)
+
+#define IB200_TILED_GROUPED_ENTRY(NAME, TYPE, MODE)                                                              \
+  extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3), \
+                      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW2(a5), int32_t group_size, int32_t zero_point,      \
+                      int32_t block_rows, void* stream) {                                                        \
+    ib200::View3 w;                                                                                              \
+    if (a4_d0 != a3_d0 || !ib200::tiled_as_experts(IB200_VIEW2_ARG(a3), a0_d1, a4_d2, &w))                       \
+      return INTENT_B200_ERR_SHAPE;                                                                              \
+    return ib200::run_grouped<TYPE, ib200::MODE>(IB200_VIEW2_ARG(a0), IB200_VIEW1_ARG(a1), IB200_VIEW1_ARG(a2),  \
+                                                 w, IB200_VIEW3_ARG(a4), IB200_VIEW2_ARG(a5), group_size,        \
+                                                 zero_point, block_rows, static_cast<cudaStream_t>(stream),      \
+                                                 true);                                                          \
+  }
+IB200_TILED_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_tiled_bf16, __nv_bfloat16, MODE_UPGATE_SILU)
+IB200_TILED_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_upgate_silu_tiled_f16, __half, MODE_UPGATE_SILU)
+IB200_TILED_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_tiled_bf16, __nv_bfloat16, MODE_GROUPED_F32)
+IB200_TILED_GROUPED_ENTRY(intent_b200_moe_grouped_w4a16_down_f32_tiled_f16, __half, MODE_GROUPED_F32)
+
+#define IB200_TILED_DOWN_SCATTER_ENTRY(NAME, TYPE)                                                                  \
+  extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW1(a1), INTENT_B200_VIEW1(a2), INTENT_B200_VIEW2(a3),     \
+                      INTENT_B200_VIEW3(a4), INTENT_B200_VIEW1(a5), INTENT_B200_VIEW2(a6), INTENT_B200_VIEW2(a7),     \
+                      int32_t group_size, int32_t zero_point, int32_t block_rows, void* stream) {                    \
+    ib200::View3 w;                                                                                                  \
+    if (a4_d0 != a3_d0 || !ib200::tiled_as_experts(IB200_VIEW2_ARG(a3), a0_d1, a4_d2, &w))                           \
+      return INTENT_B200_ERR_SHAPE;                                                                                  \
+    return ib200::run_down_scatter<TYPE>(IB200_VIEW2_ARG(a0), IB200_VIEW1_ARG(a1), IB200_VIEW1_ARG(a2), w,           \
+                                         IB200_VIEW3_ARG(a4), IB200_VIEW1_ARG(a5), IB200_VIEW2_ARG(a6),              \
+                                         IB200_VIEW2_ARG(a7), group_size, zero_point, block_rows,                    \
+                                         static_cast<cudaStream_t>(stream), true);                                   \
+  }
+IB200_TILED_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_tiled_bf16, __nv_bfloat16)
+IB200_TILED_DOWN_SCATTER_ENTRY(intent_b200_moe_grouped_w4a16_down_scatter_tiled_f16, __half)

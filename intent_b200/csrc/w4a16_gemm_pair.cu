@@ -53,6 +53,7 @@ struct PairParams {
   int M, K, N;
   int k_blocks, m_tiles, n_tiles;
   int group_size, twos_complement;
+  int prelaid;      // packed points at the tiled copy (w4a16_prelayout.cu) instead of the [K/8, N] matrix
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -307,9 +308,18 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
         f_col_ok = col < p.N;
         f_w = p.packed + (f_col_ok ? col : 0);
         f_s = p.scales + (f_col_ok ? col : 0);
+        if (p.prelaid)   // [column block of 128][k block][part][column][4 words]; a column past N reads word 0, unused
+          f_w = f_col_ok ? p.packed + ((size_t(col >> 7) * p.k_blocks * DQ_PARTS + part) * 128 + (col & 127)) * 4
+                         : p.packed;
       }
       const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
-      if (f_col_ok && rows_left >= DQ_ROWS) {
+      if (p.prelaid) {
+        // tiled copy: this thread's four words of the k block are one 16-byte load, a warp reads 512 contiguous
+        // bytes; rows past K are stored as zeros
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(f_w));
+        b.w[0] = f_col_ok ? v.x : 0u; b.w[1] = f_col_ok ? v.y : 0u;
+        b.w[2] = f_col_ok ? v.z : 0u; b.w[3] = f_col_ok ? v.w : 0u;
+      } else if (f_col_ok && rows_left >= DQ_ROWS) {
         const uint32_t* q = f_w + size_t(part * DQ_ROWS) * p.N;
 #pragma unroll
         for (int r = 0; r < DQ_ROWS; ++r, q += p.N) b.w[r] = __ldg(q);
@@ -324,7 +334,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       const uint32_t c = g1 == g0 ? a : ((f_col_ok && g1 < scale_rows) ? __ldg(f_s + size_t(g1) * p.N) : 0u);
       b.s_lo = a | (a << 16);
       b.s_hi = c | (c << 16);
-      f_w += size_t(BK / 8) * p.N;
+      f_w += p.prelaid ? (f_col_ok ? size_t(DQ_PARTS) * 128 * 4 : 0) : size_t(BK / 8) * p.N;
       if (++f_kb == p.k_blocks) {
         f_kb = 0;
         f_tile += pairs;
@@ -391,7 +401,7 @@ int g_pair_enabled = 1;
 // single-CTA kernel instead.  Arguments are already validated by the caller.
 template <typename T>
 int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
-                    int group_size, int zero_point, cudaStream_t stream) {
+                    int group_size, int zero_point, cudaStream_t stream, bool prelaid) {
   if (!g_pair_enabled || M < PAIR_ROWS) return INTENT_B200_ERR_UNSUPPORTED;
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
@@ -411,6 +421,7 @@ int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const vo
   p.n_tiles = int((N + BN - 1) / BN);
   p.group_size = group_size;
   p.twos_complement = zero_point == -1 ? 1 : 0;
+  p.prelaid = prelaid ? 1 : 0;
   CUtensorMap map_x;
   if (!make_tensor_map_2d(&map_x, type, x, uint64_t(M), uint64_t(K), uint64_t(K) * 2, BM, BK,
                           CU_TENSOR_MAP_SWIZZLE_128B))
@@ -443,9 +454,9 @@ int w4a16_gemm_pair_take_status(int* value) {
 }
 
 template int w4a16_gemm_pair<__half>(const void*, int64_t, int64_t, const void*, const void*, int64_t, void*, int, int,
-                                     cudaStream_t);
+                                     cudaStream_t, bool);
 template int w4a16_gemm_pair<__nv_bfloat16>(const void*, int64_t, int64_t, const void*, const void*, int64_t, void*,
-                                            int, int, cudaStream_t);
+                                            int, int, cudaStream_t, bool);
 
 }  // namespace ib200
 

@@ -123,7 +123,9 @@ class MoEW4A16FFN:
     number of received rows with ``top_k = 1``)."""
 
     def __init__(self, *, tokens, hidden, intermediate, experts, top_k=2, group_size=128, zero_point=8,
-                 act_dtype="bf16", block_size=128, target: B200Target | None = None):
+                 act_dtype="bf16", block_size=128, target: B200Target | None = None, prelayout: bool = False):
+        """``prelayout``: the expert weights are static model state; the grouped contractions then run on tiled
+        copies (intent_b200.prelayout) that are made the first time a weight tensor is seen."""
         self.tokens, self.hidden, self.intermediate = tokens, hidden, intermediate
         self.experts, self.top_k = experts, top_k
         self.alignment = MoEAlignment.build(tokens=tokens, top_k=top_k, experts=experts, block_size=block_size,
@@ -136,7 +138,12 @@ class MoEW4A16FFN:
         self.positions = _compile(programs.moe_route_positions, target=target, constexprs=align)
         self.gather = _compile(programs.moe_gather_rows, target=target,
                                constexprs={"ACT_DTYPE": act_dtype, "TOP_K": top_k})
-        grouped = dict(quant, BLOCK_ROWS=block_size)
+        grouped = dict(quant, BLOCK_ROWS=block_size, WEIGHT_LAYOUT="tiled" if prelayout else "reference")
+        self.prelayout = None
+        if prelayout:
+            from .prelayout import PrelayoutCache
+
+            self.prelayout = PrelayoutCache()
         self.up_gate = _compile(programs.moe_grouped_upgate_silu, target=target, constexprs=grouped)
         self.down = _compile(programs.moe_grouped_down, target=target, constexprs=grouped)
         self.combine = _compile(programs.moe_combine, target=target)
@@ -151,11 +158,18 @@ class MoEW4A16FFN:
         """logits [T, E_total] f32 -> (ids [T,2] i32, weights [T,2] f32)."""
         return self.router.run(logits)
 
+    def _weights(self, up_gate_packed, down_packed):
+        """The packed expert weights as the grouped programs take them (tiled copies with ``prelayout``)."""
+        if self.prelayout is None:
+            return up_gate_packed, down_packed
+        return self.prelayout.get(up_gate_packed).tensor, self.prelayout.get(down_packed).tensor
+
     def experts_forward(self, x, topk_ids, up_gate_packed, up_gate_scales, down_packed, down_scales,
                         clear_positions=False):
         """Rows of the down projection in the expert-sorted layout plus the inverse map:
         returns (rows f32 [P, H], route_positions i32 [T*top_k]).  ``clear_positions``: routes whose
         expert id matches no local expert (padding of a fixed-capacity exchange) get position 0."""
+        up_gate_packed, down_packed = self._weights(up_gate_packed, down_packed)
         sorted_routes, expert_blocks, total = self.alignment.run(topk_ids)
         if clear_positions:
             import torch
@@ -176,6 +190,7 @@ class MoEW4A16FFN:
         if y is None:
             y = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
         if self.fused_combine:
+            up_gate_packed, down_packed = self._weights(up_gate_packed, down_packed)
             sorted_routes, expert_blocks, total = self.alignment.run(topk_ids)
             rows = self.gather.run(x, sorted_routes, total)
             hidden = self.up_gate.run(rows, expert_blocks, total, up_gate_packed, up_gate_scales)
@@ -195,6 +210,7 @@ class MoEW4A16FFN:
         ``y`` unless ``launch(accumulate=True)``."""
         import torch
 
+        up_gate_packed, down_packed = self._weights(up_gate_packed, down_packed)
         align = self.alignment.prepare(topk_ids)
         sorted_routes, expert_blocks, total = align.result()
         if self.fused_combine and not clear_positions:

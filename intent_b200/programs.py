@@ -55,6 +55,31 @@ def _lower_w4a16(constants, device):
     stem = {"auto": "weight_only_int4_matmul", "gemv": "w4a16_gemv", "gemm": "w4a16_gemm"}.get(kernel)
     if stem is None:
         raise CompilationStageError("frontend_kir", "KERNEL must be 'auto', 'gemv' or 'gemm'")
+    layout = constants.get("WEIGHT_LAYOUT", "reference")
+    if layout not in ("reference", "tiled"):
+        raise CompilationStageError("frontend_kir", "WEIGHT_LAYOUT must be 'reference' or 'tiled'")
+    if layout == "tiled":
+        # packed_weight is the tiled copy made by intent_b200.prelayout.tile: tensor-core kernels only
+        if kernel == "gemv":
+            raise CompilationStageError("provider_native_compilation",
+                                        "the bandwidth kernel reads the reference layout; WEIGHT_LAYOUT='tiled' "
+                                        "needs KERNEL 'auto' or 'gemm'")
+        from . import prelayout
+
+        tiled_interface = PublicInterface((
+            ViewParameter(0, "activation", act, ("M", "K"), IN),
+            ViewParameter(1, "packed_weight", dtypes.i32, ("W",), IN),
+            ViewParameter(2, "scales", act, ("G", "N"), IN),
+            ViewParameter(3, "output", act, ("M", "N"), OUT),
+        ), dimension_rules=(
+            _rule(lambda d: d["K"] % group == 0 and d["G"] * group == d["K"],
+                  lambda d: f"scales.shape[0] must be K/GROUP_SIZE with K a multiple of {group}"),
+            _rule(lambda d: d["W"] == prelayout.words(d["K"], d["N"]),
+                  lambda d: f"packed_weight must hold the {prelayout.words(d['K'], d['N'])} words of the tiled copy "
+                            f"of a [{d['K'] // 8}, {d['N']}] weight, got {d['W']}"),
+        ))
+        return NativeProgram(interface=tiled_interface, entry_name=f"intent_b200_w4a16_gemm_tiled_{act.name}",
+                             constants=(group, zp), device=device, empty=lambda d: d["M"] == 0 or d["N"] == 0)
     interface = PublicInterface((
         ViewParameter(0, "activation", act, ("M", "K"), IN),
         ViewParameter(1, "packed_weight", dtypes.i32, ("P", "N"), IN),
@@ -77,16 +102,85 @@ def _lower_w4a16(constants, device):
         rows = d["M"] if kernel != "gemm" else 1 << 30
         return int(query(rows, d["K"], d["N"])) if kernel != "gemm" else 0
 
-    return NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
-                         constants=(group, zp), device=device, workspace=workspace_bytes,
-                         empty=lambda d: d["M"] == 0 or d["N"] == 0,
-                         workspace_status="intent_b200_w4a16_gemv_workspace_status",
-                         device_status=() if kernel == "gemv" else ("intent_b200_w4a16_gemm_device_status",))
+    program = NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
+                            constants=(group, zp), device=device, workspace=workspace_bytes,
+                            empty=lambda d: d["M"] == 0 or d["N"] == 0,
+                            workspace_status="intent_b200_w4a16_gemv_workspace_status",
+                            device_status=() if kernel == "gemv" else ("intent_b200_w4a16_gemm_device_status",))
+    if constants.get("PRELAYOUT"):
+        if kernel == "gemv":
+            raise CompilationStageError("provider_native_compilation", "PRELAYOUT applies to the tensor-core kernels")
+        tiled = _lower_w4a16({**constants, "WEIGHT_LAYOUT": "tiled", "PRELAYOUT": False, "KERNEL": "gemm"}, device)
+        return PrelayoutProgram(program, tiled)
+    return program
+
+
+class PrelayoutProgram:
+    """``weight_only_int4_matmul`` with ``PRELAYOUT=True``: the call surface and the weight format are the
+    reference's, but the weights are taken to be static model state.  Calls with more than 16 activation rows
+    run on a tiled copy of the weight that is made the first time a weight tensor is seen and kept in a
+    :class:`intent_b200.prelayout.PrelayoutCache`; calls with at most 16 rows go to the bandwidth kernel, which
+    reads the reference layout directly."""
+
+    SKINNY_ROWS = 16
+
+    def __init__(self, reference: NativeProgram, tiled: NativeProgram):
+        from .prelayout import PrelayoutCache
+
+        self.reference, self.tiled = reference, tiled
+        self.cache = PrelayoutCache()
+        self.interface = reference.interface
+        self.device = reference.device
+        self.entry_name = tiled.entry_name
+        self.constants = reference.constants
+        self._last = reference
+
+    @property
+    def observation(self):
+        return self._last.observation
+
+    def _route(self, arguments: tuple):
+        """(program, arguments) with the packed weight swapped for its tiled copy when the call is a GEMM."""
+        import torch
+
+        if (len(arguments) >= 3 and all(isinstance(a, torch.Tensor) for a in arguments[:3]) and
+                arguments[0].dim() == 2 and arguments[0].shape[0] > self.SKINNY_ROWS and arguments[1].is_cuda):
+            # validate against the reference interface first: errors name the caller's own arguments
+            self.reference.interface.bind(tuple(arguments[:3]), device=self.reference._torch_device, abstract=True)
+            tiled = self.cache.get(arguments[1])
+            self._last = self.tiled
+            return self.tiled, (arguments[0], tiled.tensor, *arguments[2:])
+        self._last = self.reference
+        return self.reference, arguments
+
+    def run(self, *arguments):
+        program, routed = self._route(arguments)
+        return program.run(*routed)
+
+    def launch(self, *arguments) -> None:
+        program, routed = self._route(arguments)
+        program.launch(*routed)
+
+    def prepare(self, *arguments, outputs=None, explicit_outputs=False):
+        program, routed = self._route(arguments)
+        return program.prepare(*routed, outputs=outputs, explicit_outputs=explicit_outputs)
+
+    def prepare_call(self, arguments: tuple, *, outputs=None):
+        return self.prepare(*arguments, outputs=outputs)
+
+    def infer_outputs(self, arguments: tuple):
+        return self.reference.infer_outputs(arguments)
+
+    def check(self, workspace=None) -> None:
+        self.reference.check(workspace)
+        self.tiled.check(None)
+
 
 
 weight_only_int4_matmul = KernelDefinition(
     name="weight_only_int4_matmul",
-    constexprs={"GROUP_SIZE": 64, "ZERO_POINT": "twos_complement", "ACT_DTYPE": "f16", "KERNEL": "auto"},
+    constexprs={"GROUP_SIZE": 64, "ZERO_POINT": "twos_complement", "ACT_DTYPE": "f16", "KERNEL": "auto",
+                "WEIGHT_LAYOUT": "reference", "PRELAYOUT": False},
     lower=_lower_w4a16,
     reference="examples/kernels/contraction/weight_only_int4.py:18-51",
     summary="Y = X @ dequant(int4 packed along K, per-group scales); f32 accumulation",
@@ -283,24 +377,43 @@ def _lower_grouped(c, device, *, gated):
     if block not in (128, 256):
         raise CompilationStageError("provider_native_compilation", "BLOCK_ROWS must be 128 or 256")
     out_cols = Derived("I", lambda d: d["WN"] // 2) if gated else "WN"
+    weight, weight_rule, suffix = _grouped_weight(c, group)
     interface = PublicInterface((
         ViewParameter(0, "rows", act, ("P", "K"), IN),
         ViewParameter(1, "expert_blocks", dtypes.i32, ("B",), IN, alignment=4),
         ViewParameter(2, "total_padded", dtypes.i32, (1,), IN, alignment=4),
-        ViewParameter(3, "packed_weight", dtypes.i32, ("E", "KP", "WN"), IN),
+        weight,
         ViewParameter(4, "scales", act, ("E", "KG", "WN"), IN),
         ViewParameter(5, "output", act if gated else dtypes.f32, ("P", out_cols), OUT),
     ), dimension_rules=(
-        _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
-              "packed_weight / scales do not match K and GROUP_SIZE"),
+        weight_rule,
         _rule(lambda d: d["B"] * block >= d["P"], f"expert_blocks must cover every {block}-row block of rows"),
     ))
     stem = "upgate_silu" if gated else "down_f32"
-    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_{stem}_{act.name}",
+    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_{stem}{suffix}_{act.name}",
                          constants=(group, zp, block), device=device)
 
 
-_GROUPED_CONSTEXPRS = {"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16", "BLOCK_ROWS": 128}
+def _grouped_weight(c, group):
+    """Parameter 3 of the grouped int4 programs, its shape rule and the entry-name suffix: the reference layout
+    ``[E, K/8, WN]`` or, with ``WEIGHT_LAYOUT='tiled'``, the tiled copies ``[E, words]``
+    (intent_b200.prelayout.tile of the same tensor)."""
+    layout = c.get("WEIGHT_LAYOUT", "reference")
+    if layout == "reference":
+        return (ViewParameter(3, "packed_weight", dtypes.i32, ("E", "KP", "WN"), IN),
+                _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
+                      "packed_weight / scales do not match K and GROUP_SIZE"), "")
+    if layout != "tiled":
+        raise CompilationStageError("frontend_kir", "WEIGHT_LAYOUT must be 'reference' or 'tiled'")
+    from . import prelayout
+
+    return (ViewParameter(3, "packed_weight", dtypes.i32, ("E", "W"), IN),
+            _rule(lambda d: d["KG"] * group == d["K"] and d["W"] == prelayout.words(d["K"], d["WN"]),
+                  "packed_weight must hold the tiled copy of every expert's [K/8, WN] weight"), "_tiled")
+
+
+_GROUPED_CONSTEXPRS = {"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16", "BLOCK_ROWS": 128,
+                       "WEIGHT_LAYOUT": "reference"}
 moe_grouped_upgate_silu = KernelDefinition(
     "moe_grouped_upgate_silu", dict(_GROUPED_CONSTEXPRS), lambda c, d: _lower_grouped(c, d, gated=True),
     "examples/kernels/ragged/grouped_gemm.py:42-70, examples/kernels/ragged/moe.py:37-42, "
@@ -318,22 +431,23 @@ def _lower_down_scatter(c, device):
     block = int(c["BLOCK_ROWS"])
     if block not in (128, 256):
         raise CompilationStageError("provider_native_compilation", "BLOCK_ROWS must be 128 or 256")
+    weight, weight_rule, suffix = _grouped_weight(c, group)
     interface = PublicInterface((
         ViewParameter(0, "rows", act, ("P", "K"), IN),
         ViewParameter(1, "expert_blocks", dtypes.i32, ("B",), IN, alignment=4),
         ViewParameter(2, "total_padded", dtypes.i32, (1,), IN, alignment=4),
-        ViewParameter(3, "packed_weight", dtypes.i32, ("E", "KP", "WN"), IN),
+        weight,
         ViewParameter(4, "scales", act, ("E", "KG", "WN"), IN),
         ViewParameter(5, "sorted_route_ids", dtypes.i32, ("S",), IN, alignment=4),
         ViewParameter(6, "route_weights", dtypes.f32, ("T", "TOP_K"), IN, alignment=4),
         ViewParameter(7, "y", dtypes.f32, ("T", "WN"), INOUT),
     ), dimension_rules=(
-        _rule(lambda d: d["KP"] * 8 == d["K"] and d["KG"] * group == d["K"],
-              "packed_weight / scales do not match K and GROUP_SIZE"),
+        weight_rule,
         _rule(lambda d: d["B"] * block >= d["P"], f"expert_blocks must cover every {block}-row block of rows"),
         _rule(lambda d: d["S"] >= d["P"], "sorted_route_ids must cover every row"),
     ))
-    return NativeProgram(interface=interface, entry_name=f"intent_b200_moe_grouped_w4a16_down_scatter_{act.name}",
+    return NativeProgram(interface=interface,
+                         entry_name=f"intent_b200_moe_grouped_w4a16_down_scatter{suffix}_{act.name}",
                          constants=(group, zp, block), device=device)
 
 

@@ -356,6 +356,9 @@ class CompiledArtifact:
                 (staging / "kernel.source").write_text(self.source, encoding="utf-8")
                 (staging / "kernel.mlir").write_text(self.mlir, encoding="utf-8")
                 (staging / "artifact.json").write_text(json.dumps(self.metadata, indent=2) + "\n", encoding="utf-8")
+                cache = getattr(self.runtime, "cache", None)      # PRELAYOUT artifacts: the tiled weight copies
+                if cache is not None:
+                    cache.export(staging / "prelayout")
                 staging.rename(path)
         except (OSError, UnicodeError, TypeError, ValueError) as error:
             raise CompilationStageError("generated_program_export", str(error),
