@@ -526,10 +526,11 @@ def run_prefill(args, rank: int, world: int, device):
     M, K, N = PREFILL["M"], PREFILL["K"], PREFILL["N"]
     x, packed, scales = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=GROUP, seed=0)
     cols = column_shard(N, world, rank)
-    # the weight is static model state: the artifact keeps a tiled copy of it (made once, outside the timed region)
+    # --prelayout: the artifact keeps a tiled copy of the static weight (made once, outside the timed region).
+    # Measured slower than reading the reference layout directly (about 10 % on this shape), so it is off here.
     artifact = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(device.index),
                           constexprs={"GROUP_SIZE": GROUP, "ZERO_POINT": 8, "ACT_DTYPE": "bf16",
-                                      "PRELAYOUT": not args.no_prelayout})
+                                      "PRELAYOUT": args.prelayout})
     xd = x.to(device)
     pd, sd = packed[:, cols].contiguous().to(device), scales[:, cols].contiguous().to(device)
     call = artifact.prepare(xd, pd, sd)
@@ -557,8 +558,8 @@ def run_prefill(args, rank: int, world: int, device):
     per_launch_flops = flops / world
     achieved = per_launch_flops / (ms * 1e-3) / 1e12
     config = workload_config("prefill", world)
-    weight_note = ("reference [K/8, N] layout read directly" if args.no_prelayout else
-                   "PRELAYOUT: the artifact keeps a tiled copy of the static weight (made once, before the timed region)")
+    weight_note = ("PRELAYOUT: the artifact keeps a tiled copy of the static weight (made once, before the timed "
+                   "region)" if args.prelayout else "reference [K/8, N] layout read directly")
     line = {
         "metric": "w4a16_prefill_TFLOPs", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
@@ -768,7 +769,7 @@ def run_moe(args, rank: int, world: int, device):
     if world == 1:
         ffn = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts,
                           block_size=args.moe_block, target=ib.B200Target(device.index),
-                          prelayout=not args.no_prelayout)
+                          prelayout=args.prelayout)
 
         def forward(lg, xx):
             ids, w = ffn.route(lg)
@@ -1330,8 +1331,9 @@ def main() -> int:
                         help="rows every expert span is padded to (= row tile of the grouped contraction)")
     parser.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores/loads, or NCCL all-to-all")
-    parser.add_argument("--no-prelayout", action="store_true",
-                        help="tensor-core W4A16 kernels read the reference [K/8, N] layout instead of a tiled copy")
+    parser.add_argument("--prelayout", action="store_true",
+                        help="tensor-core W4A16 kernels read a tiled copy of the weight (intent_b200.prelayout) "
+                             "instead of the reference [K/8, N] layout")
     parser.add_argument("--moe-eager", action="store_true",
                         help="1 GPU: launch the bound MoE step eagerly instead of replaying it as one CUDA graph")
     parser.add_argument("--moe-graph", action="store_true",

@@ -445,6 +445,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p)
       const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
       if (p.prelaid) {
         // tiled copy: this thread's four words of the k block are one 16-byte load (rows past K are zeros)
+        static_assert(DQ_ROWS == 4 && DQ_PARTS == 2, "the tiled layout is two halves of four words per column");
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(f_w));
         const bool use = f_col_ok;
         b.w[0] = use ? v.x : 0u; b.w[1] = use ? v.y : 0u; b.w[2] = use ? v.z : 0u; b.w[3] = use ? v.w : 0u;

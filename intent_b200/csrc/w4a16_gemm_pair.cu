@@ -40,8 +40,8 @@ constexpr int A_BYTES = BM * BK * 2;        // one 128-row box of X
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the operand tile, 16 KiB
 constexpr int A_STAGES = 3, B_STAGES = 4;
 constexpr int DEQUANT_WARPS = 16;
-constexpr int DQ_PARTS = DEQUANT_WARPS * 32 / (BN / 2);  // threads per weight column (2)
-constexpr int DQ_ROWS = (BK / 8) / DQ_PARTS;             // packed words per thread and k block (4)
+constexpr int DQ_PARTS = DEQUANT_WARPS * 32 / (BN / 2);  // threads per weight column (4)
+constexpr int DQ_ROWS = (BK / 8) / DQ_PARTS;             // packed words per thread and k block (2)
 constexpr int THREADS = (6 + DEQUANT_WARPS) * 32;
 constexpr int SMEM_BYTES = 1024 + A_STAGES * MT * A_BYTES + B_STAGES * B_HALF_BYTES + 256;
 constexpr int BAND_TILES = 4;               // 512-row tiles per band of the tile walk
@@ -308,17 +308,21 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
         f_col_ok = col < p.N;
         f_w = p.packed + (f_col_ok ? col : 0);
         f_s = p.scales + (f_col_ok ? col : 0);
-        if (p.prelaid)   // [column block of 128][k block][part][column][4 words]; a column past N reads word 0, unused
-          f_w = f_col_ok ? p.packed + ((size_t(col >> 7) * p.k_blocks * DQ_PARTS + part) * 128 + (col & 127)) * 4
+        // tiled copy: [column block of 128][k block][half of the k block][column][4 words].  This kernel puts four
+        // threads on a column (DQ_ROWS = 2 words each): thread `part` takes words 2 * (part & 1) .. + 1 of half
+        // part >> 1.  A column past N reads word 0 of the buffer, unused.
+        if (p.prelaid)
+          f_w = f_col_ok ? p.packed + ((size_t(col >> 7) * p.k_blocks * 2 + (part >> 1)) * 128 + (col & 127)) * 4 +
+                               (part & 1) * 2
                          : p.packed;
       }
       const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
       if (p.prelaid) {
-        // tiled copy: this thread's four words of the k block are one 16-byte load, a warp reads 512 contiguous
-        // bytes; rows past K are stored as zeros
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(f_w));
-        b.w[0] = f_col_ok ? v.x : 0u; b.w[1] = f_col_ok ? v.y : 0u;
-        b.w[2] = f_col_ok ? v.z : 0u; b.w[3] = f_col_ok ? v.w : 0u;
+        // tiled copy: this thread's words of the k block are adjacent (rows past K are stored as zeros)
+        static_assert(DQ_ROWS == 2, "the tiled fetch below reads this thread's two words as one 8-byte load");
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(f_w));
+        b.w[0] = f_col_ok ? v.x : 0u;
+        b.w[1] = f_col_ok ? v.y : 0u;
       } else if (f_col_ok && rows_left >= DQ_ROWS) {
         const uint32_t* q = f_w + size_t(part * DQ_ROWS) * p.N;
 #pragma unroll
@@ -334,7 +338,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       const uint32_t c = g1 == g0 ? a : ((f_col_ok && g1 < scale_rows) ? __ldg(f_s + size_t(g1) * p.N) : 0u);
       b.s_lo = a | (a << 16);
       b.s_hi = c | (c << 16);
-      f_w += p.prelaid ? (f_col_ok ? size_t(DQ_PARTS) * 128 * 4 : 0) : size_t(BK / 8) * p.N;
+      f_w += p.prelaid ? (f_col_ok ? size_t(2) * 128 * 4 : 0) : size_t(BK / 8) * p.N;
       if (++f_kb == p.k_blocks) {
         f_kb = 0;
         f_tile += pairs;
