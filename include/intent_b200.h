@@ -108,14 +108,6 @@ INTENT_B200_API int intent_b200_w4a16_gemm_f16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int intent_b200_w4a16_gemm_bf16(INTENT_B200_W4A16_SLOTS);
 INTENT_B200_API int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N);
 INTENT_B200_API int64_t intent_b200_w4a16_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N);
-/* Scratch of the tensor-core entries (0 for most shapes).  With at least 512 activation rows the kernel may cut
- * the k blocks of all output tiles into one equal range per CTA pair ("stream-K") when whole tiles would leave
- * pairs idle - 64 tiles for 74 pairs on a column shard of a multi-GPU run; pairs that share a tile exchange f32
- * partial tiles through this scratch.  It needs no clearing by the caller (the entry clears its counters on
- * `stream`); without it (NULL / too small) the kernel uses whole tiles.  Not shared by overlapping launches. */
-INTENT_B200_API int64_t intent_b200_w4a16_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
-/* Stream-K split of the CTA-pair kernel; 0 forces whole tiles.  For measurement and tests; process-global. */
-INTENT_B200_API int intent_b200_w4a16_gemm_stream_k(int32_t enable);
 /* Synchronises `stream`, returns the status word of a bandwidth-kernel workspace (0 or
  * INTENT_B200_ERR_TIMEOUT) and, when it is set, zero-fills the workspace again so that it can be reused.
  * Call it wherever the host synchronises anyway (end of a decode step, before results are consumed). */

@@ -12,9 +12,8 @@ void note_launch(int count) { g_launches.fetch_add(count, std::memory_order_rela
 int w4a16_stream_f16(View2, View2, View2, View2, int, int, void*, int64_t, cudaStream_t);
 int w4a16_stream_bf16(View2, View2, View2, View2, int, int, void*, int64_t, cudaStream_t);
 int64_t w4a16_stream_workspace_bytes(int64_t M, int64_t K, int64_t N);
-int w4a16_gemm_f16(View2, View2, View2, View2, int, int, cudaStream_t, void*, int64_t);
-int w4a16_gemm_bf16(View2, View2, View2, View2, int, int, cudaStream_t, void*, int64_t);
-int64_t w4a16_gemm_pair_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int w4a16_gemm_f16(View2, View2, View2, View2, int, int, cudaStream_t);
+int w4a16_gemm_bf16(View2, View2, View2, View2, int, int, cudaStream_t);
 
 // Rows of activation up to which the bandwidth kernel is used.
 constexpr int64_t kSkinnyMaxM = 16;
@@ -93,7 +92,7 @@ extern "C" int64_t intent_b200_launch_count(void) { return ib200::g_launches.loa
                                         workspace_bytes, static_cast<cudaStream_t>(stream));              \
     return ib200::w4a16_gemm_##TYPE(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2),        \
                                     IB200_VIEW2_ARG(a3), group_size, zero_point,                          \
-                                    static_cast<cudaStream_t>(stream), workspace, workspace_bytes);       \
+                                    static_cast<cudaStream_t>(stream));                                   \
   }
 
 IB200_W4A16_ENTRY(intent_b200_weight_only_int4_matmul_f16, f16, a0_d0 <= ib200::kSkinnyMaxM)
@@ -104,12 +103,7 @@ IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_f16, f16, false)
 IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_bf16, bf16, false)
 
 extern "C" int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N) {
-  return M <= ib200::kSkinnyMaxM ? ib200::w4a16_stream_workspace_bytes(M, K, N)
-                                 : ib200::w4a16_gemm_pair_workspace_bytes(M, K, N);
-}
-
-extern "C" int64_t intent_b200_w4a16_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N) {
-  return ib200::w4a16_gemm_pair_workspace_bytes(M, K, N);
+  return M <= ib200::kSkinnyMaxM ? ib200::w4a16_stream_workspace_bytes(M, K, N) : 0;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -55,8 +55,7 @@ __device__ int g_w4a16_gemm_status = 0;
 
 template <typename T>
 int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
-                    int group_size, int zero_point, cudaStream_t stream, bool prelaid, void* workspace,
-                    int64_t workspace_bytes);
+                    int group_size, int zero_point, cudaStream_t stream, bool prelaid);
 int w4a16_gemm_pair_take_status(int* value);
 int64_t w4a16_prelayout_words(int64_t K, int64_t N);
 
@@ -589,7 +588,7 @@ int launch_gemm(const void* x, int64_t rows, int64_t K, const void* w, const voi
 
 template <typename T>
 int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cudaStream_t stream,
-        bool prelaid = false, void* workspace = nullptr, int64_t workspace_bytes = 0) {
+        bool prelaid = false) {
   const int64_t M = x.d0, K = x.d1, N = w.d1;
   if (group_size != 32 && group_size != 64 && group_size != 128) return INTENT_B200_ERR_UNSUPPORTED;
   if (zero_point != -1 && zero_point != 8) return INTENT_B200_ERR_UNSUPPORTED;
@@ -601,8 +600,7 @@ int run(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, cuda
   if (!aligned16(x.p) || !aligned16(w.p) || !aligned16(s.p) || !aligned16(y.p)) return INTENT_B200_ERR_LAYOUT;
   if (K == 0 || N % 8 != 0 || M > (1 << 24) || K > (1 << 24) || N > (1 << 24)) return INTENT_B200_ERR_UNSUPPORTED;
   {  // large M: CTA pairs, each CTA dequantises half of every weight tile
-    const int status = w4a16_gemm_pair<T>(x.p, M, K, w.p, s.p, N, y.p, group_size, zero_point, stream, prelaid,
-                                          workspace, workspace_bytes);
+    const int status = w4a16_gemm_pair<T>(x.p, M, K, w.p, s.p, N, y.p, group_size, zero_point, stream, prelaid);
     if (status != INTENT_B200_ERR_UNSUPPORTED) return status;
   }
   if (M > BM)   // two row blocks per tile share every dequantised weight tile
@@ -694,13 +692,11 @@ inline bool tiled_as_experts(View2 tiled, int64_t K, int64_t WN, View3* w) {
 }  // namespace ib200
 
 namespace ib200 {
-int w4a16_gemm_f16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream, void* workspace,
-                   int64_t workspace_bytes) {
-  return run<__half>(x, w, s, y, g, zp, stream, false, workspace, workspace_bytes);
+int w4a16_gemm_f16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream) {
+  return run<__half>(x, w, s, y, g, zp, stream);
 }
-int w4a16_gemm_bf16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream, void* workspace,
-                    int64_t workspace_bytes) {
-  return run<__nv_bfloat16>(x, w, s, y, g, zp, stream, false, workspace, workspace_bytes);
+int w4a16_gemm_bf16(View2 x, View2 w, View2 s, View2 y, int g, int zp, cudaStream_t stream) {
+  return run<__nv_bfloat16>(x, w, s, y, g, zp, stream);
 }
 }  // namespace ib200
 

@@ -18,17 +18,6 @@
 // 2..5 epilogue (own TMEM lanes).  Only the leader CTA (cluster rank 0) issues MMAs (one thread
 // of warp 1); its commits arrive on the stage barriers of both CTAs.
 // No TMA load here is a multicast load.  Every wait is bounded (tma.cuh).
-//
-// Work split.  When the tile count is (close to) a multiple of the pair count, pair p takes tiles p, p + pairs, ...
-// Otherwise - a column shard of a multi-GPU run leaves 64 tiles for 74 pairs - the k blocks of all tiles form one
-// sequence of units that is cut into equal contiguous ranges, one per pair ("stream-K"): every pair then works the
-// same time.  A tile whose k blocks are shared by several pairs is finished by the pair that holds its LAST k
-// block: the other pairs store their f32 partial tile to scratch and bump the tile's counter; the finisher waits
-// (bounded) for those arrivals and adds the partials, in pair order, to its own accumulators in the epilogue.
-// Pairs walk their ranges from the high end down, so a finisher only ever waits for lower-numbered pairs, which
-// reach the shared tile first; all pairs are resident at once (the grid is capped at the number of clusters the
-// device can hold).  The summation order is fixed, so results are reproducible; they differ in the last bits from
-// the unsplit order.
 #include <type_traits>
 
 #include "common.cuh"
@@ -65,54 +54,6 @@ struct PairParams {
   int k_blocks, m_tiles, n_tiles;
   int group_size, twos_complement;
   int prelaid;      // packed points at the tiled copy (w4a16_prelayout.cu) instead of the [K/8, N] matrix
-  int stream_k;     // 1: units (tile, k block) cut into one contiguous range per pair
-  float* partials;  // stream-K: [pairs][512][256] f32, one partial tile per pair
-  int* arrivals;    // stream-K: [tiles] epilogue warps that have stored their share of a partial, zero at launch
-};
-
-struct Segment {
-  int tile, kb0, kb1;   // k blocks [kb0, kb1) of one tile
-};
-
-// A pair's work as a list of segments.  Plain split: whole tiles pair, pair + pairs, ...  Stream-K: the pair's unit
-// range [u0, u1), highest tile first.
-struct Walk {
-  int stream_k, pair, pairs, tiles, k_blocks;
-  long long u0, u1;
-  __device__ __forceinline__ static long long range_start(long long pair, long long pairs, long long units) {
-    return pair * units / pairs;
-  }
-  __device__ Walk(const PairParams& p, int pair_, int pairs_) {
-    stream_k = p.stream_k;
-    pair = pair_;
-    pairs = pairs_;
-    tiles = p.m_tiles * p.n_tiles;
-    k_blocks = p.k_blocks;
-    const long long units = (long long)tiles * k_blocks;
-    u0 = range_start(pair, pairs, units);
-    u1 = range_start(pair + 1, pairs, units);
-  }
-  __device__ __forceinline__ int count() const {
-    if (!stream_k) return tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
-    return u1 > u0 ? int((u1 - 1) / k_blocks - u0 / k_blocks) + 1 : 0;
-  }
-  __device__ __forceinline__ Segment at(int i) const {
-    if (!stream_k) return Segment{pair + i * pairs, 0, k_blocks};
-    const int tile = int((u1 - 1) / k_blocks) - i;
-    const long long first = (long long)tile * k_blocks;
-    return Segment{tile, int(u0 > first ? u0 - first : 0), int(u1 - first < k_blocks ? u1 - first : k_blocks)};
-  }
-  __device__ __forceinline__ long long k_block_total() const {
-    return stream_k ? u1 - u0 : (long long)count() * k_blocks;
-  }
-  // the pair whose range holds unit u
-  __device__ __forceinline__ int pair_of(long long u) const {
-    const long long units = (long long)tiles * k_blocks;
-    long long q = u * pairs / units;
-    while (q + 1 < pairs && range_start(q + 1, pairs, units) <= u) ++q;
-    while (q > 0 && range_start(q, pairs, units) > u) --q;
-    return int(q);
-  }
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -199,8 +140,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
   const int lane = tid & 31;
   const uint32_t rank = cluster_rank();
   const int pair = int(blockIdx.x) >> 1, pairs = int(gridDim.x) >> 1;
-  const Walk walk(p, pair, pairs);
-  const int segments = walk.count();
+  const int tiles = p.m_tiles * p.n_tiles;
 
   if (tid == 0) {
     for (int s = 0; s < A_STAGES; ++s) {
@@ -228,12 +168,11 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int i = 0; i < segments && ok; ++i) {
-        const Segment seg = walk.at(i);
+      for (int tile = pair; tile < tiles && ok; tile += pairs) {
         int m_tile, n_tile;
-        pair_tile_coords(seg.tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
+        pair_tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
         const int row0 = m_tile * PAIR_ROWS + int(rank) * (MT * BM);
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % A_STAGES;
           if (!mbar_wait(empty_a + 8 * s, ((it / A_STAGES) & 1) ^ 1)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(full_a + 8 * s, 2 * MT * A_BYTES);
@@ -250,7 +189,8 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
     if (lane == 0 && rank != 0) {
       // Peer CTA: relay "my half of operand tile t is written" to the leader with one cluster-scope
       // arrival per k block (the dequantiser warps themselves only synchronise inside their CTA).
-      const uint32_t total = uint32_t(walk.k_block_total());
+      const int my_tiles = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
+      const uint32_t total = uint32_t(my_tiles) * uint32_t(p.k_blocks);
       const uint32_t leader_full_b = map_to_rank(full_b, 0);
       bool ok = true;
       for (uint32_t it = 0; it < total; ++it) {
@@ -265,11 +205,10 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       constexpr uint32_t idesc = umma_idesc(1, fmt, fmt, 0, 0, 2 * BM, BN);
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int i = 0; i < segments && ok; ++i, ++local) {
-        const Segment seg = walk.at(i);
+      for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
         if (!mbar_wait(tmem_empty, (local & 1) ^ 1)) { ok = false; break; }
         tcgen05_fence_after();
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % A_STAGES, t = it % B_STAGES;
           if (!mbar_wait(full_a + 8 * s, (it / A_STAGES) & 1) ||
               !mbar_wait(full_b + 8 * t, (it / B_STAGES) & 1)) { ok = false; break; }
@@ -281,7 +220,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk)
               umma_f16_pair(tmem_base + mt * BN, desc_a + uint64_t(2 * kk), desc_b + uint64_t(2 * kk), idesc,
-                            kb != seg.kb0 || kk != 0);
+                            (kb | kk) != 0);
           }
           umma_commit_pair(empty_a + 8 * s);
           umma_commit_pair(empty_b + 8 * t);
@@ -296,71 +235,23 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
     uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
     const uint32_t leader_empty = map_to_rank(tmem_empty, 0);
     uint32_t local = 0;
-    for (int i = 0; i < segments; ++i, ++local) {
-      const Segment seg = walk.at(i);
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
       int m_tile, n_tile;
-      pair_tile_coords(seg.tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
-      // Stream-K: who shares this tile.  first_pair .. last_pair hold its k blocks in that order; the last one
-      // finishes the tile, the others leave a partial.
-      int first_pair = pair, last_pair = pair;
-      if (p.stream_k && (seg.kb0 != 0 || seg.kb1 != p.k_blocks)) {
-        const long long tile_first = (long long)seg.tile * p.k_blocks;
-        first_pair = walk.pair_of(tile_first);
-        last_pair = walk.pair_of(tile_first + p.k_blocks - 1);
-      }
-      const bool leaves_partial = pair != last_pair;
+      pair_tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
       if (!__all_sync(0xffffffffu, mbar_wait(tmem_full, local & 1))) {
         if (lane == 0) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
         break;
       }
       tcgen05_fence_after();
-      bool partials_ready = true;
-      if (!leaves_partial && first_pair != last_pair) {
-        // finisher: every epilogue warp (4 per CTA, 2 CTAs) of every other pair of the tile has stored its share
-        const int expected = 8 * (last_pair - first_pair);
-        int seen = 0;
-        if (lane == 0) {
-          for (int poll = 0; poll < (1 << 22); ++poll) {
-            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.arrivals + seg.tile) : "memory");
-            if (seen >= expected) break;
-            __nanosleep(100);
-          }
-        }
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        partials_ready = seen >= expected;
-        if (!partials_ready && lane == 0) atomicExch(&g_w4a16_pair_status, INTENT_B200_ERR_TIMEOUT);
-      }
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
-        const int tile_row = int(rank) * (MT * BM) + mt * BM + quadrant * 32 + lane;   // row inside the 512-row tile
-        const int row = m_tile * PAIR_ROWS + tile_row;
+        const int row = m_tile * PAIR_ROWS + int(rank) * (MT * BM) + mt * BM + quadrant * 32 + lane;
         const uint32_t taddr = tmem_base + mt * BN + (uint32_t(quadrant * 32) << 16);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tmem_load_32x32(taddr + c * 32, v);
           tmem_load_wait();
-          if (leaves_partial) {
-            float4* dst = reinterpret_cast<float4*>(p.partials + (size_t(pair) * PAIR_ROWS + tile_row) * BN + c * 32);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                   __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
-            continue;
-          }
-          if (partials_ready)
-            for (int other = first_pair; other < last_pair; ++other) {   // fixed order: reproducible
-              const float4* src =
-                  reinterpret_cast<const float4*>(p.partials + (size_t(other) * PAIR_ROWS + tile_row) * BN + c * 32);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 a = __ldcg(src + q);
-                v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + a.x);
-                v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + a.y);
-                v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + a.z);
-                v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + a.w);
-              }
-            }
           const int col = n_tile * BN + c * 32;
           if (row < p.M) {
             uint16_t* dst = y + size_t(row) * p.N + col;
@@ -382,14 +273,6 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
           }
         }
       }
-      if (leaves_partial) {
-        // this warp's share of the partial is written: release it to the tile's finisher
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence();
-          atomicAdd(p.arrivals + seg.tile, 1);
-        }
-      }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_empty);
@@ -403,28 +286,24 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
     const uint32_t row_off = uint32_t(n) * 128u;
     const uint32_t swz = uint32_t(n & 7);
     const int packed_rows = p.K >> 3, scale_rows = p.K / p.group_size;
-    const int total = int(walk.k_block_total());
+    const int my_tiles = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
+    const int total = my_tiles * p.k_blocks;
     const int group_shift = 31 - __clz(p.group_size);
 
     struct Block {
       uint32_t w[DQ_ROWS];
       uint32_t s_lo, s_hi;
     };
-    int f_seg = 0, f_kb = 0, f_kb_end = 0, f_left = total;
-    bool f_new_segment = true;
+    int f_tile = pair, f_kb = 0, f_left = total;
     bool f_col_ok = false;
     const uint32_t* f_w = p.packed;
     const uint16_t* f_s = p.scales;
     auto fetch = [&](Block& b) {
       if (f_left <= 0) return;
       --f_left;
-      if (f_new_segment) {
-        const Segment seg = walk.at(f_seg);
-        f_kb = seg.kb0;
-        f_kb_end = seg.kb1;
-        f_new_segment = false;
+      if (f_kb == 0) {
         int m_tile, n_tile;
-        pair_tile_coords(seg.tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
+        pair_tile_coords(f_tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
         const int col = n_tile * BN + int(rank) * (BN / 2) + n;
         f_col_ok = col < p.N;
         f_w = p.packed + (f_col_ok ? col : 0);
@@ -436,8 +315,6 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
           f_w = f_col_ok ? p.packed + ((size_t(col >> 7) * p.k_blocks * 2 + (part >> 1)) * 128 + (col & 127)) * 4 +
                                (part & 1) * 2
                          : p.packed;
-        // a segment may start in the middle of the tile's k range (stream-K)
-        f_w += size_t(f_kb) * (p.prelaid ? (f_col_ok ? size_t(2) * 128 * 4 : 0) : size_t(BK / 8) * p.N);
       }
       const int rows_left = packed_rows - f_kb * (BK / 8) - part * DQ_ROWS;
       if (p.prelaid) {
@@ -462,9 +339,9 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
       b.s_lo = a | (a << 16);
       b.s_hi = c | (c << 16);
       f_w += p.prelaid ? (f_col_ok ? size_t(2) * 128 * 4 : 0) : size_t(BK / 8) * p.N;
-      if (++f_kb == f_kb_end) {
-        f_new_segment = true;
-        ++f_seg;
+      if (++f_kb == p.k_blocks) {
+        f_kb = 0;
+        f_tile += pairs;
       }
     };
     bool ok = true;
@@ -521,53 +398,14 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const PairPara
 }
 
 int g_pair_enabled = 1;
-int g_stream_k = 1;        // 0 forces the plain tile split (tests: bit equality with the single-CTA kernel)
-
-// Clusters of two CTAs of this kernel that the device can hold at once (0 when the query fails).
-template <typename T>
-int resident_pairs(int sms) {
-  static int cached = -1;
-  if (cached >= 0) return cached;
-  auto kernel = w4a16_gemm_pair_kernel<T>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(unsigned(sms / 2 * 2), 1, 1);
-  config.blockDim = dim3(THREADS, 1, 1);
-  config.dynamicSmemBytes = SMEM_BYTES;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = 2;
-  attribute[0].val.clusterDim.y = 1;
-  attribute[0].val.clusterDim.z = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  cached = clusters;
-  return cached;
-}
-
-inline size_t align256(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 
 }  // namespace
 
 // Dense W4A16 on CTA pairs; returns INTENT_B200_ERR_UNSUPPORTED when the shape should use the
 // single-CTA kernel instead.  Arguments are already validated by the caller.
-// Scratch the stream-K split of a shape needs (0: the shape runs with the plain split or on the single-CTA kernel).
-int64_t w4a16_gemm_pair_workspace_bytes(int64_t M, int64_t K, int64_t N) {
-  if (M < PAIR_ROWS || N <= 0 || K <= 0) return 0;
-  const int64_t tiles = ((M + PAIR_ROWS - 1) / PAIR_ROWS) * ((N + BN - 1) / BN);
-  // sized for the 74 pairs of the 148-SM part this library targets; the entry checks the actual need
-  return int64_t(align256(size_t(tiles) * 4) + size_t(74) * PAIR_ROWS * BN * 4);
-}
-
 template <typename T>
 int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const void* s, int64_t N, void* y,
-                    int group_size, int zero_point, cudaStream_t stream, bool prelaid, void* workspace,
-                    int64_t workspace_bytes) {
+                    int group_size, int zero_point, cudaStream_t stream, bool prelaid) {
   if (!g_pair_enabled || M < PAIR_ROWS) return INTENT_B200_ERR_UNSUPPORTED;
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
@@ -597,32 +435,9 @@ int w4a16_gemm_pair(const void* x, int64_t M, int64_t K, const void* w, const vo
   if (e != cudaSuccess) return cuda_status(e);
   const int tiles = p.m_tiles * p.n_tiles;
   int pairs = sms / 2;
-  const int resident = resident_pairs<T>(sms);
-  if (resident > 0 && resident < pairs) pairs = resident;      // every pair of the grid is resident at once
-  // Stream-K when whole tiles would leave more than a twentieth of the pair-time idle, the scratch is there, and
-  // the device confirmed that all pairs run concurrently (a finisher waits for other pairs).
-  const int waves = (tiles + pairs - 1) / pairs;
-  const bool uneven = tiles * 20 < waves * pairs * 19;
-  const size_t counters_bytes = align256(size_t(tiles) * 4);
-  // a pair's range is at least 16 k blocks (a partial tile costs 512 KB of traffic each way)
-  const long long units = (long long)tiles * p.k_blocks;
-  int sharing = units / 16 < pairs ? int(units / 16) : pairs;
-  const size_t need = counters_bytes + size_t(sharing > 0 ? sharing : 1) * PAIR_ROWS * BN * 4;
-  if (g_stream_k && uneven && resident > 0 && sharing > 1 && sharing > tiles / 2 && workspace &&
-      aligned16(workspace) && workspace_bytes >= int64_t(need) && units < (1ll << 40)) {
-    p.stream_k = 1;
-    pairs = sharing;
-    p.arrivals = static_cast<int*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes);
-    e = cudaMemsetAsync(p.arrivals, 0, counters_bytes, stream);
-    if (e != cudaSuccess) return cuda_status(e);
-  } else if (pairs > tiles) {
-    pairs = tiles;
-  }
+  if (pairs > tiles) pairs = tiles;
   if (LaunchFacts* sink = observe_sink())
-    return record_launch(sink, reinterpret_cast<const void*>(kernel),
-                         p.stream_k ? "w4a16_gemm_pair_kernel CTA pairs, 512x256 tiles, stream-K"
-                                    : "w4a16_gemm_pair_kernel CTA pairs, 512x256 tiles",
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "w4a16_gemm_pair_kernel CTA pairs, 512x256 tiles",
                          2 * pairs, THREADS, SMEM_BYTES, 2);
   kernel<<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(map_x, p);
   note_launch();
@@ -643,18 +458,13 @@ int w4a16_gemm_pair_take_status(int* value) {
 }
 
 template int w4a16_gemm_pair<__half>(const void*, int64_t, int64_t, const void*, const void*, int64_t, void*, int, int,
-                                     cudaStream_t, bool, void*, int64_t);
+                                     cudaStream_t, bool);
 template int w4a16_gemm_pair<__nv_bfloat16>(const void*, int64_t, int64_t, const void*, const void*, int64_t, void*,
-                                            int, int, cudaStream_t, bool, void*, int64_t);
+                                            int, int, cudaStream_t, bool);
 
 }  // namespace ib200
 
 extern "C" int intent_b200_w4a16_gemm_pairs(int32_t enable) {
   ib200::g_pair_enabled = enable ? 1 : 0;
-  return INTENT_B200_OK;
-}
-
-extern "C" int intent_b200_w4a16_gemm_stream_k(int32_t enable) {
-  ib200::g_stream_k = enable ? 1 : 0;
   return INTENT_B200_OK;
 }

@@ -96,21 +96,16 @@ def _lower_w4a16(constants, device):
 
         from .runtime import native
 
-        library = native.library()
-        name = {"auto": "intent_b200_weight_only_int4_matmul_workspace_bytes",
-                "gemv": "intent_b200_w4a16_gemv_workspace_bytes",
-                "gemm": "intent_b200_w4a16_gemm_workspace_bytes"}[kernel]
-        query = getattr(library, name)
+        query = native.library().intent_b200_weight_only_int4_matmul_workspace_bytes
         query.restype = ctypes.c_int64
         query.argtypes = [ctypes.c_int64] * 3
-        return int(query(d["M"], d["K"], d["N"]))
+        rows = d["M"] if kernel != "gemm" else 1 << 30
+        return int(query(rows, d["K"], d["N"])) if kernel != "gemm" else 0
 
     program = NativeProgram(interface=interface, entry_name=f"intent_b200_{stem}_{act.name}",
                             constants=(group, zp), device=device, workspace=workspace_bytes,
                             empty=lambda d: d["M"] == 0 or d["N"] == 0,
                             workspace_status="intent_b200_w4a16_gemv_workspace_status",
-                            workspace_kind=lambda d: "gemm" if kernel == "gemm" or (kernel == "auto" and d["M"] > 16)
-                            else "gemv",
                             device_status=() if kernel == "gemv" else ("intent_b200_w4a16_gemm_device_status",))
     if constants.get("PRELAYOUT"):
         if kernel == "gemv":

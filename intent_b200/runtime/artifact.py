@@ -71,9 +71,6 @@ class PreparedCall:
         self._observation: NativeObservation | None = None
         self._skip = program.is_empty(bound)
         self._facts: dict | None = None     # resource facts of this binding, observed once
-        # only the bandwidth kernel keeps a status word at the head of its scratch
-        kind = program._workspace_kind(bound.dimensions) if program._workspace_kind is not None else None
-        self._status_workspace = () if kind == "gemm" else self._workspace
 
     @property
     def outputs(self) -> tuple:
@@ -97,7 +94,7 @@ class PreparedCall:
         """Synchronise the current stream and raise ``CompilationStageError('provider_invocation')`` if a
         bounded device-side wait of an earlier launch of this call gave up (its output is then incomplete).
         A workspace that such a launch left dirty is cleared, so the call can be launched again."""
-        self.program.check(self._status_workspace)
+        self.program.check(self._workspace)
 
     def launch(self) -> None:
         import torch
@@ -179,13 +176,12 @@ class NativeProgram:
 
     def __init__(self, *, interface: PublicInterface, entry_name: str, constants: tuple = (),
                  device: int, workspace=None, empty=None, scalar_carriers=None,
-                 workspace_status: str | None = None, device_status: tuple = (), workspace_kind=None) -> None:
+                 workspace_status: str | None = None, device_status: tuple = ()) -> None:
         self.interface = interface
         self.entry_name = entry_name
         self.constants = tuple(int(c) for c in constants)
         self.device = device
         self._workspace_spec = workspace     # callable(dimensions) -> workspace bytes (0 = none)
-        self._workspace_kind = workspace_kind   # callable(dimensions) -> which kernel's scratch this binding needs
         self._stream_workspaces: dict = {}   # stream handle -> zero-initialised buffer reused by run()
         self._empty = empty                  # callable(dimensions) -> bool
         self._observation: NativeObservation | None = None
@@ -238,8 +234,7 @@ class NativeProgram:
                 reader = getattr(library, self._workspace_status)
                 reader.restype = ctypes.c_int
                 reader.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
-                buffers = workspace if workspace is not None else tuple(
-                    buffer for (_, kind), buffer in self._stream_workspaces.items() if kind != "gemm")
+                buffers = workspace if workspace is not None else tuple(self._stream_workspaces.values())
                 for buffer in buffers:
                     if buffer.numel() >= 4:
                         failures.append(int(reader(ctypes.c_void_p(buffer.data_ptr()),
@@ -270,10 +265,7 @@ class NativeProgram:
             return (torch.empty((0,), dtype=torch.uint8, device=self._torch_device),)
         if not per_stream:
             return (torch.zeros((size,), dtype=torch.uint8, device=self._torch_device),)
-        # one buffer per stream and per kind of scratch: an entry that picks between kernels by shape keeps the
-        # zero-filled scratch of one kernel apart from the free-form scratch of another
-        kind = self._workspace_kind(bound.dimensions) if self._workspace_kind is not None else None
-        key = (torch.cuda.current_stream(self.device).cuda_stream, kind)
+        key = torch.cuda.current_stream(self.device).cuda_stream
         cached = self._stream_workspaces.get(key)
         if cached is None or cached.numel() < size:
             cached = torch.zeros((max(size, 1 << 16),), dtype=torch.uint8, device=self._torch_device)

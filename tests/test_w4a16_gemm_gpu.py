@@ -131,7 +131,6 @@ def test_cta_pair_kernel_equals_single_cta_kernel(cuda_device, M, K, N):
     artifact = _compile("bf16", 128, 8)
     xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
     try:
-        lib.intent_b200_w4a16_gemm_stream_k(0)      # whole tiles: the k loop of a tile is then one accumulation
         lib.intent_b200_w4a16_gemm_pairs(1)
         paired = artifact.run(xd, pd, sd)
         lib.intent_b200_w4a16_gemm_pairs(0)
@@ -139,41 +138,7 @@ def test_cta_pair_kernel_equals_single_cta_kernel(cuda_device, M, K, N):
         torch.cuda.synchronize()
     finally:
         lib.intent_b200_w4a16_gemm_pairs(1)
-        lib.intent_b200_w4a16_gemm_stream_k(1)
     assert _device_status() == 0
     assert torch.equal(paired, single)
     ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
     assert max_abs_rel(paired.cpu(), ref) <= 2e-2
-
-
-@pytest.mark.parametrize("M,K,N", [(512, 2048, 256), (1100, 1024, 776), (2048, 2048, 2048), (8192, 2048, 1024)])
-def test_stream_k_split(cuda_device, M, K, N):
-    """Tile counts that do not fill the CTA pairs evenly (one tile, 12, 32, and the 64 tiles of an 8-GPU column
-    shard's row-tile grid): the k blocks of all tiles are cut into equal ranges per pair and shared tiles are
-    summed from f32 partials in a fixed order.  Within tolerance of the oracle, close to the whole-tile result,
-    the same bits on every run, and the same result from a prepared call that is launched repeatedly (the
-    scratch is reused)."""
-    lib = native.library()
-    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=128, seed=17)
-    artifact = _compile("bf16", 128, 8)
-    xd, pd, sd = x.to(cuda_device), p.to(cuda_device), s.to(cuda_device)
-    try:
-        lib.intent_b200_w4a16_gemm_stream_k(0)
-        whole = artifact.run(xd, pd, sd)
-    finally:
-        lib.intent_b200_w4a16_gemm_stream_k(1)
-    split = artifact.run(xd, pd, sd)
-    torch.cuda.synchronize()
-    assert _device_status() == 0
-    assert "stream-K" in artifact.observation.kernel
-    ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
-    assert max_abs_rel(split.cpu(), ref) <= 2e-2
-    assert max_abs_rel(split.cpu(), whole.cpu()) <= 8e-3          # a different f32 summation order, one bf16 ulp apart
-    assert torch.equal(artifact.run(xd, pd, sd), split)
-    call = artifact.prepare(xd, pd, sd)
-    for _ in range(3):
-        call.result().zero_()
-        call.launch()
-    torch.cuda.synchronize()
-    assert _device_status() == 0
-    assert torch.equal(call.result(), split)
