@@ -406,7 +406,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
     # ---- what the slot ring alone can stream: the same long table with every unit's arithmetic skipped -------
     probe_ms, probe_launches = None, 0
     if long_calls and "probe" in modes:
-        native.check(tune(b"probe", 1), "intent_b200_w4a16_gemv_table_tune")
+        native.check(tune(b"probe", args.probe_level), "intent_b200_w4a16_gemv_table_tune")
         try:
             probe_ms, probe_launches, _ = graph_time(long_step, 0.2)
         finally:
@@ -1342,6 +1342,9 @@ def main() -> int:
     parser.add_argument("--table-tune", default="",
                         help="measurement knobs of the table kernel, e.g. 'warps=16,areas=4' "
                              "(see intent_b200_w4a16_gemv_table_tune)")
+    parser.add_argument("--probe-level", type=int, default=1,
+                        help="decode 'probe' mode: 1 = arithmetic skipped, 2 = reduction skipped too, 3 = only the packed "
+                             "weights are loaded (results are wrong by design; shows where the time goes)")
     parser.add_argument("--decode-modes", default="long,probe,projection",
                         help="extra decode measurements beside the one-launch-per-step table: 'long' (eight steps "
                              "per call), 'probe' (the long table with the arithmetic skipped: the ring's streaming "

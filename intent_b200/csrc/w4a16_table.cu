@@ -10,10 +10,10 @@
 //
 // One CTA per SM.  Every problem's packed weight [K/8, N] is cut into units of 32 columns x 32 packed
 // rows (256 k, 4 KiB) and the units of a problem are split evenly over the CTAs (+-1).  A CTA owns a
-// ring of 32 shared-memory slots; unit number g of the CTA's sequence - the concatenation of its shares
-// of all problems - lands in slot g % 32 through one 128B-swizzled TMA box (plus a box of its scales)
-// on the slot's mbarrier, is consumed by warp g % WARPS, and that warp then requests unit g + 32 into
-// the same slot, whichever problem it belongs to.
+// ring of S shared-memory slots (S is chosen per launch); unit number g of the CTA's sequence - the
+// concatenation of its shares of all problems - lands in slot g % S through one 128B-swizzled TMA box
+// (plus a box of its scales) on the slot's mbarrier, is consumed by ring warp g % RING, and that warp
+// then requests unit g + S into the same slot, whichever problem it belongs to.
 //
 // Unit order inside a problem.  K is cut into chunk blocks of `cb` chunks (cb = all chunks when the
 // activations of the whole K range fit in shared memory, smaller for larger M); units are numbered
@@ -25,21 +25,25 @@
 // Reduction over K, fixed order (bitwise reproducible):
 //   1. units of one span inside one CTA: per-unit partials [M x 32] f32 in shared memory, a shared
 //      ticket per span, the warp with the last ticket adds them in chunk order;
-//   2. a span shared by neighbouring CTAs: each publishes ONE partial to global scratch and takes a
-//      ticket on the span's global counter; the last one adds the partials in CTA order;
+//   2. a span shared by neighbouring CTAs: each publishes ONE partial to global scratch; staged form:
+//      and takes a ticket on the span's global counter, the last one adds the partials in CTA order;
+//      ride-along form: the CTA that holds the span's end hands its own sum to its reducer warp, which
+//      waits for the others' and adds them in CTA order (the ring warps never wait for global memory);
 //   3. several chunk blocks: the block sums of a column tile meet the same way on the tile's counter
 //      and are added in block order.
-// Counters are left at zero for the next launch.  Partial spans at the ends of a CTA's share are
-// processed first, so their global round trips overlap the rest of the share.
+// No memory fence at GPU scope anywhere: such a fence makes the SM wait for all its loads in flight
+// (measured on a bare ring: two per 48 units cost a quarter of the stream).  Published partials carry
+// their own validity instead (publish / take_published).  Counters and scratch are left at zero for
+// the next launch.  Partial spans at the ends of a CTA's share are processed first.
 //
 // Two forms of the kernel.  STAGED (above): a CTA-wide barrier on either side of the staging of every
 // problem.  RIDE (problems of at most two rows): every unit's TMA transaction also brings the 256
 // activations per row it needs, the consuming warp derives the correction sums of its unit from them, and
 // nothing is staged - so there is no CTA-wide barrier after start-up and the warps drift apart instead of
 // re-synchronising at every problem (a ring whose slots are all requested and consumed in lock-step leaves
-// HBM idle while it computes).  Per-problem partial areas rotate through four buffers (two when four do not
-// fit); a warp writes its first partial of problem i + 4 only after every warp has left problem i (a bounded
-// wait on a shared counter that practically never has to wait).
+// HBM idle while it computes).  Per-problem partial areas rotate through two buffers; a warp writes its
+// first partial of problem i + 2 only after every ring warp has left problem i (a bounded wait on a shared
+// counter).  The last warp of the CTA is the reducer of cut spans and takes no units.
 //
 // Every mbarrier wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the
 // workspace's status word, the CTA skips its remaining units (still meeting its barriers) and exits.
@@ -55,11 +59,13 @@ namespace {
 constexpr int kCols = 32;            // columns of a unit
 constexpr int kRows = 32;            // packed rows of a unit (8 k each)
 constexpr int kWeightBytes = kCols * kRows * 4;
-constexpr int kScaleBytes = 512;     // up to 8 groups x 32 columns of 16-bit scales
-constexpr int kSlots = 32;
+constexpr int kMinSlots = 32;        // slots of the ring every plan is made for; a launch takes as many as fit
+constexpr int kMaxSlots = 64;
 constexpr int kMaxProblems = 8;
 constexpr int kMaxSpans = 64;        // spans a CTA may touch in one problem
-constexpr int kSmemLimit = 227 * 1024;
+constexpr int kMailEntries = 4;      // ride-along form: spans waiting for the reducer warp
+constexpr int kMailRows = 2;         // rows of a problem the ride-along form takes
+constexpr int kSmemLimit = 227 * 1024 - 2048;   // dynamic shared memory (the kernel's static part is below 2 KB)
 
 struct TableProblem {
   const void* x;
@@ -89,6 +95,10 @@ struct TableParams {
   // ride-along form: every unit brings its own activations (box of M x 256 values behind the scales)
   int xbox_offset, xbox_bytes, finished_offset, part_stride;
   int part_depth;     // ride-along form: partial areas the problems rotate through (2 or 4)
+  int slots;          // slots of the ring (as many as fit beside the other regions)
+  uint32_t magic_slots;
+  int uses_offset;    // per slot: how many times it has been requested (read only when slots % warps != 0)
+  int sched_offset;   // w4a16_ride_kernel: the CTA's schedule, 16 bytes per unit of its whole sequence
   int probe;          // measurement only: 1 = skip the arithmetic of every unit (stream and reduction traffic only)
 };
 
@@ -106,12 +116,44 @@ struct Share {
   int row0;          // first staged packed row (start of the first chunk block touched)
   int rows;          // staged packed rows
   int span0;         // span index (block * tiles + tile) of unit u0
+  int reads;         // ride-along form: 1 if the share ends a span that began in another CTA (the reducer adds it up)
 };
 
 struct Unit {
   int block, tile, chunk;
   int span_first, span_len;   // first unit and length of the span (tile x chunk block)
 };
+
+// Cross-CTA hand-over of a partial sum without memory fences.  Scratch words are zero while empty; a value is
+// stored as the complement of its bits, which is never zero (the one pattern that would be, the NaN 0xFFFFFFFF,
+// is stored as the canonical NaN).  The reader polls each word until it is non-zero, then clears it for the
+// next launch.  Every vector is written once and read once per launch.
+__device__ __forceinline__ uint32_t published_word(float v) {
+  const uint32_t bits = __float_as_uint(v);
+  return ~(bits == 0xFFFFFFFFu ? 0x7FFFFFFFu : bits);
+}
+
+__device__ __forceinline__ void publish(float4* dst, float4 v) {
+  asm volatile("st.global.cg.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(published_word(v.x)), "r"(published_word(v.y)),
+               "r"(published_word(v.z)), "r"(published_word(v.w))
+               : "memory");
+}
+
+// false if the vector did not arrive within the bound (about a second)
+__device__ __forceinline__ bool take_published(const float4* src, float4* out) {
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    uint32_t a, b, c, d;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(src) : "memory");
+    if (a != 0u && b != 0u && c != 0u && d != 0u) {
+      *out = make_float4(__uint_as_float(~a), __uint_as_float(~b), __uint_as_float(~c), __uint_as_float(~d));
+      asm volatile("st.global.cg.v4.u32 [%0], {%1,%1,%1,%1};" ::"l"(src), "r"(0u) : "memory");
+      return true;
+    }
+    if (spin > 16) __nanosleep(128);
+  }
+  *out = make_float4(0.f, 0.f, 0.f, 0.f);
+  return false;
+}
 
 // u / d for 0 <= u < 2^31 with magic = ceil(2^32 / d): the product can overestimate by one, never underestimate
 __device__ __forceinline__ int fast_div(int u, int d, uint32_t magic) {
@@ -164,6 +206,12 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   __shared__ Share shares[kMaxProblems];
   __shared__ int total_units;
   __shared__ int abort_flag;
+  // ride-along form: segment sums handed to the reducer warp (entry = ticket % kMailEntries)
+  __shared__ __align__(16) float mail_data[kMailEntries][kMailRows][kCols];
+  __shared__ int mail_ctx[kMailEntries][4];    // problem, span, column tile, partials published by other CTAs
+  __shared__ int mail_ready[kMailEntries];     // ticket + 1 once the entry is complete
+  __shared__ int mail_tail, mail_head;         // tickets given out / entries consumed
+  constexpr int RING = RIDE ? WARPS - 1 : WARPS;   // warps that serve the slot ring (the last warp of RIDE is the reducer)
 
   if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -172,8 +220,15 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t scale_base = base + kSlots * kWeightBytes;
-  const uint32_t bars = scale_base + kSlots * kScaleBytes;
+  constexpr int kScaleBytes = GPC * 64;   // a unit's scales: GPC groups x 32 columns x 16 bit
+  const int S = p.slots;
+  const uint32_t scale_base = base + uint32_t(S) * kWeightBytes;
+  const uint32_t bars = scale_base + uint32_t(S) * kScaleBytes;
+  volatile int* uses = reinterpret_cast<volatile int*>(base_ptr + p.uses_offset);
+  // With slots % WARPS == 0 a slot is always consumed by the same warp, in order.  Otherwise the warp that
+  // takes a slot's k-th unit first makes sure the (k-1)-th was consumed and the k-th requested: a parity wait
+  // on a barrier that is still a whole phase behind would return at once.
+  const bool shared_slots = (S % RING) != 0;
   float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
   uint4* xs = reinterpret_cast<uint4*>(base_ptr + p.xs_offset);
   const uint32_t xs_addr = base + uint32_t(p.xs_offset);
@@ -189,7 +244,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     s.u0 = cta * q.each + min(cta, q.extra);
     s.u1 = s.u0 + q.each + (cta < q.extra ? 1 : 0);
     s.head = s.tail = 0;
-    s.row0 = s.rows = s.span0 = 0;
+    s.row0 = s.rows = s.span0 = s.reads = 0;
     if (s.u1 > s.u0) {
       const Unit a = decode_unit(q, s.u0), b = decode_unit(q, s.u1 - 1);
       if (a.span_first < s.u0) s.head = min(s.u1, a.span_first + a.span_len) - s.u0;
@@ -198,10 +253,13 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       s.row0 = a.block * q.cb * kRows;
       s.rows = min(q.chunks, (b.block + 1) * q.cb) * kRows - s.row0;
       s.span0 = a.block * q.tiles + a.tile;
+      s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
     }
     shares[tid] = s;
   }
   if (tid == 0) abort_flag = 0;
+  if (tid == 0) mail_tail = mail_head = 0;
+  if (tid < kMailEntries) mail_ready[tid] = 0;
   if (RIDE) {
     for (int i = tid; i < kMaxProblems * kMaxSpans; i += THREADS) span_counts[i] = 0;
     if (tid < kMaxProblems) finished[tid] = 0;
@@ -215,7 +273,10 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     }
     total_units = first;
   }
-  if (tid < kSlots) mbar_init(bars + uint32_t(tid) * 8u, 1);
+  for (int i = tid; i < S; i += THREADS) {
+    mbar_init(bars + uint32_t(i) * 8u, 1);
+    uses[i] = 0;
+  }
   if (tid == 0) fence_mbar_init();
   __syncthreads();
   const int total = total_units;
@@ -227,8 +288,15 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     while (i + 1 < p.count && seq >= shares[i + 1].first) ++i;
     const TableProblem& q = p.problem[i];
     const Unit u = decode_unit(q, unit_at(shares[i], seq - shares[i].first));
-    const uint32_t slot = uint32_t(seq % kSlots);
+    const uint32_t slot = uint32_t(seq - fast_div(seq, S, p.magic_slots) * S);
     const uint32_t bar = bars + slot * 8u;
+    if (p.probe >= 3) {   // measurement: the packed weights alone
+      if (parts & 1) {
+        mbar_expect_tx(bar, kWeightBytes);
+        tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
+      }
+      return;
+    }
     if (parts & 1) {
       mbar_expect_tx(bar, kWeightBytes + GPC * 64 + (RIDE ? uint32_t(q.M) * 512u : 0u));
       tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
@@ -238,11 +306,71 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   };
   // First wave: slot s is owned by warp s % WARPS.  With launch overlap the packed weights (static) are requested
   // before the wait for the kernel ahead of this one; activations, which that kernel may have produced, after it.
-  if (lane == 0)
-    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0, 1);
+  if (lane == 0 && warp < RING)
+    for (int seq = warp; seq < min(total, S); seq += RING) issue(seq, 0, 1);
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (RIDE && lane == 0)
-    for (int seq = warp; seq < min(total, kSlots); seq += WARPS) issue(seq, 0, 2);
+  if (RIDE && lane == 0 && warp < RING)
+    for (int seq = warp; seq < min(total, S); seq += RING) issue(seq, 0, 2);
+
+  if (RIDE && warp == RING) {
+    // ---- the reducer warp ------------------------------------------------------------------------
+    // A span cut by a CTA boundary: every CTA but the one holding its end publishes its segment's sum to global
+    // scratch and moves on; the warp that completes the LAST segment leaves that sum here.  This warp then waits
+    // for the published sums (round trips behind a deep queue of bulk loads: microseconds), adds them in CTA
+    // order, its own last, and writes Y.  The warps that serve the ring never wait for global memory.
+    int expected = 0;
+    for (int i = 0; i < p.count; ++i) expected += shares[i].reads;
+    if (p.probe >= 2 && p.probe <= 5) expected = 0;   // measurement modes that skip the hand-over
+    const int v8r = lane & 7;
+    for (int n = 0; n < expected; ++n) {
+      const int e = n % kMailEntries;
+      bool ok = false;
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (*reinterpret_cast<volatile int*>(&mail_ready[e]) == n + 1) { ok = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(256);
+      }
+      if (!ok) {
+        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        return;
+      }
+      __threadfence_block();
+      const TableProblem& q = p.problem[mail_ctx[e][0]];
+      const int span = mail_ctx[e][1], tile = mail_ctx[e][2], published = mail_ctx[e][3];
+      const int part_floats = q.M * kCols;
+      const float* span_scratch = q.scratch1 + size_t(span) * q.maxp * part_floats;
+      uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
+      for (int m = lane >> 3; m < q.M; m += 4) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < published; ++c) {
+          float4 a;
+          if (!take_published(reinterpret_cast<const float4*>(span_scratch + size_t(c) * part_floats + m * kCols + 4 * v8r), &a)) {
+            atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // a neighbour's sum never arrived
+            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+          }
+          sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+        }
+        const float4 own = *reinterpret_cast<const float4*>(&mail_data[e][m][4 * v8r]);
+        sum.x += own.x; sum.y += own.y; sum.z += own.z; sum.w += own.w;
+        const int col = tile * kCols + 4 * v8r;
+        if (col < q.N) {
+          uint2 out;
+          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
+          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+          *reinterpret_cast<uint2*>(y + size_t(m) * q.N + col) = out;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&mail_head) = n + 1;   // the entry may be reused
+      }
+    }
+    return;
+  }
 
   uint32_t magic_a, magic_b;
   Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
@@ -312,15 +440,26 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const int group0 = sh.row0 / RPG;   // first staged group
 
     // this warp's units of the problem: sequence numbers congruent to the warp modulo WARPS
-    int j = ((warp - sh.first) % WARPS + WARPS) % WARPS;
-    for (; j < n_units; j += WARPS) {
+    int j = ((warp - sh.first) % RING + RING) % RING;
+    for (; j < n_units; j += RING) {
       if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
       const int seq = sh.first + j;
       const int unit = unit_at(sh, j);
       const Unit u = decode_unit(q, unit);
-      const uint32_t slot = uint32_t(seq % kSlots);
+      const int use = fast_div(seq, S, p.magic_slots);
+      const uint32_t slot = uint32_t(seq - use * S);
       const uint32_t bar = bars + slot * 8u;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar, uint32_t(seq / kSlots) & 1u))) {
+      bool requested = true;
+      if (shared_slots && use > 0) {
+        requested = false;
+        for (int spin = 0; spin < (1 << 20); ++spin) {
+          if (uses[slot] >= use) { requested = true; break; }
+          if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+          __nanosleep(64);
+        }
+        __threadfence_block();
+      }
+      if (!__all_sync(0xffffffffu, requested && mbar_wait(bar, uint32_t(use) & 1u))) {
         if (lane == 0) {
           atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // this unit's loads never completed
           *reinterpret_cast<volatile int*>(&abort_flag) = 1;
@@ -329,6 +468,21 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       }
       const uint32_t wslot = base + slot * kWeightBytes;
       const uint32_t sslot = scale_base + slot * kScaleBytes;
+      auto refill = [&]() {
+        if (seq + S < total) {
+          __syncwarp();
+          fence_proxy_async();
+          if (lane == 0) {
+            issue(seq + S, pi, 3);
+            if (shared_slots) {
+              __threadfence_block();
+              uses[slot] = use + 1;
+            }
+          }
+        }
+      };
+      const bool skip_math = p.probe >= 1 && p.probe <= 5;
+      if (p.probe == 6) refill();   // measurement: the slot is given up before it is read (results are garbage)
       float facc[MB][8];
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb)
@@ -338,7 +492,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       const int staged_row = u.chunk * kRows - sh.row0;   // first staged row of this unit
       const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
       float* my_corr = corr + warp * (GPC * CP);            // RIDE: this warp's correction sums of the unit
-      if (RIDE && !p.probe) {
+      if (RIDE && !skip_math) {
         // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
         // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
         // their share of the correction sum with the same fixed-order butterfly as the staged form
@@ -364,7 +518,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       // only on its own column of the activation fragment, and output columns >= M are never stored.
       const int m_lane = min(g, M - 1);
 #pragma unroll
-      for (int gi = 0; gi < (p.probe ? 0 : GPC); ++gi) {
+      for (int gi = 0; gi < (skip_math ? 0 : GPC); ++gi) {
         const int group = u.chunk * GPC + gi;
         float gacc[MB][8];
 #pragma unroll
@@ -417,19 +571,16 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         }
       }
       // the slot is free: request the unit that maps to it next, whichever problem that is
-      if (seq + kSlots < total) {
-        __syncwarp();
-        fence_proxy_async();
-        if (lane == 0) issue(seq + kSlots, pi, 3);
-      }
+      if (p.probe != 6) refill();
 
+      if (p.probe == 2 || p.probe == 3) continue;   // measurement: no reduction either
       if (RIDE && !area_checked) {
         // Before this warp's first write into the problem's partial area: every warp must have left problem
         // pi - depth, which used the same area.  Checked here, after the unit's data has arrived and been
         // multiplied, because by then it practically always holds (the wait above was the long one).
         bool ok = false;
         for (int spin = 0; spin < (1 << 20); ++spin) {
-          if (finished[pi - p.part_depth] >= WARPS) { ok = true; break; }
+          if (finished[pi - p.part_depth] >= RING) { ok = true; break; }
           if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
           __nanosleep(256);
         }
@@ -466,7 +617,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         last = atomicAdd(span_count + seg, 1) == seg_len - 1;
       }
       last = __shfl_sync(0xffffffffu, last, 0);
-      if (!last) continue;
+      if (!last || p.probe == 4) continue;
       __threadfence_block();
 
       // sum of `count` partials spaced `stride` floats apart, for row m: quarter q4 adds partials q4, q4+4, ...
@@ -481,7 +632,12 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
             a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (cc < count) {
               const float4* src = reinterpret_cast<const float4*>(first + size_t(cc) * stride + m * kCols + 4 * v8);
-              a[k] = global ? __ldcg(src) : *src;
+              if (!global) {
+                a[k] = *src;
+              } else if (!take_published(src, &a[k])) {
+                atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // a neighbour's partial never arrived
+                *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+              }
             }
           }
 #pragma unroll
@@ -507,28 +663,67 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
           *reinterpret_cast<uint2*>(y + size_t(m) * q.N + n) = out;
         }
       };
-      auto store_rows = [&](float* dst, float4 sum, int m) {
-        if (q4 == 0) *reinterpret_cast<float4*>(dst + m * kCols + 4 * v8) = sum;
+      auto store_rows = [&](float* dst, float4 sum, int m) {   // to global scratch, for another CTA's warp
+        if (q4 == 0) publish(reinterpret_cast<float4*>(dst + m * kCols + 4 * v8), sum);
       };
+      // No fence on either side of the ticket: a release or acquire at GPU scope makes the SM wait for all of
+      // its loads in flight (measured: two per 48 units cost a quarter of the stream).  The partials carry their
+      // own validity instead (publish / take_published), and the ticket only elects the warp that adds them.
       auto take_ticket = [&](int* counter, int arrivals) {   // true for the last of `arrivals`
         __syncwarp();
         int final_one = 0;
-        if (lane == 0) {
-          int old;
-          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
-          final_one = old == arrivals - 1;
-        }
+        if (lane == 0) final_one = atomicAdd(counter, 1) == arrivals - 1;
         return __shfl_sync(0xffffffffu, final_one, 0) != 0;
       };
 
       const float* seg_first = part + size_t(seg_begin - sh.u0) * part_floats;
-      const bool whole = seg_len == u.span_len;     // the whole span was added here: this is the block sum
+      const bool whole = seg_len == u.span_len || p.probe == 5;     // the whole span was added here: this is the block sum
       float* block_dst = q.nblocks > 1 ? q.scratch2 + (size_t(u.tile) * q.nblocks + u.block) * part_floats : nullptr;
       if (whole) {
         for (int m = 0; m < M; ++m) {
           const float4 sum = sum_partials(seg_first, seg_len, part_floats, false, m);
           if (block_dst) store_rows(block_dst, sum, m); else write_y(m, sum);
         }
+      } else if (RIDE) {
+        // ---- level 2, ride-along form: publish and move on, or leave the span's end to the reducer warp ----
+        const int first_cta = cta_of(q, u.span_first);
+        if (seg_end != u.span_first + u.span_len) {
+          float* slot_dst = q.scratch1 + (size_t(span) * q.maxp + (cta - first_cta)) * part_floats;
+          for (int m = 0; m < M; ++m) store_rows(slot_dst, sum_partials(seg_first, seg_len, part_floats, false, m), m);
+        } else {
+          int ticket = 0;
+          if (lane == 0) ticket = atomicAdd(&mail_tail, 1);
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          bool room = false;
+          for (int spin = 0; spin < (1 << 22); ++spin) {
+            if (ticket - *reinterpret_cast<volatile int*>(&mail_head) < kMailEntries) { room = true; break; }
+            if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+            __nanosleep(256);
+          }
+          if (!room) {
+            if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+              atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+              *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+            }
+            break;
+          }
+          __threadfence_block();
+          const int e = ticket % kMailEntries;
+          for (int m = 0; m < M; ++m) {
+            const float4 sum = sum_partials(seg_first, seg_len, part_floats, false, m);
+            if (q4 == 0) *reinterpret_cast<float4*>(&mail_data[e][m][4 * v8]) = sum;
+          }
+          __syncwarp();
+          if (lane == 0) {
+            mail_ctx[e][0] = pi;
+            mail_ctx[e][1] = span;
+            mail_ctx[e][2] = u.tile;
+            mail_ctx[e][3] = cta - first_cta;
+            __threadfence_block();
+            *reinterpret_cast<volatile int*>(&mail_ready[e]) = ticket + 1;
+          }
+        }
+        continue;
       } else {
         // ---- level 2: a span shared with neighbouring CTAs ------------------------------------
         const int first_cta = cta_of(q, u.span_first), last_cta = cta_of(q, u.span_first + u.span_len - 1);
@@ -567,6 +762,488 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------
+// The ride-along form as a kernel of its own (problems of at most two rows).
+//
+// The work is the same as in the RIDE branch of the kernel above; what differs is the bookkeeping, which is
+// what bounds this kernel (it issues about as many instructions as the SM can take while the stream runs):
+//   * at start-up every thread works out ONE unit of the CTA's whole sequence - problem, column tile, chunk,
+//     segment, partial slot, what happens when the segment is complete - and leaves it as a 16-byte entry in a
+//     schedule in shared memory; the loop reads an entry instead of dividing unit numbers again (twice per unit);
+//   * 31 ring warps own one slot each (or a whole number), so slot and phase need no division either, and a
+//     warp's refill is always its own next unit;
+//   * one loop over the warp's units of all problems.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int STEPS>
+__global__ void __launch_bounds__(1024, 1)
+w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
+  constexpr int THREADS = 1024, RING = 31;
+  constexpr int RPG = 4 * STEPS;        // packed rows per quantisation group
+  constexpr int GPC = kRows / RPG;      // groups per unit
+  constexpr int CP = 8;                 // row pitch of the correction table
+  constexpr int kScaleBytes = GPC * 64;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Share shares[kMaxProblems];
+  __shared__ int total_units;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) float mail_data[kMailEntries][kMailRows][kCols];
+  __shared__ int mail_ctx[kMailEntries][4];    // problem, span, column tile, partials published by other CTAs
+  __shared__ int mail_ready[kMailEntries];     // ticket + 1 once the entry is complete
+  __shared__ int mail_tail, mail_head;         // tickets given out / entries consumed
+  __shared__ int next_unit;                    // the next unit of the CTA's sequence nobody has taken yet
+
+  if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int cta = int(blockIdx.x);
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const int S = p.slots;
+  volatile int* uses = reinterpret_cast<volatile int*>(base_ptr + p.uses_offset);   // refills requested so far, per slot
+  const uint32_t scale_base = base + uint32_t(S) * kWeightBytes;
+  const uint32_t bars = scale_base + uint32_t(S) * kScaleBytes;
+  float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
+  int* span_counts = reinterpret_cast<int*>(base_ptr + p.span_offset);   // one row of tickets per problem
+  float* parts = reinterpret_cast<float*>(base_ptr + p.part_offset);
+  const uint32_t xbox_base = base + uint32_t(p.xbox_offset);
+  volatile int* finished = reinterpret_cast<volatile int*>(base_ptr + p.finished_offset);   // ring warps done per problem
+  uint4* sched = reinterpret_cast<uint4*>(base_ptr + p.sched_offset);
+
+  // ---- this CTA's share of every problem ---------------------------------------------------
+  if (tid < p.count) {
+    const TableProblem& q = p.problem[tid];
+    Share s;
+    s.u0 = cta * q.each + min(cta, q.extra);
+    s.u1 = s.u0 + q.each + (cta < q.extra ? 1 : 0);
+    s.head = s.tail = 0;
+    s.row0 = s.rows = s.span0 = s.reads = 0;
+    if (s.u1 > s.u0) {
+      const Unit a = decode_unit(q, s.u0), b = decode_unit(q, s.u1 - 1);
+      if (a.span_first < s.u0) s.head = min(s.u1, a.span_first + a.span_len) - s.u0;
+      if (b.span_first + b.span_len > s.u1 && b.span_first >= s.u0 + s.head) s.tail = s.u1 - max(b.span_first, s.u0);
+      if (s.head == s.u1 - s.u0) s.tail = 0;
+      s.span0 = a.tile;
+      s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
+    }
+    shares[tid] = s;
+  }
+  if (tid == 0) abort_flag = 0;
+  if (tid == 0) mail_tail = mail_head = 0;
+  if (tid == 0) next_unit = 0;
+  if (tid < kMailEntries) mail_ready[tid] = 0;
+  for (int i = tid; i < kMaxProblems * kMaxSpans; i += THREADS) span_counts[i] = 0;
+  if (tid < kMaxProblems) finished[tid] = 0;
+  for (int i = tid; i < S; i += THREADS) {
+    mbar_init(bars + uint32_t(i) * 8u, 1);
+    uses[i] = 0;
+  }
+  if (tid == 0) fence_mbar_init();
+  __syncthreads();
+  if (tid == 0) {
+    int first = 0;
+    for (int i = 0; i < p.count; ++i) {
+      shares[i].first = first;
+      first += shares[i].u1 - shares[i].u0;
+    }
+    total_units = first;
+  }
+  __syncthreads();
+  const int total = total_units;
+
+  // Schedule entry: x = tile | problem << 24 | whole << 28 | ends the span << 29 | (M - 1) << 30
+  //                 y = chunk | segment index in the share << 20
+  //                 z = units of the segment | CTAs that hold earlier parts of the span << 20
+  //                 w = partial slot of the unit | partial slot of the segment's first unit << 16
+  auto issue = [&](uint4 ent, uint32_t slot, int what) {
+    const int tile = int(ent.x & 0xFFFFFFu), i = int((ent.x >> 24) & 15u), chunk = int(ent.y & 0xFFFFFu);
+    const uint32_t rows = 1u + ((ent.x >> 30) & 1u);
+    const uint32_t bar = bars + slot * 8u;
+    if (p.probe >= 3) {   // measurement: the packed weights alone
+      if (what & 1) {
+        mbar_expect_tx(bar, kWeightBytes);
+        tma_load_2d(base + slot * kWeightBytes, &maps.w[i], tile * kCols, chunk * kRows, bar);
+      }
+      return;
+    }
+    if (what & 1) {
+      mbar_expect_tx(bar, kWeightBytes + GPC * 64 + rows * 512u);
+      tma_load_2d(base + slot * kWeightBytes, &maps.w[i], tile * kCols, chunk * kRows, bar);
+      tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], tile * kCols, chunk * GPC, bar);
+    }
+    if (what & 2) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], chunk * 256, 0, bar);
+  };
+
+  // One entry per thread (a CTA has at most kMaxProblems * units-per-share of them, below THREADS is the
+  // common case); the threads of the first S entries request them at once.  With launch overlap the packed
+  // weights (static) are requested before the wait for the kernel ahead, the activations after it.
+  uint4 mine_ent = make_uint4(0, 0, 0, 0);
+  for (int e = tid; e < total; e += THREADS) {
+    int i = 0;
+    while (i + 1 < p.count && e >= shares[i + 1].first) ++i;
+    const TableProblem& q = p.problem[i];
+    const Share& sh = shares[i];
+    const int unit = unit_at(sh, e - sh.first);
+    const Unit u = decode_unit(q, unit);
+    const int seg_begin = max(u.span_first, sh.u0), seg_end = min(u.span_first + u.span_len, sh.u1);
+    const int seg_len = seg_end - seg_begin;
+    const bool whole = seg_len == u.span_len;
+    const bool ends = seg_end == u.span_first + u.span_len;
+    const int earlier = whole ? 0 : cta - cta_of(q, u.span_first);
+    uint4 ent;
+    ent.x = uint32_t(u.tile) | (uint32_t(i) << 24) | (whole ? 1u << 28 : 0u) | (ends ? 1u << 29 : 0u) |
+            (uint32_t(q.M - 1) << 30);
+    ent.y = uint32_t(u.chunk) | (uint32_t(u.tile - sh.span0) << 20);
+    ent.z = uint32_t(seg_len) | (uint32_t(earlier) << 20);
+    ent.w = uint32_t(unit - sh.u0) | (uint32_t(seg_begin - sh.u0) << 16);
+    sched[e] = ent;
+    if (e == tid) mine_ent = ent;
+  }
+  if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 1);
+  if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 2);
+  __syncthreads();   // the schedule is complete
+
+  if (warp == RING) {
+    // ---- the reducer warp ------------------------------------------------------------------------
+    // A span cut by a CTA boundary: every CTA but the one holding its end publishes its segment's sum to global
+    // scratch and moves on; the warp that completes the LAST segment leaves that sum here.  This warp then waits
+    // for the published sums (round trips behind a deep queue of bulk loads: microseconds), adds them in CTA
+    // order, its own last, and writes Y.  The warps that serve the ring never wait for global memory.
+    int expected = 0;
+    for (int i = 0; i < p.count; ++i) expected += shares[i].reads;
+    if (p.probe >= 2 && p.probe <= 5) expected = 0;   // measurement modes that skip the hand-over
+    const int v8r = lane & 7;
+    for (int n = 0; n < expected; ++n) {
+      const int e = n % kMailEntries;
+      bool ok = false;
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (*reinterpret_cast<volatile int*>(&mail_ready[e]) == n + 1) { ok = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(512);
+      }
+      if (!ok) {
+        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        return;
+      }
+      __threadfence_block();
+      const TableProblem& q = p.problem[mail_ctx[e][0]];
+      const int span = mail_ctx[e][1], tile = mail_ctx[e][2], published = mail_ctx[e][3];
+      const int part_floats = q.M * kCols;
+      const float* span_scratch = q.scratch1 + size_t(span) * q.maxp * part_floats;
+      uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
+      for (int m = lane >> 3; m < q.M; m += 4) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < published; ++c) {
+          float4 a;
+          if (!take_published(reinterpret_cast<const float4*>(span_scratch + size_t(c) * part_floats + m * kCols + 4 * v8r), &a)) {
+            atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // a neighbour's sum never arrived
+            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+          }
+          sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+        }
+        const float4 own = *reinterpret_cast<const float4*>(&mail_data[e][m][4 * v8r]);
+        sum.x += own.x; sum.y += own.y; sum.z += own.z; sum.w += own.w;
+        const int col = tile * kCols + 4 * v8r;
+        if (col < q.N) {
+          uint2 out;
+          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
+          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+          *reinterpret_cast<uint2*>(y + size_t(m) * q.N + col) = out;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&mail_head) = n + 1;   // the entry may be reused
+      }
+    }
+    return;
+  }
+
+  // ---- the ring warps ------------------------------------------------------------------------------
+  uint32_t magic_a, magic_b;
+  Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
+  int row_of[STEPS];
+  uint32_t off_of[STEPS];
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    row_of[i] = STEPS >= 2 ? 8 * (i >> 1) + 2 * t + (i & 1) : t;
+    off_of[i] = uint32_t(row_of[i]) * 128u + (uint32_t(g ^ (row_of[i] & 7)) << 4);
+  }
+  const int q4 = lane >> 3, v8 = lane & 7;   // reduction lanes: quarter q4 takes partials q4, q4+4, ...; columns 4*v8..+3
+  float* my_corr = corr + warp * (GPC * CP);  // this warp's correction sums of the unit in hand
+  const bool skip_math = p.probe >= 1 && p.probe <= 5;
+
+  // a ring warp has left problems [from, to): their partial areas may be reused two problems later
+  auto leave = [&](int from, int to) {
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      for (int k = max(from, 0); k < to; ++k) atomicAdd(const_cast<int*>(&finished[k]), 1);
+    }
+  };
+
+  // Units are taken in sequence order by whichever ring warp is free (a ticket per unit): the warps' cycles vary
+  // by tens of percent, and with a fixed unit-to-warp map the CTA ends with its unluckiest warp while the others
+  // have long been idle.  Unit number u lives in slot u % S; the warp that takes it first makes sure that the
+  // slot's previous unit was consumed and this one requested (almost always so: units arrive in order), because
+  // a parity wait on a barrier that is still a whole phase behind would return at once.
+  int cur = -1, M = 1, part_floats = kCols;
+  float* part = parts;
+  int* span_count = span_counts;
+  bool area_checked = true;
+  for (;;) {
+    if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+    int seq = 0;
+    if (lane == 0) seq = atomicAdd(&next_unit, 1);
+    seq = __shfl_sync(0xffffffffu, seq, 0);
+    if (seq >= total) break;
+    const uint4 now = sched[seq];
+    const int use = fast_div(seq, S, p.magic_slots);
+    const uint32_t slot = uint32_t(seq - use * S);
+    const int pi = int((now.x >> 24) & 15u);
+    if (pi != cur) {
+      leave(cur, pi);
+      cur = pi;
+      M = int((now.x >> 30) & 1u) + 1;
+      part_floats = M * kCols;
+      part = parts + size_t(pi % p.part_depth) * p.part_stride;
+      span_count = span_counts + pi * kMaxSpans;
+      area_checked = pi < p.part_depth;   // this partial area was last used by problem pi - depth
+    }
+    const uint32_t bar = bars + slot * 8u;
+    bool requested = true;
+    if (use > 0 && uses[slot] < use) {
+      requested = false;
+      for (int spin = 0; spin < (1 << 20); ++spin) {
+        if (uses[slot] >= use) { requested = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(64);
+      }
+    }
+    __threadfence_block();
+    if (!__all_sync(0xffffffffu, requested && mbar_wait(bar, uint32_t(use) & 1u))) {
+      if (lane == 0) {
+        atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // this unit's loads never completed
+        *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+      }
+      break;
+    }
+    const uint32_t wslot = base + slot * kWeightBytes;
+    const uint32_t sslot = scale_base + slot * kScaleBytes;
+    const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
+    float facc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) facc[i] = 0.f;
+
+    if (!skip_math) {
+      // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
+      // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
+      // their share of the correction sum  - sum_k x[m,k] * (bias_k + 8)  with a fixed-order butterfly
+      for (int m = 0; m < M; ++m) {
+        const uint32_t addr = xslot + uint32_t(m) * 512u + uint32_t(lane) * 16u;
+        const uint4 val = lds128(addr);
+        uint4 o;
+        o.x = prmt(val.x, val.z, 0x5410);                        // (k0, k4)
+        o.y = Expand<T>::scale_odd(prmt(val.x, val.z, 0x7632));  // (k1, k5)
+        o.z = prmt(val.y, val.w, 0x5410);                        // (k2, k6)
+        o.w = Expand<T>::scale_odd(prmt(val.y, val.w, 0x7632));  // (k3, k7)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                     : "memory");
+        float partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
+                        Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
+#pragma unroll
+        for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+        if ((lane % RPG) == 0) my_corr[(lane / RPG) * CP + m] = -partial;
+      }
+      __syncwarp();
+      // Rows of X beyond M: the lanes that would hold them read row M - 1 instead.  An MMA output column depends
+      // only on its own column of the activation fragment, and output columns >= M are never stored.
+      const uint32_t xrow = xslot + uint32_t(min(g, M - 1)) * 512u;
+#pragma unroll
+      for (int gi = 0; gi < GPC; ++gi) {
+        float gacc[8];
+        {
+          const float2 c = *reinterpret_cast<const float2*>(&my_corr[gi * CP + 2 * t]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gacc[i] = (i & 1) ? c.y : c.x;
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+          const int row = gi * RPG + row_of[i];
+          const uint32_t off = STEPS >= 2 ? off_of[i] + uint32_t(gi * RPG * 128)
+                                          : uint32_t(row) * 128u + (uint32_t(g ^ (row & 7)) << 4);
+          const uint4 w = lds128(wslot + off);
+          const uint4 b = lds128(xrow + uint32_t(row) * 16u);
+          uint32_t c0[4], c1[4], c2[4], c3[4];
+          Expand<T>::word(w.x, magic_a, magic_b, c0);
+          Expand<T>::word(w.y, magic_a, magic_b, c1);
+          Expand<T>::word(w.z, magic_a, magic_b, c2);
+          Expand<T>::word(w.w, magic_a, magic_b, c3);
+          float(&a01)[4] = *reinterpret_cast<float(*)[4]>(&gacc[0]);
+          float(&a23)[4] = *reinterpret_cast<float(*)[4]>(&gacc[4]);
+          Elem<T>::mma16816(a01, c0[0], c1[0], c0[1], c1[1], b.x, b.y);
+          Elem<T>::mma16816(a23, c2[0], c3[0], c2[1], c3[1], b.x, b.y);
+          Elem<T>::mma16816(a01, c0[2], c1[2], c0[3], c1[3], b.z, b.w);
+          Elem<T>::mma16816(a23, c2[2], c3[2], c2[3], c3[3], b.z, b.w);
+        }
+        uint2 s;  // this lane's four column scales of the group (zero outside the matrix)
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(s.x), "=r"(s.y) : "r"(sslot + gi * 64 + g * 8));
+        const float s0 = Elem<T>::to_float(uint16_t(s.x & 0xFFFF)), s1 = Elem<T>::to_float(uint16_t(s.x >> 16));
+        const float s2 = Elem<T>::to_float(uint16_t(s.y & 0xFFFF)), s3 = Elem<T>::to_float(uint16_t(s.y >> 16));
+        facc[0] = fmaf(gacc[0], s0, facc[0]);
+        facc[1] = fmaf(gacc[1], s0, facc[1]);
+        facc[2] = fmaf(gacc[2], s1, facc[2]);
+        facc[3] = fmaf(gacc[3], s1, facc[3]);
+        facc[4] = fmaf(gacc[4], s2, facc[4]);
+        facc[5] = fmaf(gacc[5], s2, facc[5]);
+        facc[6] = fmaf(gacc[6], s3, facc[6]);
+        facc[7] = fmaf(gacc[7], s3, facc[7]);
+      }
+    }
+
+    // the slot is free: the unit S places further on goes into it
+    if (seq + S < total) {
+      __syncwarp();
+      fence_proxy_async();
+      if (lane == 0) {
+        issue(sched[seq + S], slot, 3);
+        __threadfence_block();
+        uses[slot] = use + 1;
+      }
+    }
+    if (p.probe == 2 || p.probe == 3) continue;   // measurement: no reduction either
+
+    if (!area_checked) {
+      // Before this warp's first write into the problem's partial area: every ring warp must have left problem
+      // pi - depth, which used the same area.
+      bool ok = false;
+      for (int spin = 0; spin < (1 << 20); ++spin) {
+        if (finished[pi - p.part_depth] >= RING) { ok = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(256);
+      }
+      __threadfence_block();
+      if (!ok) {
+        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        break;
+      }
+      area_checked = true;
+    }
+    // ---- level 1: the unit's partial joins its segment's partials in shared memory ----------------
+    // accumulator element i: row m = 2t + (i & 1), column 4g + (i >> 1)
+    const int tile = int(now.x & 0xFFFFFFu);
+    const int seg = int((now.y >> 20) & 63u), seg_len = int(now.z & 0xFFFFFu);
+    float* mine = part + size_t(now.w & 0xFFFFu) * part_floats;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int m = 2 * t + hh;
+      if (m < M)
+        *reinterpret_cast<float4*>(mine + m * kCols + 4 * g) = make_float4(facc[0 + hh], facc[2 + hh], facc[4 + hh], facc[6 + hh]);
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(span_count + seg, 1) == seg_len - 1;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last || p.probe == 4) continue;
+    __threadfence_block();
+
+    // the segment's partials for row m, in unit order: quarter q4 adds partials q4, q4 + 4, ... (four loads in
+    // flight), then the quarters are added in a fixed order
+    const float* seg_first = part + size_t(now.w >> 16) * part_floats;
+    auto segment_sum = [&](int m) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = q4; c < seg_len; c += 16) {
+        float4 a[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int cc = c + 4 * k;
+          a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cc < seg_len) a[k] = *reinterpret_cast<const float4*>(seg_first + size_t(cc) * part_floats + m * kCols + 4 * v8);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          sum.x += a[k].x; sum.y += a[k].y; sum.z += a[k].z; sum.w += a[k].w;
+        }
+      }
+#pragma unroll
+      for (int d = 16; d >= 8; d >>= 1) {
+        sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
+        sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
+        sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
+        sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+      }
+      return sum;
+    };
+    const TableProblem& q = p.problem[pi];
+    const bool whole = ((now.x >> 28) & 1u) != 0 || p.probe == 5;
+    const int col = tile * kCols + 4 * v8;
+    if (whole) {
+      uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
+      for (int m = 0; m < M; ++m) {
+        const float4 sum = segment_sum(m);
+        if (q4 == 0 && col < q.N) {   // N is a multiple of 8, so the four columns are inside together
+          uint2 out;
+          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
+          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+          *reinterpret_cast<uint2*>(y + size_t(m) * q.N + col) = out;
+        }
+      }
+    } else if (((now.x >> 29) & 1u) == 0) {
+      // the span goes on in the next CTA: publish this segment's sum and move on
+      float* dst = q.scratch1 + (size_t(tile) * q.maxp + (now.z >> 20)) * part_floats;
+      for (int m = 0; m < M; ++m) {
+        const float4 sum = segment_sum(m);
+        if (q4 == 0) publish(reinterpret_cast<float4*>(dst + m * kCols + 4 * v8), sum);
+      }
+    } else {
+      // the span ends here: its sum goes to the reducer warp
+      int ticket = 0;
+      if (lane == 0) ticket = atomicAdd(&mail_tail, 1);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      bool room = false;
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (ticket - *reinterpret_cast<volatile int*>(&mail_head) < kMailEntries) { room = true; break; }
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+        __nanosleep(256);
+      }
+      if (!room) {
+        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
+        break;
+      }
+      __threadfence_block();
+      const int e = ticket % kMailEntries;
+      for (int m = 0; m < M; ++m) {
+        const float4 sum = segment_sum(m);
+        if (q4 == 0) *reinterpret_cast<float4*>(&mail_data[e][m][4 * v8]) = sum;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mail_ctx[e][0] = pi;
+        mail_ctx[e][1] = tile;      // one chunk block: the span is the column tile
+        mail_ctx[e][2] = tile;
+        mail_ctx[e][3] = int(now.z >> 20);
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&mail_ready[e]) = ticket + 1;
+      }
+    }
+  }
+  leave(cur, p.count);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct HostProblem {
@@ -584,9 +1261,12 @@ struct ProblemPlan {
   size_t counters1, counters2, scratch1, scratch2, bytes;   // workspace layout (offsets) and size
 };
 
-constexpr size_t kRingBytes = size_t(kSlots) * (kWeightBytes + kScaleBytes + 8);
-// alignment slack + ring + span tickets (one row per problem) + finished counters + rounding of the regions
-constexpr size_t kFixedBytes = 1024 + kRingBytes + 128 + kMaxProblems * kMaxSpans * 4 + 64 + 64;
+// One slot of the ring: the packed weights, the unit's scales, the mbarrier and the use count.
+size_t slot_bytes(int group_size) { return size_t(kWeightBytes) + size_t(256 / group_size) * 64 + 8 + 4; }
+// alignment slack + smallest ring + span tickets (one row per problem) + finished counters + rounding of the regions
+size_t fixed_bytes(int group_size) {
+  return 1024 + size_t(kMinSlots) * slot_bytes(group_size) + 256 + kMaxProblems * kMaxSpans * 4 + 64 + 128;
+}
 constexpr size_t kRideCorrBytes = 32 * 8 * 16 * 4;   // per-warp correction sums, widest case
 
 // Spans a CTA may touch and rows it must stage, worst case over CTAs, for a chunk-block size.
@@ -602,7 +1282,7 @@ void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched,
 
 bool plan_problem(int M, int K, int N, int group_size, int grid, ProblemPlan* out) {
   ProblemPlan q{};
-  const size_t smem_budget = size_t(kSmemLimit) - kFixedBytes;
+  const size_t smem_budget = size_t(kSmemLimit) - fixed_bytes(group_size);
   q.tiles = (N + kCols - 1) / kCols;
   q.chunks = (K / 8 + kRows - 1) / kRows;
   if ((long long)q.tiles * q.chunks > (1ll << 30)) return false;   // unit numbers are 32-bit
@@ -618,7 +1298,7 @@ bool plan_problem(int M, int K, int N, int group_size, int grid, ProblemPlan* ou
     int blocks, spans;
     share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
     q.ride = M <= 2 && spans <= kMaxSpans &&
-             size_t(kSlots) * M * 512 + kRideCorrBytes + 2 * q.part_bytes <= smem_budget;
+             size_t(kMinSlots) * M * 512 + kRideCorrBytes + 2 * q.part_bytes <= smem_budget;
   }
   if (q.ride) {
     q.xs_bytes = 0;
@@ -680,7 +1360,9 @@ int validate(const HostProblem& h, int group_size) {
 
 int g_table_warps = 0;     // ride-along form: 16 or 32 warps per CTA (0 = built-in choice); for measurement
 int g_table_probe = 0;
-int g_table_depth = 0;     // ride-along form: partial areas (2 or 4; 0 = as many as fit); for measurement
+int g_table_depth = 0;     // ride-along form: partial areas (4 = four when they fit; otherwise two); for measurement
+int g_table_slots = 0;     // upper limit on the ring's slots (0 = as many as fit); for measurement
+int g_table_lean = 1;      // ride-along problems run w4a16_ride_kernel (0 = the RIDE form of w4a16_table_kernel); for measurement
 
 template <typename T, int MB, int STEPS, bool RIDE, int WARPS>
 int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream);
@@ -716,6 +1398,30 @@ int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, si
   return launch_status();
 }
 
+template <typename T, int STEPS>
+int launch_ride(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
+  auto kernel = w4a16_ride_kernel<T, STEPS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (e != cudaSuccess) return cuda_status(e);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid, 1, 1);
+  config.blockDim = dim3(1024, 1, 1);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = p.overlap ? 1 : 0;
+  if (LaunchFacts* sink = observe_sink())
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "w4a16_ride_kernel activations ride with the units",
+                         grid, 1024, int(smem), 1);
+  e = cudaLaunchKernelEx(&config, kernel, maps, p);
+  if (e != cudaSuccess) return cuda_status(e);
+  note_launch();
+  return launch_status();
+}
+
 // Lays out the workspace of a whole table: a 256-byte header (status word), then every problem's part.
 int64_t table_workspace(const HostProblem* problems, int count, int group_size, int grid, ProblemPlan* plans,
                         size_t* offsets) {
@@ -737,7 +1443,7 @@ int64_t table_workspace(const HostProblem* problems, int count, int group_size, 
         const size_t rows = size_t(plans[i].chunks) * kRows;
         plans[i].xs_bytes = rows * size_t(h.M) * 16;
         plans[i].corr_bytes = (rows / (group_size / 8) + 1) * 16 * 4;
-        if (plans[i].xs_bytes + plans[i].corr_bytes + plans[i].part_bytes > size_t(kSmemLimit) - kFixedBytes) return -1;
+        if (plans[i].xs_bytes + plans[i].corr_bytes + plans[i].part_bytes > size_t(kSmemLimit) - fixed_bytes(group_size)) return -1;
       }
       offsets[i] = offset;
       offset += plans[i].bytes;
@@ -779,7 +1485,7 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   // Problems that share a launch share the space behind the slot ring, each region sized for the largest of
   // them: a launch takes as many problems (at most kMaxProblems) of one form as fit together.  The problems are
   // independent, so they may run in any order: the ride-along ones first, then the staged ones.
-  const size_t behind_ring = size_t(kSmemLimit) - kFixedBytes;
+  const size_t behind_ring = size_t(kSmemLimit) - fixed_bytes(group_size);
   int* order = new int[count];
   struct OrderCleanup {
     int* a;
@@ -794,7 +1500,7 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   for (int begin = 0; begin < count;) {
     TableMaps maps;
     TableParams p{};
-    size_t xs_max = 0, corr_max = 0, part_max = 0;
+    size_t xs_max = 0, corr_max = 0, part_max = 0, sequence = 0;
     int n = 0, mb = 1, i = begin, rows_max = 0;
     bool ride = false;
     for (; i < count && n < kMaxProblems; ++i) {
@@ -809,7 +1515,8 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
         const size_t corr_b = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
         const size_t part_b = q.part_bytes > part_max ? q.part_bytes : part_max;
         const int rows = int(h.M) > rows_max ? int(h.M) : rows_max;
-        const size_t together = ride ? size_t(kSlots) * rows * 512 + corr_b + 2 * part_b : xs + corr_b + part_b;
+        const size_t together =
+            ride ? size_t(kMinSlots) * rows * 512 + corr_b + 2 * part_b + (sequence + q.each + 1) * 16 : xs + corr_b + part_b;
         if (n > 0 && together > behind_ring) break;
       }
       TableProblem& d = p.problem[n];
@@ -848,6 +1555,7 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
                                       uint32_t(h.M), 256, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INTENT_B200_ERR_UNSUPPORTED;
       if (int(h.M) > rows_max) rows_max = int(h.M);
+      sequence += size_t(q.each) + (q.extra ? 1 : 0);
       xs_max = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
       corr_max = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
       part_max = q.part_bytes > part_max ? q.part_bytes : part_max;
@@ -867,10 +1575,36 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     p.twos_complement = zero_point == -1 ? 1 : 0;
     p.overlap = g_table_overlap;
     p.status = reinterpret_cast<int*>(ws);
-    size_t offset = (kRingBytes + 127) & ~size_t(127);
-    p.xbox_offset = int(offset);
+    // As many slots as fit beside this launch's other regions: the ring's depth is what bounds the stream.
+    const auto round16 = [](size_t v) { return (v + 15) & ~size_t(15); };
     p.xbox_bytes = ride ? rows_max * 512 : 0;
-    offset += size_t(kSlots) * p.xbox_bytes;
+    p.part_depth = 2;   // measured: two partial areas are faster than four (the warps stay closer together)
+    if (ride && g_table_depth >= 4 &&
+        fixed_bytes(group_size) + size_t(kMinSlots) * p.xbox_bytes + round16(corr_max) +
+                size_t(g_table_depth) * round16(part_max) <= size_t(kSmemLimit))
+      p.part_depth = g_table_depth;
+    {
+      const size_t others = 1024 + 256 + size_t(ride ? kMaxProblems : 1) * kMaxSpans * 4 + 64 + 128 + round16(corr_max) +
+                            round16(xs_max) + round16(part_max) * (ride ? p.part_depth : 1) + (ride ? sequence * 16 : 0);
+      if (others >= size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;
+      size_t slots = (size_t(kSmemLimit) - others) / (slot_bytes(group_size) + p.xbox_bytes);
+      if (slots > size_t(kMaxSlots)) slots = kMaxSlots;
+      if (g_table_slots > 0 && slots > size_t(g_table_slots)) slots = g_table_slots;
+      // a whole number of slots per ring warp (w4a16_table_kernel: every slot then always belongs to the same
+      // warp, and no warp has to check who used a slot before it); measured: a deeper ring does not stream faster
+      const size_t ring = ride ? size_t(g_table_lean ? 31 : (g_table_warps == 16 ? 15 : 31)) : size_t(mb == 1 ? 32 : 16);
+      if (g_table_slots == 0 && slots >= ring) slots = slots / ring * ring;
+      if (slots < 8) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned for kMinSlots
+      p.slots = int(slots);
+      p.magic_slots = uint32_t(((1ll << 32) + p.slots - 1) / p.slots);
+    }
+    size_t offset = size_t(p.slots) * (slot_bytes(group_size) - 4);
+    offset = (offset + 15) & ~size_t(15);
+    p.uses_offset = int(offset);
+    offset += size_t(p.slots) * 4;
+    offset = (offset + 127) & ~size_t(127);
+    p.xbox_offset = int(offset);
+    offset += size_t(p.slots) * p.xbox_bytes;
     p.span_offset = int(offset);
     offset += size_t(ride ? kMaxProblems : 1) * kMaxSpans * 4;
     p.finished_offset = int(offset);
@@ -881,11 +1615,10 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     offset += (xs_max + 15) & ~size_t(15);
     p.part_offset = int(offset);
     p.part_stride = int(((part_max + 15) & ~size_t(15)) / 4);      // in floats
-    // four areas when they fit (a warp then practically never waits for the slowest warp of an older problem)
-    p.part_depth = ride && 1024 + offset + ((part_max + 15) & ~size_t(15)) * 4 <= size_t(kSmemLimit) ? 4 : 2;
     p.probe = g_table_probe;
-    if (g_table_depth != 4) p.part_depth = 2;   // measured: two areas are faster than four (the warps stay closer together)
     offset += ((part_max + 15) & ~size_t(15)) * (ride ? p.part_depth : 1);
+    p.sched_offset = int(offset);
+    if (ride) offset += sequence * 16;
     const size_t smem = 1024 + offset;
     if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned to fit
     int status;
@@ -893,7 +1626,11 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   status = steps == 4   ? launch_table<T, MB_, 4, RIDE_>(maps, p, grid, smem, stream)           \
            : steps == 2 ? launch_table<T, MB_, 2, RIDE_>(maps, p, grid, smem, stream)           \
                         : launch_table<T, MB_, 1, RIDE_>(maps, p, grid, smem, stream);
-    if (ride) {
+    if (ride && g_table_lean) {
+      status = steps == 4   ? launch_ride<T, 4>(maps, p, grid, smem, stream)
+               : steps == 2 ? launch_ride<T, 2>(maps, p, grid, smem, stream)
+                            : launch_ride<T, 1>(maps, p, grid, smem, stream);
+    } else if (ride) {
       IB200_TABLE_STEPS(1, true)        // the ride-along form is only planned for M <= 2
     } else if (mb == 1) {
       IB200_TABLE_STEPS(1, false)
@@ -964,11 +1701,19 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
     ib200::g_table_warps = value;
     return INTENT_B200_OK;
   }
-  if (is("areas") && (value == 0 || value == 2 || value == 4)) {
+  if (is("areas") && (value == 0 || value == 2 || value == 4 || value == 8)) {
     ib200::g_table_depth = value;
     return INTENT_B200_OK;
   }
-  if (is("probe") && (value == 0 || value == 1)) {
+  if (is("lean") && (value == 0 || value == 1)) {
+    ib200::g_table_lean = value;
+    return INTENT_B200_OK;
+  }
+  if (is("slots") && (value == 0 || (value >= 8 && value <= 64))) {
+    ib200::g_table_slots = value;
+    return INTENT_B200_OK;
+  }
+  if (is("probe") && value >= 0 && value <= 6) {
     ib200::g_table_probe = value;
     return INTENT_B200_OK;
   }
