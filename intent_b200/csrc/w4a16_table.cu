@@ -64,8 +64,7 @@ constexpr int kMaxSlots = 64;
 constexpr int kMaxProblems = 8;
 constexpr int kMaxSpans = 64;        // spans a CTA may touch in one problem
 constexpr int kMailEntries = 4;      // ride-along form: spans waiting for the reducer warp
-constexpr int kMailRows = 2;         // rows of a problem the ride-along form takes
-constexpr int kSmemLimit = 227 * 1024 - 2048;   // dynamic shared memory (the kernel's static part is below 2 KB)
+constexpr int kSmemLimit = 227 * 1024 - 5120;   // dynamic shared memory (the kernels' static part is below 5 KB)
 
 struct TableProblem {
   const void* x;
@@ -99,6 +98,8 @@ struct TableParams {
   uint32_t magic_slots;
   int uses_offset;    // per slot: how many times it has been requested (read only when slots % warps != 0)
   int sched_offset;   // w4a16_ride_kernel: the CTA's schedule, 16 bytes per unit of its whole sequence
+  int chains, chain_shift;   // w4a16_ride_kernel: chains per segment (a power of two) and its logarithm
+  int acc_ring_shift;        // w4a16_ride_kernel: log2 of the number of segments whose chains exist at a time
   int probe;          // measurement only: 1 = skip the arithmetic of every unit (stream and reduction traffic only)
 };
 
@@ -195,7 +196,7 @@ __device__ __forceinline__ int unit_at(const Share& s, int j) {
   return s.u0 + s.head + (j - s.tail - s.head);
 }
 
-template <typename T, int MB, int STEPS, int WARPS, bool RIDE>
+template <typename T, int MB, int STEPS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
   constexpr int THREADS = WARPS * 32;
@@ -206,12 +207,6 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   __shared__ Share shares[kMaxProblems];
   __shared__ int total_units;
   __shared__ int abort_flag;
-  // ride-along form: segment sums handed to the reducer warp (entry = ticket % kMailEntries)
-  __shared__ __align__(16) float mail_data[kMailEntries][kMailRows][kCols];
-  __shared__ int mail_ctx[kMailEntries][4];    // problem, span, column tile, partials published by other CTAs
-  __shared__ int mail_ready[kMailEntries];     // ticket + 1 once the entry is complete
-  __shared__ int mail_tail, mail_head;         // tickets given out / entries consumed
-  constexpr int RING = RIDE ? WARPS - 1 : WARPS;   // warps that serve the slot ring (the last warp of RIDE is the reducer)
 
   if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -228,14 +223,12 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   // With slots % WARPS == 0 a slot is always consumed by the same warp, in order.  Otherwise the warp that
   // takes a slot's k-th unit first makes sure the (k-1)-th was consumed and the k-th requested: a parity wait
   // on a barrier that is still a whole phase behind would return at once.
-  const bool shared_slots = (S % RING) != 0;
+  const bool shared_slots = (S % WARPS) != 0;
   float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
   uint4* xs = reinterpret_cast<uint4*>(base_ptr + p.xs_offset);
   const uint32_t xs_addr = base + uint32_t(p.xs_offset);
-  int* span_counts = reinterpret_cast<int*>(base_ptr + p.span_offset);   // RIDE: one row of tickets per problem
-  float* parts = reinterpret_cast<float*>(base_ptr + p.part_offset);
-  const uint32_t xbox_base = base + uint32_t(p.xbox_offset);
-  volatile int* finished = reinterpret_cast<volatile int*>(base_ptr + p.finished_offset);   // RIDE: warps done per problem
+  int* span_count = reinterpret_cast<int*>(base_ptr + p.span_offset);   // tickets of the spans this CTA touches
+  float* part = reinterpret_cast<float*>(base_ptr + p.part_offset);      // per-unit partial sums of the problem in hand
 
   // ---- this CTA's share of every problem ---------------------------------------------------
   if (tid < p.count) {
@@ -253,17 +246,10 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
       s.row0 = a.block * q.cb * kRows;
       s.rows = min(q.chunks, (b.block + 1) * q.cb) * kRows - s.row0;
       s.span0 = a.block * q.tiles + a.tile;
-      s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
     }
     shares[tid] = s;
   }
   if (tid == 0) abort_flag = 0;
-  if (tid == 0) mail_tail = mail_head = 0;
-  if (tid < kMailEntries) mail_ready[tid] = 0;
-  if (RIDE) {
-    for (int i = tid; i < kMaxProblems * kMaxSpans; i += THREADS) span_counts[i] = 0;
-    if (tid < kMaxProblems) finished[tid] = 0;
-  }
   __syncthreads();
   if (tid == 0) {
     int first = 0;
@@ -281,9 +267,8 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
   __syncthreads();
   const int total = total_units;
 
-  // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).  `parts`: 1 = packed
-  // weights and scales (and the barrier's byte count for everything), 2 = the activations that ride along, 3 = both.
-  auto issue = [&](int seq, int hint, int parts) {
+  // Requests unit number `seq` of the CTA's sequence into its slot (one lane calls this).
+  auto issue = [&](int seq, int hint) {
     int i = hint;                        // the sequence only moves forward: start at the caller's problem
     while (i + 1 < p.count && seq >= shares[i + 1].first) ++i;
     const TableProblem& q = p.problem[i];
@@ -291,86 +276,19 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const uint32_t slot = uint32_t(seq - fast_div(seq, S, p.magic_slots) * S);
     const uint32_t bar = bars + slot * 8u;
     if (p.probe >= 3) {   // measurement: the packed weights alone
-      if (parts & 1) {
-        mbar_expect_tx(bar, kWeightBytes);
-        tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
-      }
+      mbar_expect_tx(bar, kWeightBytes);
+      tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
       return;
     }
-    if (parts & 1) {
-      mbar_expect_tx(bar, kWeightBytes + GPC * 64 + (RIDE ? uint32_t(q.M) * 512u : 0u));
-      tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
-      tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
-    }
-    if (RIDE && (parts & 2)) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], u.chunk * 256, 0, bar);
+    mbar_expect_tx(bar, kWeightBytes + GPC * 64);
+    tma_load_2d(base + slot * kWeightBytes, &maps.w[i], u.tile * kCols, u.chunk * kRows, bar);
+    tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], u.tile * kCols, u.chunk * GPC, bar);
   };
   // First wave: slot s is owned by warp s % WARPS.  With launch overlap the packed weights (static) are requested
   // before the wait for the kernel ahead of this one; activations, which that kernel may have produced, after it.
-  if (lane == 0 && warp < RING)
-    for (int seq = warp; seq < min(total, S); seq += RING) issue(seq, 0, 1);
+  if (lane == 0)
+    for (int seq = warp; seq < min(total, S); seq += WARPS) issue(seq, 0);
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (RIDE && lane == 0 && warp < RING)
-    for (int seq = warp; seq < min(total, S); seq += RING) issue(seq, 0, 2);
-
-  if (RIDE && warp == RING) {
-    // ---- the reducer warp ------------------------------------------------------------------------
-    // A span cut by a CTA boundary: every CTA but the one holding its end publishes its segment's sum to global
-    // scratch and moves on; the warp that completes the LAST segment leaves that sum here.  This warp then waits
-    // for the published sums (round trips behind a deep queue of bulk loads: microseconds), adds them in CTA
-    // order, its own last, and writes Y.  The warps that serve the ring never wait for global memory.
-    int expected = 0;
-    for (int i = 0; i < p.count; ++i) expected += shares[i].reads;
-    if (p.probe >= 2 && p.probe <= 5) expected = 0;   // measurement modes that skip the hand-over
-    const int v8r = lane & 7;
-    for (int n = 0; n < expected; ++n) {
-      const int e = n % kMailEntries;
-      bool ok = false;
-      for (int spin = 0; spin < (1 << 22); ++spin) {
-        if (*reinterpret_cast<volatile int*>(&mail_ready[e]) == n + 1) { ok = true; break; }
-        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
-        __nanosleep(256);
-      }
-      if (!ok) {
-        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
-          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
-          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-        }
-        return;
-      }
-      __threadfence_block();
-      const TableProblem& q = p.problem[mail_ctx[e][0]];
-      const int span = mail_ctx[e][1], tile = mail_ctx[e][2], published = mail_ctx[e][3];
-      const int part_floats = q.M * kCols;
-      const float* span_scratch = q.scratch1 + size_t(span) * q.maxp * part_floats;
-      uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
-      for (int m = lane >> 3; m < q.M; m += 4) {
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = 0; c < published; ++c) {
-          float4 a;
-          if (!take_published(reinterpret_cast<const float4*>(span_scratch + size_t(c) * part_floats + m * kCols + 4 * v8r), &a)) {
-            atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);   // a neighbour's sum never arrived
-            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-          }
-          sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
-        }
-        const float4 own = *reinterpret_cast<const float4*>(&mail_data[e][m][4 * v8r]);
-        sum.x += own.x; sum.y += own.y; sum.z += own.z; sum.w += own.w;
-        const int col = tile * kCols + 4 * v8r;
-        if (col < q.N) {
-          uint2 out;
-          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
-          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
-          *reinterpret_cast<uint2*>(y + size_t(m) * q.N + col) = out;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        *reinterpret_cast<volatile int*>(&mail_head) = n + 1;   // the entry may be reused
-      }
-    }
-    return;
-  }
 
   uint32_t magic_a, magic_b;
   Expand<T>::magic(p.twos_complement != 0, magic_a, magic_b);
@@ -390,58 +308,53 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
     const int M = q.M;
     const int part_floats = M * kCols;
 
-    int* span_count = RIDE ? span_counts + pi * kMaxSpans : span_counts;
-    float* part = RIDE ? parts + size_t(pi % p.part_depth) * p.part_stride : parts;
-    bool area_checked = !RIDE || pi < p.part_depth;   // RIDE: this partial area was last used by problem pi - depth
     // ---- stage this problem's activations and correction sums -------------------------------
     // corr[group][m] = - sum over the group's k of x[m,k] * (bias_k + 8); rows of one group sit in RPG
     // adjacent lanes and are added by a fixed-order butterfly.
-    if (!RIDE) {
-      const uint4* xg = reinterpret_cast<const uint4*>(q.x);
-      const int k8 = q.K >> 3;
-      const int items = sh.rows * M;
-      constexpr int BATCH = 4;
-      for (int start = 0; start < items; start += THREADS * BATCH) {
-        uint4 val[BATCH];
-        int ms[BATCH], lr[BATCH];
-        bool in_range[BATCH], real[BATCH];
+    const uint4* xg = reinterpret_cast<const uint4*>(q.x);
+    const int k8 = q.K >> 3;
+    const int items = sh.rows * M;
+    constexpr int BATCH = 4;
+    for (int start = 0; start < items; start += THREADS * BATCH) {
+      uint4 val[BATCH];
+      int ms[BATCH], lr[BATCH];
+      bool in_range[BATCH], real[BATCH];
 #pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-          const int i = start + b * THREADS + tid;
-          in_range[b] = i < items;
-          ms[b] = in_range[b] ? i / sh.rows : 0;
-          lr[b] = in_range[b] ? i - ms[b] * sh.rows : 0;
-          real[b] = in_range[b] && sh.row0 + lr[b] < k8;
-          val[b] = real[b] ? xg[size_t(ms[b]) * k8 + sh.row0 + lr[b]] : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-          float partial = 0.f;
-          uint4 o = make_uint4(0, 0, 0, 0);   // rows past K/8 (last chunk) are staged as zeros
-          if (real[b]) {
-            o.x = prmt(val[b].x, val[b].z, 0x5410);                        // (k0, k4)
-            o.y = Expand<T>::scale_odd(prmt(val[b].x, val[b].z, 0x7632));  // (k1, k5)
-            o.z = prmt(val[b].y, val[b].w, 0x5410);                        // (k2, k6)
-            o.w = Expand<T>::scale_odd(prmt(val[b].y, val[b].w, 0x7632));  // (k3, k7)
-            partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
-                      Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
-          }
-          if (in_range[b]) xs[lr[b] * M + ms[b]] = o;
-#pragma unroll
-          for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
-          if (in_range[b] && (lr[b] % RPG) == 0) corr[(lr[b] / RPG) * CP + ms[b]] = real[b] ? -partial : 0.f;
-        }
+      for (int b = 0; b < BATCH; ++b) {
+        const int i = start + b * THREADS + tid;
+        in_range[b] = i < items;
+        ms[b] = in_range[b] ? i / sh.rows : 0;
+        lr[b] = in_range[b] ? i - ms[b] * sh.rows : 0;
+        real[b] = in_range[b] && sh.row0 + lr[b] < k8;
+        val[b] = real[b] ? xg[size_t(ms[b]) * k8 + sh.row0 + lr[b]] : make_uint4(0, 0, 0, 0);
       }
-      for (int i = tid; i < kMaxSpans; i += THREADS) span_count[i] = 0;
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        float partial = 0.f;
+        uint4 o = make_uint4(0, 0, 0, 0);   // rows past K/8 (last chunk) are staged as zeros
+        if (real[b]) {
+          o.x = prmt(val[b].x, val[b].z, 0x5410);                        // (k0, k4)
+          o.y = Expand<T>::scale_odd(prmt(val[b].x, val[b].z, 0x7632));  // (k1, k5)
+          o.z = prmt(val[b].y, val[b].w, 0x5410);                        // (k2, k6)
+          o.w = Expand<T>::scale_odd(prmt(val[b].y, val[b].w, 0x7632));  // (k3, k7)
+          partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
+                    Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
+        }
+        if (in_range[b]) xs[lr[b] * M + ms[b]] = o;
+#pragma unroll
+        for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+        if (in_range[b] && (lr[b] % RPG) == 0) corr[(lr[b] / RPG) * CP + ms[b]] = real[b] ? -partial : 0.f;
+      }
     }
-    if (!RIDE) __syncthreads();   // staged data visible; nobody still reads the previous problem's (barrier below)
+    for (int i = tid; i < kMaxSpans; i += THREADS) span_count[i] = 0;
+    __syncthreads();   // staged data visible; nobody still reads the previous problem's (barrier below)
 
     uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
     const int group0 = sh.row0 / RPG;   // first staged group
 
     // this warp's units of the problem: sequence numbers congruent to the warp modulo WARPS
-    int j = ((warp - sh.first) % RING + RING) % RING;
-    for (; j < n_units; j += RING) {
+    int j = ((warp - sh.first) % WARPS + WARPS) % WARPS;
+    for (; j < n_units; j += WARPS) {
       if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
       const int seq = sh.first + j;
       const int unit = unit_at(sh, j);
@@ -473,7 +386,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
           __syncwarp();
           fence_proxy_async();
           if (lane == 0) {
-            issue(seq + S, pi, 3);
+            issue(seq + S, pi);
             if (shared_slots) {
               __threadfence_block();
               uses[slot] = use + 1;
@@ -482,7 +395,6 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         }
       };
       const bool skip_math = p.probe >= 1 && p.probe <= 5;
-      if (p.probe == 6) refill();   // measurement: the slot is given up before it is read (results are garbage)
       float facc[MB][8];
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb)
@@ -490,30 +402,6 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         for (int i = 0; i < 8; ++i) facc[mb][i] = 0.f;
 
       const int staged_row = u.chunk * kRows - sh.row0;   // first staged row of this unit
-      const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
-      float* my_corr = corr + warp * (GPC * CP);            // RIDE: this warp's correction sums of the unit
-      if (RIDE && !skip_math) {
-        // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
-        // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
-        // their share of the correction sum with the same fixed-order butterfly as the staged form
-        for (int m = 0; m < M; ++m) {
-          const uint32_t addr = xslot + uint32_t(m) * 512u + uint32_t(lane) * 16u;
-          const uint4 val = lds128(addr);
-          uint4 o;
-          o.x = prmt(val.x, val.z, 0x5410);
-          o.y = Expand<T>::scale_odd(prmt(val.x, val.z, 0x7632));
-          o.z = prmt(val.y, val.w, 0x5410);
-          o.w = Expand<T>::scale_odd(prmt(val.y, val.w, 0x7632));
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
-                       : "memory");
-          float partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
-                          Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
-#pragma unroll
-          for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
-          if ((lane % RPG) == 0) my_corr[(lane / RPG) * CP + m] = -partial;
-        }
-        __syncwarp();
-      }
       // Rows of X beyond M: the lanes that would hold them read row M - 1 instead.  An MMA output column depends
       // only on its own column of the activation fragment, and output columns >= M are never stored.
       const int m_lane = min(g, M - 1);
@@ -525,8 +413,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         for (int mb = 0; mb < MB; ++mb) {
           // (entries of rows >= M hold stale values: they only reach accumulator rows that are never stored)
           float2 c = make_float2(0.f, 0.f);
-          if (RIDE) c = *reinterpret_cast<const float2*>(&my_corr[gi * CP + mb * 8 + 2 * t]);
-          else if (group < q.groups) c = *reinterpret_cast<const float2*>(&corr[(group - group0) * CP + mb * 8 + 2 * t]);
+          if (group < q.groups) c = *reinterpret_cast<const float2*>(&corr[(group - group0) * CP + mb * 8 + 2 * t]);
 #pragma unroll
           for (int i = 0; i < 8; ++i) gacc[mb][i] = (i & 1) ? c.y : c.x;
         }
@@ -544,8 +431,7 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
             const int m = MB == 1 ? m_lane : min(mb * 8 + g, M - 1);
-            const uint4 b = RIDE ? lds128(xslot + uint32_t(m) * 512u + uint32_t(row) * 16u)
-                                 : lds128(xs_addr + uint32_t((staged_row + row) * M + m) * 16u);
+            const uint4 b = lds128(xs_addr + uint32_t((staged_row + row) * M + m) * 16u);
             float(&a01)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][0]);
             float(&a23)[4] = *reinterpret_cast<float(*)[4]>(&gacc[mb][4]);
             Elem<T>::mma16816(a01, c0[0], c1[0], c0[1], c1[1], b.x, b.y);
@@ -571,29 +457,9 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         }
       }
       // the slot is free: request the unit that maps to it next, whichever problem that is
-      if (p.probe != 6) refill();
+      refill();
 
       if (p.probe == 2 || p.probe == 3) continue;   // measurement: no reduction either
-      if (RIDE && !area_checked) {
-        // Before this warp's first write into the problem's partial area: every warp must have left problem
-        // pi - depth, which used the same area.  Checked here, after the unit's data has arrived and been
-        // multiplied, because by then it practically always holds (the wait above was the long one).
-        bool ok = false;
-        for (int spin = 0; spin < (1 << 20); ++spin) {
-          if (finished[pi - p.part_depth] >= RING) { ok = true; break; }
-          if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
-          __nanosleep(256);
-        }
-        __threadfence_block();
-        if (!ok) {
-          if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
-            atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
-            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-          }
-          break;
-        }
-        area_checked = true;
-      }
       // ---- level 1: the unit's partial joins its span's partials in shared memory --------------
       // accumulator element (mb, i): row m = 8*mb + 2t + (i & 1), column 4g + (i >> 1)
       const int seg_begin = max(u.span_first, sh.u0), seg_end = min(u.span_first + u.span_len, sh.u1);
@@ -684,46 +550,6 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
           const float4 sum = sum_partials(seg_first, seg_len, part_floats, false, m);
           if (block_dst) store_rows(block_dst, sum, m); else write_y(m, sum);
         }
-      } else if (RIDE) {
-        // ---- level 2, ride-along form: publish and move on, or leave the span's end to the reducer warp ----
-        const int first_cta = cta_of(q, u.span_first);
-        if (seg_end != u.span_first + u.span_len) {
-          float* slot_dst = q.scratch1 + (size_t(span) * q.maxp + (cta - first_cta)) * part_floats;
-          for (int m = 0; m < M; ++m) store_rows(slot_dst, sum_partials(seg_first, seg_len, part_floats, false, m), m);
-        } else {
-          int ticket = 0;
-          if (lane == 0) ticket = atomicAdd(&mail_tail, 1);
-          ticket = __shfl_sync(0xffffffffu, ticket, 0);
-          bool room = false;
-          for (int spin = 0; spin < (1 << 22); ++spin) {
-            if (ticket - *reinterpret_cast<volatile int*>(&mail_head) < kMailEntries) { room = true; break; }
-            if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
-            __nanosleep(256);
-          }
-          if (!room) {
-            if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
-              atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
-              *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-            }
-            break;
-          }
-          __threadfence_block();
-          const int e = ticket % kMailEntries;
-          for (int m = 0; m < M; ++m) {
-            const float4 sum = sum_partials(seg_first, seg_len, part_floats, false, m);
-            if (q4 == 0) *reinterpret_cast<float4*>(&mail_data[e][m][4 * v8]) = sum;
-          }
-          __syncwarp();
-          if (lane == 0) {
-            mail_ctx[e][0] = pi;
-            mail_ctx[e][1] = span;
-            mail_ctx[e][2] = u.tile;
-            mail_ctx[e][3] = cta - first_cta;
-            __threadfence_block();
-            *reinterpret_cast<volatile int*>(&mail_ready[e]) = ticket + 1;
-          }
-        }
-        continue;
       } else {
         // ---- level 2: a span shared with neighbouring CTAs ------------------------------------
         const int first_cta = cta_of(q, u.span_first), last_cta = cta_of(q, u.span_first + u.span_len - 1);
@@ -745,34 +571,33 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
         if (lane == 0) q.counters2[u.tile] = 0;
       }
     }
-    if (RIDE) {
-      // this warp has left the problem (its partial area may be reused two problems later)
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        atomicAdd(const_cast<int*>(&finished[pi]), 1);
-      }
-      if (*reinterpret_cast<volatile int*>(&abort_flag)) return;
-    } else {
-      // everybody is done with this problem's staged activations and partials before the next problem
-      // overwrites them (the weight ring keeps streaming meanwhile)
-      __syncthreads();
-    }
+    // everybody is done with this problem's staged activations and partials before the next problem
+    // overwrites them (the weight ring keeps streaming meanwhile)
+    __syncthreads();
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// The ride-along form as a kernel of its own (problems of at most two rows).
+// The ride-along form as a kernel of its own (problems of at most eight rows: one MMA row block).
 //
-// The work is the same as in the RIDE branch of the kernel above; what differs is the bookkeeping, which is
-// what bounds this kernel (it issues about as many instructions as the SM can take while the stream runs):
+// What bounds this kernel is the number of instructions it issues (about as many as the SM can take
+// while the stream runs), so the bookkeeping is kept out of the loop:
 //   * at start-up every thread works out ONE unit of the CTA's whole sequence - problem, column tile, chunk,
-//     segment, partial slot, what happens when the segment is complete - and leaves it as a 16-byte entry in a
-//     schedule in shared memory; the loop reads an entry instead of dividing unit numbers again (twice per unit);
-//   * 31 ring warps own one slot each (or a whole number), so slot and phase need no division either, and a
-//     warp's refill is always its own next unit;
-//   * one loop over the warp's units of all problems.
+//     its place in its segment (the part of a span inside this CTA), what happens when the segment is
+//     complete - and leaves it as a 16-byte entry in a schedule in shared memory;
+//   * units are taken in sequence order by whichever ring warp is free (a ticket per unit): the warps' cycles
+//     vary by tens of percent, and with a fixed unit-to-warp map the CTA would end with its unluckiest warp;
+//   * a segment's units are dealt round-robin to a few chains, each with an accumulator in shared memory: the
+//     warp that finishes a chain's k-th unit waits until the first k have been added, adds its own, and passes
+//     the turn on; the warp with the segment's last unit adds the chains (fixed order throughout: bitwise
+//     reproducible) and writes Y, publishes the sum for the CTA that holds the span's end, or hands it to the
+//     reducer.  Every accumulator is used once per launch, so nothing is reused and no warp waits for a buffer.
+// Unit number u lives in slot u % S; the warp that takes it first makes sure that the slot's previous unit
+// was consumed and this one requested (almost always so: units arrive in order), because a parity wait on a
+// barrier that is still a whole phase behind would return at once.
 // ---------------------------------------------------------------------------------------------
+constexpr int kRideRows = 8;
+
 template <typename T, int STEPS>
 __global__ void __launch_bounds__(1024, 1)
 w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
@@ -783,10 +608,11 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   constexpr int kScaleBytes = GPC * 64;
   extern __shared__ unsigned char smem_raw[];
   __shared__ Share shares[kMaxProblems];
-  __shared__ int total_units;
+  __shared__ int acc_first[kMaxProblems];      // index of the problem's first segment accumulator
+  __shared__ int total_units, total_segments;
   __shared__ int abort_flag;
-  __shared__ __align__(16) float mail_data[kMailEntries][kMailRows][kCols];
-  __shared__ int mail_ctx[kMailEntries][4];    // problem, span, column tile, partials published by other CTAs
+  __shared__ __align__(16) float mail_data[kMailEntries][kRideRows][kCols];
+  __shared__ int mail_ctx[kMailEntries][4];    // problem, column tile, partials published by other CTAs
   __shared__ int mail_ready[kMailEntries];     // ticket + 1 once the entry is complete
   __shared__ int mail_tail, mail_head;         // tickets given out / entries consumed
   __shared__ int next_unit;                    // the next unit of the CTA's sequence nobody has taken yet
@@ -799,14 +625,13 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const int S = p.slots;
-  volatile int* uses = reinterpret_cast<volatile int*>(base_ptr + p.uses_offset);   // refills requested so far, per slot
   const uint32_t scale_base = base + uint32_t(S) * kWeightBytes;
   const uint32_t bars = scale_base + uint32_t(S) * kScaleBytes;
+  volatile int* uses = reinterpret_cast<volatile int*>(base_ptr + p.uses_offset);   // refills requested so far, per slot
   float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
-  int* span_counts = reinterpret_cast<int*>(base_ptr + p.span_offset);   // one row of tickets per problem
-  float* parts = reinterpret_cast<float*>(base_ptr + p.part_offset);
+  volatile int* turn = reinterpret_cast<volatile int*>(base_ptr + p.span_offset);   // per chain: units added so far
+  float* accs = reinterpret_cast<float*>(base_ptr + p.part_offset);                 // per chain: [rows][32] sums
   const uint32_t xbox_base = base + uint32_t(p.xbox_offset);
-  volatile int* finished = reinterpret_cast<volatile int*>(base_ptr + p.finished_offset);   // ring warps done per problem
   uint4* sched = reinterpret_cast<uint4*>(base_ptr + p.sched_offset);
 
   // ---- this CTA's share of every problem ---------------------------------------------------
@@ -823,6 +648,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       if (b.span_first + b.span_len > s.u1 && b.span_first >= s.u0 + s.head) s.tail = s.u1 - max(b.span_first, s.u0);
       if (s.head == s.u1 - s.u0) s.tail = 0;
       s.span0 = a.tile;
+      s.rows = b.tile - a.tile + 1;   // segments of the share (one per column tile touched)
       s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
     }
     shares[tid] = s;
@@ -831,8 +657,6 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   if (tid == 0) mail_tail = mail_head = 0;
   if (tid == 0) next_unit = 0;
   if (tid < kMailEntries) mail_ready[tid] = 0;
-  for (int i = tid; i < kMaxProblems * kMaxSpans; i += THREADS) span_counts[i] = 0;
-  if (tid < kMaxProblems) finished[tid] = 0;
   for (int i = tid; i < S; i += THREADS) {
     mbar_init(bars + uint32_t(i) * 8u, 1);
     uses[i] = 0;
@@ -840,23 +664,27 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   if (tid == 0) fence_mbar_init();
   __syncthreads();
   if (tid == 0) {
-    int first = 0;
+    int first = 0, segments = 0;
     for (int i = 0; i < p.count; ++i) {
       shares[i].first = first;
       first += shares[i].u1 - shares[i].u0;
+      acc_first[i] = segments;
+      segments += shares[i].rows;
     }
     total_units = first;
+    total_segments = segments;
   }
   __syncthreads();
   const int total = total_units;
+  for (int i = tid; i < ((1 << p.acc_ring_shift) << p.chain_shift) + (1 << p.acc_ring_shift); i += THREADS) turn[i] = 0;
 
-  // Schedule entry: x = tile | problem << 24 | whole << 28 | ends the span << 29 | (M - 1) << 30
-  //                 y = chunk | segment index in the share << 20
+  // Schedule entry: x = tile | problem << 24 | whole span << 28 | ends the span << 29
+  //                 y = chunk | (M - 1) << 20
   //                 z = units of the segment | CTAs that hold earlier parts of the span << 20
-  //                 w = partial slot of the unit | partial slot of the segment's first unit << 16
+  //                 w = place of the unit in its segment | the segment's accumulator << 16
   auto issue = [&](uint4 ent, uint32_t slot, int what) {
     const int tile = int(ent.x & 0xFFFFFFu), i = int((ent.x >> 24) & 15u), chunk = int(ent.y & 0xFFFFFu);
-    const uint32_t rows = 1u + ((ent.x >> 30) & 1u);
+    const uint32_t rows = 1u + ((ent.y >> 20) & 7u);
     const uint32_t bar = bars + slot * 8u;
     if (p.probe >= 3) {   // measurement: the packed weights alone
       if (what & 1) {
@@ -873,9 +701,8 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     if (what & 2) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], chunk * 256, 0, bar);
   };
 
-  // One entry per thread (a CTA has at most kMaxProblems * units-per-share of them, below THREADS is the
-  // common case); the threads of the first S entries request them at once.  With launch overlap the packed
-  // weights (static) are requested before the wait for the kernel ahead, the activations after it.
+  // One entry per thread; the threads of the first S entries request them at once.  With launch overlap the
+  // packed weights (static) are requested before the wait for the kernel ahead, the activations after it.
   uint4 mine_ent = make_uint4(0, 0, 0, 0);
   for (int e = tid; e < total; e += THREADS) {
     int i = 0;
@@ -890,18 +717,17 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     const bool ends = seg_end == u.span_first + u.span_len;
     const int earlier = whole ? 0 : cta - cta_of(q, u.span_first);
     uint4 ent;
-    ent.x = uint32_t(u.tile) | (uint32_t(i) << 24) | (whole ? 1u << 28 : 0u) | (ends ? 1u << 29 : 0u) |
-            (uint32_t(q.M - 1) << 30);
-    ent.y = uint32_t(u.chunk) | (uint32_t(u.tile - sh.span0) << 20);
+    ent.x = uint32_t(u.tile) | (uint32_t(i) << 24) | (whole ? 1u << 28 : 0u) | (ends ? 1u << 29 : 0u);
+    ent.y = uint32_t(u.chunk) | (uint32_t(q.M - 1) << 20);
     ent.z = uint32_t(seg_len) | (uint32_t(earlier) << 20);
-    ent.w = uint32_t(unit - sh.u0) | (uint32_t(seg_begin - sh.u0) << 16);
+    ent.w = uint32_t(unit - seg_begin) | (uint32_t(acc_first[i] + u.tile - sh.span0) << 16);
     sched[e] = ent;
     if (e == tid) mine_ent = ent;
   }
   if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 1);
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 2);
-  __syncthreads();   // the schedule is complete
+  __syncthreads();   // the schedule and the turn counters are complete
 
   if (warp == RING) {
     // ---- the reducer warp ------------------------------------------------------------------------
@@ -930,9 +756,9 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       }
       __threadfence_block();
       const TableProblem& q = p.problem[mail_ctx[e][0]];
-      const int span = mail_ctx[e][1], tile = mail_ctx[e][2], published = mail_ctx[e][3];
+      const int tile = mail_ctx[e][1], published = mail_ctx[e][2];
       const int part_floats = q.M * kCols;
-      const float* span_scratch = q.scratch1 + size_t(span) * q.maxp * part_floats;
+      const float* span_scratch = q.scratch1 + size_t(tile) * q.maxp * part_floats;   // one chunk block: span = tile
       uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
       for (int m = lane >> 3; m < q.M; m += 4) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -973,28 +799,9 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     row_of[i] = STEPS >= 2 ? 8 * (i >> 1) + 2 * t + (i & 1) : t;
     off_of[i] = uint32_t(row_of[i]) * 128u + (uint32_t(g ^ (row_of[i] & 7)) << 4);
   }
-  const int q4 = lane >> 3, v8 = lane & 7;   // reduction lanes: quarter q4 takes partials q4, q4+4, ...; columns 4*v8..+3
   float* my_corr = corr + warp * (GPC * CP);  // this warp's correction sums of the unit in hand
   const bool skip_math = p.probe >= 1 && p.probe <= 5;
 
-  // a ring warp has left problems [from, to): their partial areas may be reused two problems later
-  auto leave = [&](int from, int to) {
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_block();
-      for (int k = max(from, 0); k < to; ++k) atomicAdd(const_cast<int*>(&finished[k]), 1);
-    }
-  };
-
-  // Units are taken in sequence order by whichever ring warp is free (a ticket per unit): the warps' cycles vary
-  // by tens of percent, and with a fixed unit-to-warp map the CTA ends with its unluckiest warp while the others
-  // have long been idle.  Unit number u lives in slot u % S; the warp that takes it first makes sure that the
-  // slot's previous unit was consumed and this one requested (almost always so: units arrive in order), because
-  // a parity wait on a barrier that is still a whole phase behind would return at once.
-  int cur = -1, M = 1, part_floats = kCols;
-  float* part = parts;
-  int* span_count = span_counts;
-  bool area_checked = true;
   for (;;) {
     if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
     int seq = 0;
@@ -1004,16 +811,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     const uint4 now = sched[seq];
     const int use = fast_div(seq, S, p.magic_slots);
     const uint32_t slot = uint32_t(seq - use * S);
-    const int pi = int((now.x >> 24) & 15u);
-    if (pi != cur) {
-      leave(cur, pi);
-      cur = pi;
-      M = int((now.x >> 30) & 1u) + 1;
-      part_floats = M * kCols;
-      part = parts + size_t(pi % p.part_depth) * p.part_stride;
-      span_count = span_counts + pi * kMaxSpans;
-      area_checked = pi < p.part_depth;   // this partial area was last used by problem pi - depth
-    }
+    const int M = int((now.y >> 20) & 7u) + 1;
     const uint32_t bar = bars + slot * 8u;
     bool requested = true;
     if (use > 0 && uses[slot] < use) {
@@ -1067,6 +865,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       for (int gi = 0; gi < GPC; ++gi) {
         float gacc[8];
         {
+          // (entries of rows >= M hold stale values: they only reach accumulator rows that are never stored)
           const float2 c = *reinterpret_cast<const float2*>(&my_corr[gi * CP + 2 * t]);
 #pragma unroll
           for (int i = 0; i < 8; ++i) gacc[i] = (i & 1) ? c.y : c.x;
@@ -1117,93 +916,110 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     }
     if (p.probe == 2 || p.probe == 3) continue;   // measurement: no reduction either
 
-    if (!area_checked) {
-      // Before this warp's first write into the problem's partial area: every ring warp must have left problem
-      // pi - depth, which used the same area.
-      bool ok = false;
-      for (int spin = 0; spin < (1 << 20); ++spin) {
-        if (finished[pi - p.part_depth] >= RING) { ok = true; break; }
-        if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
-        __nanosleep(256);
+    // ---- the unit joins its segment's sum --------------------------------------------------------------
+    // A segment's units are dealt round-robin to C chains, each with an accumulator [rows][32] in shared memory
+    // and a turn counter: the warp with the chain's k-th unit waits until the first k have been added, adds its
+    // own and passes the turn on.  One chain could not keep up (a hand-over through shared memory takes longer
+    // than the stream needs per unit), C of them can, and the order of every addition stays fixed.
+    // accumulator element i of a lane: row m = 2t + (i & 1), columns 4g + (i >> 1)
+    // The CTA's segments take the chain sets of a small ring in turn (set = segment number modulo the ring,
+    // generation = segment number / ring): the units in flight belong to a handful of segments at most.  Turn
+    // counters carry the generation in their upper half, and a set is handed to its next segment by `done`.
+    const int place = int(now.w & 0xFFFFu), seg_len = int(now.z & 0xFFFFFu);
+    const int set = int(now.w >> 16) & ((1 << p.acc_ring_shift) - 1), generation = int(now.w >> 16) >> p.acc_ring_shift;
+    const int chain0 = set << p.chain_shift;                     // the set's first chain
+    const int chain = chain0 + (place & (p.chains - 1)), position = place >> p.chain_shift;
+    const int turn0 = generation << 16;
+    volatile int* done = turn + ((1 << p.acc_ring_shift) << p.chain_shift);   // per set: generations finished
+    float* acc = accs + size_t(chain) * p.part_stride + 4 * g;
+    auto await = [&](volatile int* counter, int count) {   // true once the counter has reached `count`
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (*counter >= count) return true;
+        if (*reinterpret_cast<volatile int*>(&abort_flag)) return false;
+        if (spin > 8) __nanosleep(32);
       }
+      if (lane == 0) {
+        atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
+        *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+      }
+      return false;
+    };
+    if (position == 0) {
+      if (generation > 0 && !await(done + set, generation)) break;   // the set's previous segment has been read out
+    } else {
+      if (!await(turn + chain, turn0 + position)) break;
       __threadfence_block();
-      if (!ok) {
-        if (lane == 0 && !*reinterpret_cast<volatile int*>(&abort_flag)) {
-          atomicExch(p.status, INTENT_B200_ERR_TIMEOUT);
-          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
-        }
-        break;
-      }
-      area_checked = true;
-    }
-    // ---- level 1: the unit's partial joins its segment's partials in shared memory ----------------
-    // accumulator element i: row m = 2t + (i & 1), column 4g + (i >> 1)
-    const int tile = int(now.x & 0xFFFFFFu);
-    const int seg = int((now.y >> 20) & 63u), seg_len = int(now.z & 0xFFFFFu);
-    float* mine = part + size_t(now.w & 0xFFFFu) * part_floats;
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int m = 2 * t + hh;
-      if (m < M)
-        *reinterpret_cast<float4*>(mine + m * kCols + 4 * g) = make_float4(facc[0 + hh], facc[2 + hh], facc[4 + hh], facc[6 + hh]);
+      for (int hh = 0; hh < 2; ++hh)
+        if (2 * t + hh < M) {
+          const float4 v = *reinterpret_cast<const float4*>(acc + (2 * t + hh) * kCols);
+          facc[0 + hh] += v.x; facc[2 + hh] += v.y; facc[4 + hh] += v.z; facc[6 + hh] += v.w;
+        }
     }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+      if (2 * t + hh < M)
+        *reinterpret_cast<float4*>(acc + (2 * t + hh) * kCols) = make_float4(facc[0 + hh], facc[2 + hh], facc[4 + hh], facc[6 + hh]);
     __syncwarp();
-    int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(span_count + seg, 1) == seg_len - 1;
+      turn[chain] = turn0 + position + 1;
     }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last || p.probe == 4) continue;
-    __threadfence_block();
+    if (place + 1 < seg_len || p.probe == 4) continue;
 
-    // the segment's partials for row m, in unit order: quarter q4 adds partials q4, q4 + 4, ... (four loads in
-    // flight), then the quarters are added in a fixed order
-    const float* seg_first = part + size_t(now.w >> 16) * part_floats;
-    auto segment_sum = [&](int m) {
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = q4; c < seg_len; c += 16) {
-        float4 a[4];
+    // ---- the segment's last unit: add the chains in order ----------------------------------------------
+    {
+      bool complete = true;
+      const int used = min(p.chains, seg_len);
+      for (int c = 0; c < used && complete; ++c)
+        complete = await(turn + chain0 + c, turn0 + ((seg_len - c + p.chains - 1) >> p.chain_shift));
+      if (!complete) break;
+      __threadfence_block();
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int cc = c + 4 * k;
-          a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (cc < seg_len) a[k] = *reinterpret_cast<const float4*>(seg_first + size_t(cc) * part_floats + m * kCols + 4 * v8);
-        }
+      for (int i = 0; i < 8; ++i) facc[i] = 0.f;
+      for (int c = 0; c < used; ++c) {
+        const float* from = accs + size_t(chain0 + c) * p.part_stride + 4 * g;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          sum.x += a[k].x; sum.y += a[k].y; sum.z += a[k].z; sum.w += a[k].w;
-        }
+        for (int hh = 0; hh < 2; ++hh)
+          if (2 * t + hh < M) {
+            const float4 v = *reinterpret_cast<const float4*>(from + (2 * t + hh) * kCols);
+            facc[0 + hh] += v.x; facc[2 + hh] += v.y; facc[4 + hh] += v.z; facc[6 + hh] += v.w;
+          }
       }
-#pragma unroll
-      for (int d = 16; d >= 8; d >>= 1) {
-        sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
-        sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
-        sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
-        sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        done[set] = generation + 1;
       }
-      return sum;
-    };
+    }
+
+    // ---- the segment is complete: this warp holds its sum ----------------------------------------------
+    const int pi = int((now.x >> 24) & 15u);
+    const int tile = int(now.x & 0xFFFFFFu);
     const TableProblem& q = p.problem[pi];
     const bool whole = ((now.x >> 28) & 1u) != 0 || p.probe == 5;
-    const int col = tile * kCols + 4 * v8;
+    const int col = tile * kCols + 4 * g;
     if (whole) {
       uint16_t* y = reinterpret_cast<uint16_t*>(q.y);
-      for (int m = 0; m < M; ++m) {
-        const float4 sum = segment_sum(m);
-        if (q4 == 0 && col < q.N) {   // N is a multiple of 8, so the four columns are inside together
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int m = 2 * t + hh;
+        if (m < M && col < q.N) {   // N is a multiple of 8, so the four columns are inside together
           uint2 out;
-          out.x = uint32_t(Elem<T>::from_float(sum.x)) | (uint32_t(Elem<T>::from_float(sum.y)) << 16);
-          out.y = uint32_t(Elem<T>::from_float(sum.z)) | (uint32_t(Elem<T>::from_float(sum.w)) << 16);
+          out.x = uint32_t(Elem<T>::from_float(facc[0 + hh])) | (uint32_t(Elem<T>::from_float(facc[2 + hh])) << 16);
+          out.y = uint32_t(Elem<T>::from_float(facc[4 + hh])) | (uint32_t(Elem<T>::from_float(facc[6 + hh])) << 16);
           *reinterpret_cast<uint2*>(y + size_t(m) * q.N + col) = out;
         }
       }
     } else if (((now.x >> 29) & 1u) == 0) {
       // the span goes on in the next CTA: publish this segment's sum and move on
-      float* dst = q.scratch1 + (size_t(tile) * q.maxp + (now.z >> 20)) * part_floats;
-      for (int m = 0; m < M; ++m) {
-        const float4 sum = segment_sum(m);
-        if (q4 == 0) publish(reinterpret_cast<float4*>(dst + m * kCols + 4 * v8), sum);
+      float* dst = q.scratch1 + (size_t(tile) * q.maxp + (now.z >> 20)) * (M * kCols);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int m = 2 * t + hh;
+        if (m < M)
+          publish(reinterpret_cast<float4*>(dst + m * kCols + 4 * g),
+                  make_float4(facc[0 + hh], facc[2 + hh], facc[4 + hh], facc[6 + hh]));
       }
     } else {
       // the span ends here: its sum goes to the reducer warp
@@ -1225,22 +1041,22 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       }
       __threadfence_block();
       const int e = ticket % kMailEntries;
-      for (int m = 0; m < M; ++m) {
-        const float4 sum = segment_sum(m);
-        if (q4 == 0) *reinterpret_cast<float4*>(&mail_data[e][m][4 * v8]) = sum;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int m = 2 * t + hh;
+        if (m < M)
+          *reinterpret_cast<float4*>(&mail_data[e][m][4 * g]) = make_float4(facc[0 + hh], facc[2 + hh], facc[4 + hh], facc[6 + hh]);
       }
       __syncwarp();
       if (lane == 0) {
         mail_ctx[e][0] = pi;
-        mail_ctx[e][1] = tile;      // one chunk block: the span is the column tile
-        mail_ctx[e][2] = tile;
-        mail_ctx[e][3] = int(now.z >> 20);
+        mail_ctx[e][1] = tile;
+        mail_ctx[e][2] = int(now.z >> 20);
         __threadfence_block();
         *reinterpret_cast<volatile int*>(&mail_ready[e]) = ticket + 1;
       }
     }
   }
-  leave(cur, p.count);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1257,6 +1073,7 @@ struct HostProblem {
 struct ProblemPlan {
   int chunks, tiles, cb, nblocks, units, each, extra, maxp;
   bool ride;                                     // the ride-along form (no staging, no CTA barriers)
+  int segments, sequence;                        // ride-along form: segment accumulators and schedule entries (worst CTA)
   size_t xs_bytes, corr_bytes, part_bytes;       // shared memory this problem needs (worst CTA)
   size_t counters1, counters2, scratch1, scratch2, bytes;   // workspace layout (offsets) and size
 };
@@ -1267,7 +1084,15 @@ size_t slot_bytes(int group_size) { return size_t(kWeightBytes) + size_t(256 / g
 size_t fixed_bytes(int group_size) {
   return 1024 + size_t(kMinSlots) * slot_bytes(group_size) + 256 + kMaxProblems * kMaxSpans * 4 + 64 + 128;
 }
-constexpr size_t kRideCorrBytes = 32 * 8 * 16 * 4;   // per-warp correction sums, widest case
+constexpr size_t kRideCorrBytes = 32 * 8 * 8 * 4;    // ride-along form: per-warp correction sums, widest case (g32)
+constexpr int kMinRideSlots = 20;                    // the ride-along form is planned only if this many slots fit
+// ride-along form: what a launch needs in shared memory besides its slots
+int ride_chains(int rows) { return rows <= 2 ? 8 : 4; }        // chains per segment
+int ride_ring_shift(int rows) { return rows <= 4 ? 4 : 3; }     // log2 of the chain sets that exist at a time
+size_t ride_other_bytes(size_t sequence, int rows) {
+  const size_t sets = size_t(1) << ride_ring_shift(rows);
+  return 1024 + 512 + kRideCorrBytes + sets * (ride_chains(rows) * (size_t(rows) * kCols * 4 + 4) + 4) + sequence * 16;
+}
 
 // Spans a CTA may touch and rows it must stage, worst case over CTAs, for a chunk-block size.
 void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched, int* spans_touched) {
@@ -1280,7 +1105,7 @@ void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched,
   *spans_touched = n_max <= 0 ? 0 : (n_max - 1) / (shortest < cb ? shortest : cb) + 2;
 }
 
-bool plan_problem(int M, int K, int N, int group_size, int grid, ProblemPlan* out) {
+bool plan_problem(int M, int K, int N, int group_size, int grid, bool allow_ride, ProblemPlan* out) {
   ProblemPlan q{};
   const size_t smem_budget = size_t(kSmemLimit) - fixed_bytes(group_size);
   q.tiles = (N + kCols - 1) / kCols;
@@ -1297,12 +1122,16 @@ bool plan_problem(int M, int K, int N, int group_size, int grid, ProblemPlan* ou
     // ride-along form: the activations travel with every unit, the whole K range is one chunk block
     int blocks, spans;
     share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
-    q.ride = M <= 2 && spans <= kMaxSpans &&
-             size_t(kMinSlots) * M * 512 + kRideCorrBytes + 2 * q.part_bytes <= smem_budget;
+    q.segments = spans;
+    q.sequence = n_max;
+    q.ride = allow_ride && M <= kRideRows && n_max < 65536 &&
+             size_t(kMinRideSlots) * (slot_bytes(group_size) + size_t(M) * 512) + ride_other_bytes(n_max, M) <=
+                 size_t(kSmemLimit);
   }
   if (q.ride) {
     q.xs_bytes = 0;
     q.corr_bytes = kRideCorrBytes;
+    q.part_bytes = 0;
   } else {
     // the largest chunk block whose staged activations (all blocks a CTA can touch) fit beside the rest
     for (;;) {
@@ -1358,24 +1187,13 @@ int validate(const HostProblem& h, int group_size) {
   return INTENT_B200_OK;
 }
 
-int g_table_warps = 0;     // ride-along form: 16 or 32 warps per CTA (0 = built-in choice); for measurement
 int g_table_probe = 0;
-int g_table_depth = 0;     // ride-along form: partial areas (4 = four when they fit; otherwise two); for measurement
-int g_table_slots = 0;     // upper limit on the ring's slots (0 = as many as fit); for measurement
-int g_table_lean = 1;      // ride-along problems run w4a16_ride_kernel (0 = the RIDE form of w4a16_table_kernel); for measurement
+int g_table_slots = 0;     // upper limit on the ring's slots (0 = the built-in choice); for measurement
 
-template <typename T, int MB, int STEPS, bool RIDE, int WARPS>
-int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream);
-
-template <typename T, int MB, int STEPS, bool RIDE>
+template <typename T, int MB, int STEPS>
 int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
-  if (RIDE && g_table_warps == 16) return launch_table_warps<T, MB, STEPS, RIDE, 16>(maps, p, grid, smem, stream);
-  return launch_table_warps<T, MB, STEPS, RIDE, (MB == 1 ? 32 : 16)>(maps, p, grid, smem, stream);
-}
-
-template <typename T, int MB, int STEPS, bool RIDE, int WARPS>
-int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
-  auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS, RIDE>;
+  constexpr int WARPS = MB == 1 ? 32 : 16;
+  auto kernel = w4a16_table_kernel<T, MB, STEPS, WARPS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return cuda_status(e);
   cudaLaunchConfig_t config = {};
@@ -1389,9 +1207,8 @@ int launch_table_warps(const TableMaps& maps, const TableParams& p, int grid, si
   config.attrs = attribute;
   config.numAttrs = p.overlap ? 1 : 0;
   if (LaunchFacts* sink = observe_sink())
-    return record_launch(sink, reinterpret_cast<const void*>(kernel),
-                         RIDE ? "w4a16_table_kernel activations ride with the units" : "w4a16_table_kernel staged activations",
-                         grid, WARPS * 32, int(smem), 1);
+    return record_launch(sink, reinterpret_cast<const void*>(kernel), "w4a16_table_kernel staged activations", grid,
+                         WARPS * 32, int(smem), 1);
   e = cudaLaunchKernelEx(&config, kernel, maps, p);
   if (e != cudaSuccess) return cuda_status(e);
   note_launch();
@@ -1437,14 +1254,7 @@ int64_t table_workspace(const HostProblem* problems, int count, int group_size, 
         offsets[i] = offset;
         continue;
       }
-      if (!plan_problem(int(h.M), int(h.K), int(h.N), group_size, grid, &plans[i])) return -1;
-      if (!g_table_ride && plans[i].ride) {
-        plans[i].ride = false;     // staged form forced: the whole K range staged (it fits for M <= 2)
-        const size_t rows = size_t(plans[i].chunks) * kRows;
-        plans[i].xs_bytes = rows * size_t(h.M) * 16;
-        plans[i].corr_bytes = (rows / (group_size / 8) + 1) * 16 * 4;
-        if (plans[i].xs_bytes + plans[i].corr_bytes + plans[i].part_bytes > size_t(kSmemLimit) - fixed_bytes(group_size)) return -1;
-      }
+      if (!plan_problem(int(h.M), int(h.K), int(h.N), group_size, grid, g_table_ride != 0, &plans[i])) return -1;
       offsets[i] = offset;
       offset += plans[i].bytes;
     }
@@ -1500,7 +1310,7 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   for (int begin = 0; begin < count;) {
     TableMaps maps;
     TableParams p{};
-    size_t xs_max = 0, corr_max = 0, part_max = 0, sequence = 0;
+    size_t xs_max = 0, corr_max = 0, part_max = 0, sequence = 0, segments = 0;
     int n = 0, mb = 1, i = begin, rows_max = 0;
     bool ride = false;
     for (; i < count && n < kMaxProblems; ++i) {
@@ -1515,9 +1325,14 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
         const size_t corr_b = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
         const size_t part_b = q.part_bytes > part_max ? q.part_bytes : part_max;
         const int rows = int(h.M) > rows_max ? int(h.M) : rows_max;
-        const size_t together =
-            ride ? size_t(kMinSlots) * rows * 512 + corr_b + 2 * part_b + (sequence + q.each + 1) * 16 : xs + corr_b + part_b;
-        if (n > 0 && together > behind_ring) break;
+        if (ride) {
+          if (n > 0 && size_t(kMinRideSlots) * (slot_bytes(group_size) + size_t(rows) * 512) +
+                               ride_other_bytes(sequence + q.sequence, rows) >
+                           size_t(kSmemLimit))
+            break;
+        } else if (n > 0 && xs + corr_b + part_b > behind_ring) {
+          break;
+        }
       }
       TableProblem& d = p.problem[n];
       d.x = h.x;
@@ -1555,7 +1370,8 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
                                       uint32_t(h.M), 256, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INTENT_B200_ERR_UNSUPPORTED;
       if (int(h.M) > rows_max) rows_max = int(h.M);
-      sequence += size_t(q.each) + (q.extra ? 1 : 0);
+      sequence += size_t(q.sequence);
+      segments += size_t(q.segments);
       xs_max = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
       corr_max = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
       part_max = q.part_bytes > part_max ? q.part_bytes : part_max;
@@ -1575,26 +1391,27 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     p.twos_complement = zero_point == -1 ? 1 : 0;
     p.overlap = g_table_overlap;
     p.status = reinterpret_cast<int*>(ws);
-    // As many slots as fit beside this launch's other regions: the ring's depth is what bounds the stream.
+    // As many slots as fit beside this launch's other regions, up to the built-in choice.
     const auto round16 = [](size_t v) { return (v + 15) & ~size_t(15); };
     p.xbox_bytes = ride ? rows_max * 512 : 0;
-    p.part_depth = 2;   // measured: two partial areas are faster than four (the warps stay closer together)
-    if (ride && g_table_depth >= 4 &&
-        fixed_bytes(group_size) + size_t(kMinSlots) * p.xbox_bytes + round16(corr_max) +
-                size_t(g_table_depth) * round16(part_max) <= size_t(kSmemLimit))
-      p.part_depth = g_table_depth;
+    p.part_depth = 1;
     {
-      const size_t others = 1024 + 256 + size_t(ride ? kMaxProblems : 1) * kMaxSpans * 4 + 64 + 128 + round16(corr_max) +
-                            round16(xs_max) + round16(part_max) * (ride ? p.part_depth : 1) + (ride ? sequence * 16 : 0);
+      const size_t others = ride ? ride_other_bytes(sequence, rows_max)
+                                 : 1024 + 256 + size_t(kMaxSpans) * 4 + 64 + 128 + round16(corr_max) + round16(xs_max) +
+                                       round16(part_max);
       if (others >= size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;
       size_t slots = (size_t(kSmemLimit) - others) / (slot_bytes(group_size) + p.xbox_bytes);
+      // Staged form: a whole number of slots per warp (every slot then always belongs to the same warp, and no
+      // warp has to check who used a slot before it).  Ride-along form: one slot per ring warp; measured on
+      // M = 1, a deeper ring (40 slots) does not stream faster and a shallower one (24) hardly slower.
+      const size_t choice = ride ? 31 : size_t(mb == 1 ? 32 : 16);
+      if (g_table_slots > 0) {
+        if (slots > size_t(g_table_slots)) slots = g_table_slots;
+      } else if (slots >= choice) {
+        slots = ride ? choice : slots / choice * choice;
+      }
       if (slots > size_t(kMaxSlots)) slots = kMaxSlots;
-      if (g_table_slots > 0 && slots > size_t(g_table_slots)) slots = g_table_slots;
-      // a whole number of slots per ring warp (w4a16_table_kernel: every slot then always belongs to the same
-      // warp, and no warp has to check who used a slot before it); measured: a deeper ring does not stream faster
-      const size_t ring = ride ? size_t(g_table_lean ? 31 : (g_table_warps == 16 ? 15 : 31)) : size_t(mb == 1 ? 32 : 16);
-      if (g_table_slots == 0 && slots >= ring) slots = slots / ring * ring;
-      if (slots < 8) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned for kMinSlots
+      if (slots < 8) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned with more
       p.slots = int(slots);
       p.magic_slots = uint32_t(((1ll << 32) + p.slots - 1) / p.slots);
     }
@@ -1605,37 +1422,39 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     offset = (offset + 127) & ~size_t(127);
     p.xbox_offset = int(offset);
     offset += size_t(p.slots) * p.xbox_bytes;
-    p.span_offset = int(offset);
-    offset += size_t(ride ? kMaxProblems : 1) * kMaxSpans * 4;
+    p.chains = ride ? ride_chains(rows_max) : 1;
+    p.chain_shift = p.chains == 8 ? 3 : p.chains == 4 ? 2 : 0;
+    p.acc_ring_shift = ride_ring_shift(rows_max);
+    const size_t sets = size_t(1) << p.acc_ring_shift;
+    p.span_offset = int(offset);    // staged: span tickets; ride-along: the chains' turn counters, then the sets' `done`
+    offset += round16(ride ? sets * (p.chains + 1) * 4 : size_t(kMaxSpans) * 4);
     p.finished_offset = int(offset);
     offset += 64;
     p.corr_offset = int(offset);
-    offset += (corr_max + 15) & ~size_t(15);
+    offset += round16(corr_max);
     p.xs_offset = int(offset);
-    offset += (xs_max + 15) & ~size_t(15);
-    p.part_offset = int(offset);
-    p.part_stride = int(((part_max + 15) & ~size_t(15)) / 4);      // in floats
+    offset += round16(xs_max);
+    p.part_offset = int(offset);    // staged: per-unit partials; ride-along: the chains' accumulators
+    p.part_stride = ride ? rows_max * kCols : int(round16(part_max) / 4);      // in floats
     p.probe = g_table_probe;
-    offset += ((part_max + 15) & ~size_t(15)) * (ride ? p.part_depth : 1);
+    offset += ride ? sets * p.chains * size_t(rows_max) * kCols * 4 : round16(part_max);
     p.sched_offset = int(offset);
     if (ride) offset += sequence * 16;
     const size_t smem = 1024 + offset;
     if (smem > size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;   // cannot happen: every problem was planned to fit
     int status;
-#define IB200_TABLE_STEPS(MB_, RIDE_)                                                           \
-  status = steps == 4   ? launch_table<T, MB_, 4, RIDE_>(maps, p, grid, smem, stream)           \
-           : steps == 2 ? launch_table<T, MB_, 2, RIDE_>(maps, p, grid, smem, stream)           \
-                        : launch_table<T, MB_, 1, RIDE_>(maps, p, grid, smem, stream);
-    if (ride && g_table_lean) {
+#define IB200_TABLE_STEPS(MB_)                                                           \
+  status = steps == 4   ? launch_table<T, MB_, 4>(maps, p, grid, smem, stream)           \
+           : steps == 2 ? launch_table<T, MB_, 2>(maps, p, grid, smem, stream)           \
+                        : launch_table<T, MB_, 1>(maps, p, grid, smem, stream);
+    if (ride) {
       status = steps == 4   ? launch_ride<T, 4>(maps, p, grid, smem, stream)
                : steps == 2 ? launch_ride<T, 2>(maps, p, grid, smem, stream)
                             : launch_ride<T, 1>(maps, p, grid, smem, stream);
-    } else if (ride) {
-      IB200_TABLE_STEPS(1, true)        // the ride-along form is only planned for M <= 2
     } else if (mb == 1) {
-      IB200_TABLE_STEPS(1, false)
+      IB200_TABLE_STEPS(1)
     } else {
-      IB200_TABLE_STEPS(2, false)
+      IB200_TABLE_STEPS(2)
     }
 #undef IB200_TABLE_STEPS
     if (status != INTENT_B200_OK) return status;
@@ -1687,9 +1506,10 @@ extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
   return INTENT_B200_OK;
 }
 
-// Measurement knobs of the ride-along form (process-global): "warps" 16 | 32 | 0 (built-in choice); "areas" 2 | 4
-// partial areas | 0 (built-in choice); "probe" 1 = stream-only (every unit's arithmetic is skipped: the results
-// are WRONG by design, the launch only shows what the ring alone can stream) | 0 = normal.
+// Measurement knobs (process-global): "slots" = upper limit on the ring's slots (0 = the built-in choice);
+// "probe" 1 = every unit's arithmetic is skipped, 2 = the reduction too, 3 = only the packed weights are loaded,
+// 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over
+// (the results are WRONG by design for every value but 0: these launches only show where the time goes).
 extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value) {
   if (!knob) return INTENT_B200_ERR_NULL;
   const auto is = [&](const char* name) {
@@ -1697,23 +1517,11 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
     for (; name[i] && knob[i] == name[i]; ++i) {}
     return name[i] == 0 && knob[i] == 0;
   };
-  if (is("warps") && (value == 0 || value == 16 || value == 32)) {
-    ib200::g_table_warps = value;
-    return INTENT_B200_OK;
-  }
-  if (is("areas") && (value == 0 || value == 2 || value == 4 || value == 8)) {
-    ib200::g_table_depth = value;
-    return INTENT_B200_OK;
-  }
-  if (is("lean") && (value == 0 || value == 1)) {
-    ib200::g_table_lean = value;
-    return INTENT_B200_OK;
-  }
   if (is("slots") && (value == 0 || (value >= 8 && value <= 64))) {
     ib200::g_table_slots = value;
     return INTENT_B200_OK;
   }
-  if (is("probe") && value >= 0 && value <= 6) {
+  if (is("probe") && value >= 0 && value <= 5) {
     ib200::g_table_probe = value;
     return INTENT_B200_OK;
   }
