@@ -634,54 +634,10 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   const uint32_t xbox_base = base + uint32_t(p.xbox_offset);
   uint4* sched = reinterpret_cast<uint4*>(base_ptr + p.sched_offset);
 
-  // ---- this CTA's share of every problem ---------------------------------------------------
-  if (tid < p.count) {
-    const TableProblem& q = p.problem[tid];
-    Share s;
-    s.u0 = cta * q.each + min(cta, q.extra);
-    s.u1 = s.u0 + q.each + (cta < q.extra ? 1 : 0);
-    s.head = s.tail = 0;
-    s.row0 = s.rows = s.span0 = s.reads = 0;
-    if (s.u1 > s.u0) {
-      const Unit a = decode_unit(q, s.u0), b = decode_unit(q, s.u1 - 1);
-      if (a.span_first < s.u0) s.head = min(s.u1, a.span_first + a.span_len) - s.u0;
-      if (b.span_first + b.span_len > s.u1 && b.span_first >= s.u0 + s.head) s.tail = s.u1 - max(b.span_first, s.u0);
-      if (s.head == s.u1 - s.u0) s.tail = 0;
-      s.span0 = a.tile;
-      s.rows = b.tile - a.tile + 1;   // segments of the share (one per column tile touched)
-      s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
-    }
-    shares[tid] = s;
-  }
-  if (tid == 0) abort_flag = 0;
-  if (tid == 0) mail_tail = mail_head = 0;
-  if (tid == 0) next_unit = 0;
-  if (tid < kMailEntries) mail_ready[tid] = 0;
-  for (int i = tid; i < S; i += THREADS) {
-    mbar_init(bars + uint32_t(i) * 8u, 1);
-    uses[i] = 0;
-  }
-  if (tid == 0) fence_mbar_init();
-  __syncthreads();
-  if (tid == 0) {
-    int first = 0, segments = 0;
-    for (int i = 0; i < p.count; ++i) {
-      shares[i].first = first;
-      first += shares[i].u1 - shares[i].u0;
-      acc_first[i] = segments;
-      segments += shares[i].rows;
-    }
-    total_units = first;
-    total_segments = segments;
-  }
-  __syncthreads();
-  const int total = total_units;
-  for (int i = tid; i < ((1 << p.acc_ring_shift) << p.chain_shift) + (1 << p.acc_ring_shift); i += THREADS) turn[i] = 0;
-
   // Schedule entry: x = tile | problem << 24 | whole span << 28 | ends the span << 29
   //                 y = chunk | (M - 1) << 20
   //                 z = units of the segment | CTAs that hold earlier parts of the span << 20
-  //                 w = place of the unit in its segment | the segment's accumulator << 16
+  //                 w = place of the unit in its segment | number of the segment in the CTA's sequence << 16
   auto issue = [&](uint4 ent, uint32_t slot, int what) {
     const int tile = int(ent.x & 0xFFFFFFu), i = int((ent.x >> 24) & 15u), chunk = int(ent.y & 0xFFFFFu);
     const uint32_t rows = 1u + ((ent.y >> 20) & 7u);
@@ -700,9 +656,89 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     }
     if (what & 2) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], chunk * 256, 0, bar);
   };
+  // this CTA's share of problem q (everything but its place in the sequence)
+  auto share_of = [&](const TableProblem& q) {
+    Share s;
+    s.u0 = cta * q.each + min(cta, q.extra);
+    s.u1 = s.u0 + q.each + (cta < q.extra ? 1 : 0);
+    s.head = s.tail = 0;
+    s.first = s.row0 = s.rows = s.span0 = s.reads = 0;
+    if (s.u1 > s.u0) {
+      const Unit a = decode_unit(q, s.u0), b = decode_unit(q, s.u1 - 1);
+      if (a.span_first < s.u0) s.head = min(s.u1, a.span_first + a.span_len) - s.u0;
+      if (b.span_first + b.span_len > s.u1 && b.span_first >= s.u0 + s.head) s.tail = s.u1 - max(b.span_first, s.u0);
+      if (s.head == s.u1 - s.u0) s.tail = 0;
+      s.span0 = a.tile;
+      s.rows = b.tile - a.tile + 1;   // segments of the share (one per column tile touched)
+      s.reads = s.head > 0 && a.span_first + a.span_len <= s.u1 ? 1 : 0;
+    }
+    return s;
+  };
 
-  // One entry per thread; the threads of the first S entries request them at once.  With launch overlap the
-  // packed weights (static) are requested before the wait for the kernel ahead, the activations after it.
+  // ---- start-up ---------------------------------------------------------------------------------------
+  // The first units are requested before anything else is set up: lane L of warp 1 initialises the barrier of
+  // slot L, works out unit L of the CTA's sequence by itself and requests its packed weights and scales (static
+  // data: with launch overlap this happens before the wait for the kernel ahead; the activations follow after it).
+  const int early = min(S, 32);
+  uint4 early_ent = make_uint4(0, 0, 0, 0);
+  bool early_unit = false;
+  if (warp == 1 && lane < early) {
+    mbar_init(bars + uint32_t(lane) * 8u, 1);
+    fence_mbar_init();
+    fence_proxy_async();
+    int first = 0;
+    for (int i = 0; i < p.count && !early_unit; ++i) {
+      const TableProblem& q = p.problem[i];
+      const int n = q.each + (cta < q.extra ? 1 : 0);
+      if (lane < first + n) {
+        const Share sh = share_of(q);
+        const Unit u = decode_unit(q, unit_at(sh, lane - first));
+        early_ent.x = uint32_t(u.tile) | (uint32_t(i) << 24);
+        early_ent.y = uint32_t(u.chunk) | (uint32_t(q.M - 1) << 20);
+        early_unit = true;
+      }
+      first += n;
+    }
+    if (early_unit) issue(early_ent, uint32_t(lane), 1);
+  }
+  if (warp == 0) {
+    // lane i: the share of problem i; its place in the sequence and its first segment by a scan over the lanes
+    Share sh;
+    sh.u0 = sh.u1 = sh.head = sh.tail = sh.first = sh.row0 = sh.rows = sh.span0 = sh.reads = 0;
+    if (lane < p.count) sh = share_of(p.problem[lane]);
+    int units_before = sh.u1 - sh.u0, segments_before = sh.rows;   // inclusive scans
+#pragma unroll
+    for (int d = 1; d < kMaxProblems; d <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, units_before, d), b = __shfl_up_sync(0xffffffffu, segments_before, d);
+      if (lane >= d) {
+        units_before += a;
+        segments_before += b;
+      }
+    }
+    if (lane < p.count) {
+      sh.first = units_before - (sh.u1 - sh.u0);
+      shares[lane] = sh;
+      acc_first[lane] = segments_before - sh.rows;
+    }
+    if (lane == p.count - 1) {
+      total_units = units_before;
+      total_segments = segments_before;
+    }
+  }
+  if (tid == 0) abort_flag = 0;
+  if (tid == 0) mail_tail = mail_head = 0;
+  if (tid == 0) next_unit = 0;
+  if (tid < kMailEntries) mail_ready[tid] = 0;
+  for (int i = tid; i < S; i += THREADS) {
+    if (i >= early) mbar_init(bars + uint32_t(i) * 8u, 1);
+    uses[i] = 0;
+  }
+  for (int i = tid; i < ((1 << p.acc_ring_shift) << p.chain_shift) + (1 << p.acc_ring_shift); i += THREADS) turn[i] = 0;
+  if (tid == 0) fence_mbar_init();
+  __syncthreads();
+  const int total = total_units;
+
+  // One schedule entry per thread; the threads of the first S entries that were not requested above do so now.
   uint4 mine_ent = make_uint4(0, 0, 0, 0);
   for (int e = tid; e < total; e += THREADS) {
     int i = 0;
@@ -724,10 +760,11 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     sched[e] = ent;
     if (e == tid) mine_ent = ent;
   }
-  if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 1);
+  if (tid >= early && tid < min(total, S)) issue(mine_ent, uint32_t(tid), 1);
   if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (tid < min(total, S)) issue(mine_ent, uint32_t(tid), 2);
-  __syncthreads();   // the schedule and the turn counters are complete
+  if (early_unit) issue(early_ent, uint32_t(lane), 2);
+  if (tid >= early && tid < min(total, S)) issue(mine_ent, uint32_t(tid), 2);
+  __syncthreads();   // the schedule is complete
 
   if (warp == RING) {
     // ---- the reducer warp ------------------------------------------------------------------------
