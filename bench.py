@@ -418,7 +418,10 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
     single_ms, single_launches = None, 0
     if "projection" in modes:
         native.set_gemv_launch_overlap(True)
-        calls = [[artifact.prepare(xs[j], p, s) for j, (p, s) in enumerate(group)] for group in weights.sets]
+        table_module.set_launch_overlap(True)   # (M = 3 .. 8 run as a table of one problem inside the entry)
+        single = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(device.index),
+                            constexprs={"GROUP_SIZE": GROUP, "ZERO_POINT": 8, "ACT_DTYPE": "f16"})
+        calls = [[single.prepare(xs[j], p, s) for j, (p, s) in enumerate(group)] for group in weights.sets]
 
         def projection_step(i: int) -> None:
             for call in calls[i % copies]:
@@ -429,6 +432,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
             for call in group:
                 call.check()
         native.set_gemv_launch_overlap(False)
+        table_module.set_launch_overlap(False)
         del calls
 
     # ---- end to end: host activations in, results back, one table launch per step --------------------

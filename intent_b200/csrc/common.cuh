@@ -170,4 +170,10 @@ struct Elem<__nv_bfloat16> {
 
 #endif  // __CUDACC__
 
+// w4a16_table.cu: one small contraction as a table of one problem (kTableDeclined: not that kind of call)
+constexpr int kTableDeclined = -77001;
+int w4a16_table_single_f16(View2, View2, View2, View2, int, int, void*, int64_t, cudaStream_t);
+int w4a16_table_single_bf16(View2, View2, View2, View2, int, int, void*, int64_t, cudaStream_t);
+int64_t w4a16_table_single_workspace_bytes(int64_t M, int64_t K, int64_t N);
+
 }  // namespace ib200

@@ -81,11 +81,17 @@ extern "C" const char* intent_b200_status_string(int status) {
 
 extern "C" int64_t intent_b200_launch_count(void) { return ib200::g_launches.load(std::memory_order_relaxed); }
 
-#define IB200_W4A16_ENTRY(NAME, TYPE, SELECT)                                                              \
+#define IB200_W4A16_ENTRY(NAME, TYPE, SELECT, TABLE)                                                              \
   extern "C" int NAME(INTENT_B200_VIEW2(a0), INTENT_B200_VIEW2(a1), INTENT_B200_VIEW2(a2),                \
                       INTENT_B200_VIEW2(a3), int32_t group_size, int32_t zero_point, void* workspace,     \
                       int64_t workspace_bytes, void* stream) {                                            \
     const bool skinny = SELECT;                                                                           \
+    if (skinny && (TABLE)) {                                                                              \
+      const int status = ib200::w4a16_table_single_##TYPE(                                                \
+          IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2), IB200_VIEW2_ARG(a3), group_size, \
+          zero_point, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));                     \
+      if (status != ib200::kTableDeclined) return status;                                                 \
+    }                                                                                                     \
     if (skinny)                                                                                           \
       return ib200::w4a16_stream_##TYPE(IB200_VIEW2_ARG(a0), IB200_VIEW2_ARG(a1), IB200_VIEW2_ARG(a2),    \
                                         IB200_VIEW2_ARG(a3), group_size, zero_point, workspace,           \
@@ -95,15 +101,18 @@ extern "C" int64_t intent_b200_launch_count(void) { return ib200::g_launches.loa
                                     static_cast<cudaStream_t>(stream));                                   \
   }
 
-IB200_W4A16_ENTRY(intent_b200_weight_only_int4_matmul_f16, f16, a0_d0 <= ib200::kSkinnyMaxM)
-IB200_W4A16_ENTRY(intent_b200_weight_only_int4_matmul_bf16, bf16, a0_d0 <= ib200::kSkinnyMaxM)
-IB200_W4A16_ENTRY(intent_b200_w4a16_gemv_f16, f16, true)
-IB200_W4A16_ENTRY(intent_b200_w4a16_gemv_bf16, bf16, true)
-IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_f16, f16, false)
-IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_bf16, bf16, false)
+IB200_W4A16_ENTRY(intent_b200_weight_only_int4_matmul_f16, f16, a0_d0 <= ib200::kSkinnyMaxM, a0_d0 >= 2)
+IB200_W4A16_ENTRY(intent_b200_weight_only_int4_matmul_bf16, bf16, a0_d0 <= ib200::kSkinnyMaxM, a0_d0 >= 2)
+IB200_W4A16_ENTRY(intent_b200_w4a16_gemv_f16, f16, true, false)
+IB200_W4A16_ENTRY(intent_b200_w4a16_gemv_bf16, bf16, true, false)
+IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_f16, f16, false, false)
+IB200_W4A16_ENTRY(intent_b200_w4a16_gemm_bf16, bf16, false, false)
 
 extern "C" int64_t intent_b200_weight_only_int4_matmul_workspace_bytes(int64_t M, int64_t K, int64_t N) {
-  return M <= ib200::kSkinnyMaxM ? ib200::w4a16_stream_workspace_bytes(M, K, N) : 0;
+  if (M > ib200::kSkinnyMaxM) return 0;
+  const int64_t stream_bytes = ib200::w4a16_stream_workspace_bytes(M, K, N);
+  const int64_t table_bytes = ib200::w4a16_table_single_workspace_bytes(M, K, N);   // 0 unless it can run as a table of one
+  return stream_bytes > table_bytes ? stream_bytes : table_bytes;
 }
 
 // ---------------------------------------------------------------------------------------------

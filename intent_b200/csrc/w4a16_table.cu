@@ -1499,7 +1499,58 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
   return INTENT_B200_OK;
 }
 
+int g_single_through_table = 1;   // a single small problem runs as a table of one (0 = never; for measurement)
+
+bool plain_matrix(const View2& v) { return v.p != nullptr && v.s1 == 1 && v.s0 == v.d1; }
+
 }  // namespace
+
+// A single contraction of at most eight rows as a table of one problem, for the entries that take one problem
+// and a workspace: w4a16_ride_kernel handles M = 3 .. 8 far better than the single-problem bandwidth kernel.
+// Returns kTableDeclined when the call is not of that kind (the caller then uses its own kernel, which also
+// produces the proper error for invalid arguments).
+int64_t w4a16_table_single_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+  if (M <= 0 || M > kRideRows || K <= 0 || N <= 0 || K > (1 << 24) || N > (1 << 24)) return 0;
+  const int sms = table_sms();
+  int64_t most = 0;
+  for (int group : {32, 64, 128}) {
+    if (K % group) continue;
+    HostProblem h{nullptr, nullptr, nullptr, nullptr, M, K, N};
+    ProblemPlan plan;
+    size_t offset;
+    const int64_t need = table_workspace(&h, 1, group, sms > 0 ? sms : 148, &plan, &offset);
+    if (need > most && plan.ride) most = need;
+  }
+  return most;
+}
+
+template <typename T>
+int table_single(View2 x, View2 w, View2 s, View2 y, int group_size, int zero_point, void* workspace,
+                 int64_t workspace_bytes, cudaStream_t stream) {
+  if (!g_single_through_table || !g_table_ride) return kTableDeclined;
+  if (!plain_matrix(x) || !plain_matrix(w) || !plain_matrix(s) || !plain_matrix(y)) return kTableDeclined;
+  if (group_size != 32 && group_size != 64 && group_size != 128) return kTableDeclined;
+  const int64_t M = x.d0, K = x.d1, N = w.d1;
+  if (M < 1 || M > kRideRows || K <= 0 || K % group_size || w.d0 * 8 != K || s.d0 * group_size != K || s.d1 != N ||
+      y.d0 != M || y.d1 != N || N % 8)
+    return kTableDeclined;
+  HostProblem h{x.p, w.p, s.p, y.p, M, K, N};
+  if (validate(h, group_size) != INTENT_B200_OK) return kTableDeclined;
+  const int grid = table_sms();
+  if (grid <= 0) return kTableDeclined;
+  ProblemPlan plan;
+  size_t offset;
+  const int64_t need = table_workspace(&h, 1, group_size, grid, &plan, &offset);
+  if (need < 0 || !plan.ride || !workspace || workspace_bytes < need) return kTableDeclined;
+  return run_table<T>(&h, 1, group_size, zero_point, workspace, workspace_bytes, stream);
+}
+
+int w4a16_table_single_f16(View2 x, View2 w, View2 s, View2 y, int g, int zp, void* ws, int64_t bytes, cudaStream_t stream) {
+  return table_single<__half>(x, w, s, y, g, zp, ws, bytes, stream);
+}
+int w4a16_table_single_bf16(View2 x, View2 w, View2 s, View2 y, int g, int zp, void* ws, int64_t bytes, cudaStream_t stream) {
+  return table_single<__nv_bfloat16>(x, w, s, y, g, zp, ws, bytes, stream);
+}
 }  // namespace ib200
 
 static_assert(sizeof(intent_b200_w4a16_problem) == sizeof(ib200::HostProblem), "table entry layout");
@@ -1543,7 +1594,8 @@ extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
   return INTENT_B200_OK;
 }
 
-// Measurement knobs (process-global): "slots" = upper limit on the ring's slots (0 = the built-in choice);
+// Measurement knobs (process-global): "single" 0 = the single-problem entries never run as a table of one;
+// "slots" = upper limit on the ring's slots (0 = the built-in choice);
 // "probe" 1 = every unit's arithmetic is skipped, 2 = the reduction too, 3 = only the packed weights are loaded,
 // 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over
 // (the results are WRONG by design for every value but 0: these launches only show where the time goes).
@@ -1554,6 +1606,10 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
     for (; name[i] && knob[i] == name[i]; ++i) {}
     return name[i] == 0 && knob[i] == 0;
   };
+  if (is("single") && (value == 0 || value == 1)) {
+    ib200::g_single_through_table = value;
+    return INTENT_B200_OK;
+  }
   if (is("slots") && (value == 0 || (value >= 8 && value <= 64))) {
     ib200::g_table_slots = value;
     return INTENT_B200_OK;

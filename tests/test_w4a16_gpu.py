@@ -175,8 +175,17 @@ def test_call_modes_prepare_launch_graph_and_torch_op(cuda_device):
     assert artifact.observation is not None and artifact.observation.status == 0
     # resource facts of the selected kernel instance (from a dry run of the same slots; nothing is launched)
     seen = call.observation
-    assert seen.kernel.startswith("w4a16_stream_kernel") and seen.threads in (512, 1024) and seen.grid >= 1
-    assert 0 < seen.registers <= 255 and seen.spill_bytes == 0 and seen.shared_dynamic > 0 and seen.cluster == 1
+    # four rows: the entry runs the problem as a table of one in the ride-along kernel
+    assert seen.kernel.startswith("w4a16_ride_kernel") and seen.threads == 1024 and seen.grid >= 1
+    assert 0 < seen.registers <= 64 and seen.shared_dynamic > 0 and seen.cluster == 1
+    # one row: the single-problem bandwidth kernel
+    one = artifact.prepare(xd[:1].contiguous(), pd, sd)
+    one.launch()
+    torch.cuda.synchronize()
+    assert one.observation.kernel.startswith("w4a16_stream_kernel") and one.observation.threads in (512, 1024)
+    assert one.observation.spill_bytes == 0
+    # (the two kernels add in different orders: equal up to rounding, not bit for bit)
+    assert (one.result().float() - expected[:1].float()).abs().max() <= 2e-2 * expected.float().abs().max()
     # torch custom operator with a fake implementation
     op = artifact.as_torch_op("intent_b200_test::w4a16")
     assert torch.equal(op(xd, pd, sd), expected)
