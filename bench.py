@@ -303,6 +303,49 @@ class DecodeWeights:
         self.sets = [[(p.to(device), s.to(device)) for p, s in self.host] for _ in range(self.copies)]
 
 
+def run_ring_probe(device) -> dict:
+    """Diagnostic, not a benchmark line: what the bare slot ring of the decode kernels streams from HBM
+    (``intent_b200_ring_probe_ms``: TMA boxes of 32 x 32 words into a per-SM ring, no arithmetic), for the two
+    decode weight shapes, three ring depths, and with a fence or an atomic every 24th unit of a CTA."""
+    import ctypes
+
+    import torch
+
+    from intent_b200.runtime import native
+
+    probe = native.library().intent_b200_ring_probe_ms
+    probe.restype = ctypes.c_double
+    probe.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                      ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    planes = 16                                   # 16 x 29.4 MB: larger than L2
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    scratch = torch.zeros(8192 + sms * 8192, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device).cuda_stream
+    modes = {0: "nothing", 1: "__threadfence()", 2: "stores + atom.acq_rel.gpu", 3: "stores + relaxed atomic",
+             4: "stores + atom.release.gpu", 5: "stores + relaxed red"}
+    out = {"workload": "tma_ring_probe", "planes": planes, "sync_every": 24, "unit": "GB/s", "results": []}
+    for K, N in DECODE_SHAPES:
+        rows = K // 8
+        matrices = torch.randint(0, 2 ** 31 - 1, (planes, rows, N), dtype=torch.int32, device=device)
+        nbytes = matrices.numel() * 4
+        cases = [(slots, 0) for slots in (16, 32, 48)] + [(32, mode) for mode in range(1, 6)]
+        for slots, mode in cases:
+            best = None
+            for attempt in range(6):
+                ms = float(probe(matrices.data_ptr(), planes, rows, N, slots, mode, 24, scratch.data_ptr(), stream))
+                if ms < 0:
+                    raise RuntimeError(f"intent_b200_ring_probe_ms failed with status {int(-ms)}")
+                if attempt > 0:
+                    best = ms if best is None else min(best, ms)
+            if int(scratch[:4].view(torch.int32).item()) != 0:
+                raise RuntimeError("a bounded wait of the ring probe gave up")
+            scratch.zero_()
+            out["results"].append({"rows": rows, "cols": N, "slots": slots, "every_24th_unit": modes[mode],
+                                   "us_per_launch": round(best * 1e3, 1), "GBps": round(nbytes / (best * 1e-3) / 1e9)})
+        del matrices
+    return out
+
+
 def run_decode(args, rank: int, world: int, device, M: int | None = None, weights: DecodeWeights | None = None,
                steps: int | None = None, load_seconds: float | None = None):
     """One decode step = up projection + down projection.  Measured three ways, all with cold weights and
@@ -1319,7 +1362,7 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--workload", default="prefill", choices=["prefill", "decode", "w8a8", "moe", "grouped"])
+    parser.add_argument("--workload", default="prefill", choices=["prefill", "decode", "w8a8", "moe", "grouped", "ring"])
     parser.add_argument("--batch", type=int, default=1, help="decode batch M (1, 4, 8)")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference", "triton"])
     parser.add_argument("--load-seconds", type=float, default=1.5)
@@ -1356,7 +1399,7 @@ def main() -> int:
                              "projection); '' = none (for profiling)")
     args = parser.parse_args()
     if args.steps is None:
-        args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20, "grouped": 50}[args.workload]
+        args.steps = {"prefill": 50, "decode": 200, "w8a8": 100, "moe": 20, "grouped": 50, "ring": 1}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.no_decode:
@@ -1394,6 +1437,10 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    if args.workload == "ring":
+        if rank == 0:
+            print(json.dumps(run_ring_probe(device)), flush=True)
+        return 0
     cpu_wanted = rank == 0 and world == 1 and not args.no_cpu_baseline
     if args.workload == "decode":
         line, extra = run_decode(args, rank, world, device), {}

@@ -83,8 +83,10 @@ INTENT_B200_API int intent_b200_observe_end(void);
  * Y[m,n] = T( sum_k f32(X[m,k]) * f32(w[k,n]) ), f32 accumulation.
  * K must be positive (an empty contraction returns INTENT_B200_ERR_UNSUPPORTED;
  * M == 0 or N == 0 succeed without a launch).
- * The plain entries pick the kernel from M (bandwidth kernel for M <= 16,
- * tcgen05 tensor-core kernel above); the _gemv / _gemm entries force one.
+ * The plain entries pick the kernel from M (M = 1: the single-problem bandwidth
+ * kernel; M = 2 .. 8: the ride-along kernel of the table entries below, as a table
+ * of one problem; M = 9 .. 16: the bandwidth kernel; above: the tcgen05 tensor-core
+ * kernel); the _gemv / _gemm entries force the bandwidth / tensor-core kernel.
  *
  * workspace: device scratch of at least ..._workspace_bytes(M, K, N) bytes,
  * 16-byte aligned (NULL / 0 when that query returns 0).  It must be zero-filled
@@ -135,7 +137,9 @@ INTENT_B200_API int intent_b200_w4a16_gemv_warps(int32_t warps);
 
 /* ------------------------------------------------------------------------
  * weight_only_int4_matmul over a TABLE of independent problems in one persistent launch
- * (same program and numerics as intent_b200_w4a16_gemv_*, M <= 16 per problem).  The
+ * (same program and numerics as intent_b200_w4a16_gemv_*, M <= 16 per problem; the order of the
+ * additions over K differs between the kernels, so results agree to rounding, not bit for bit;
+ * every kernel is bitwise reproducible from launch to launch).  The
  * reference launches one kernel per contraction (python/intent/runtime/artifact.py:130-136);
  * a decode step's projections are small enough that launch ramp and drain cost as much as
  * the weight stream itself, so several of them can share one launch here: the weight stream
@@ -165,14 +169,27 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_bf16(const intent_b200_w4a16_pr
                                                       int64_t workspace_bytes, void* stream);
 /* Programmatic dependent launch for the table entries (see intent_b200_w4a16_gemv_overlap); process-global. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_overlap(int32_t enable);
-/* Problems of at most two rows use the form of the table kernel in which every unit brings its own
- * activations and no CTA-wide barrier separates the problems; 0 forces the staged form for them too.
- * For measurement and tests; process-global; set it before querying the workspace size. */
+/* Problems of at most eight rows run in the ride-along kernel (every unit brings its own activations, the
+ * warps take units by ticket, no CTA-wide barrier separates the problems); 0 forces the staged kernel for
+ * them too.  For measurement and tests; process-global; set it before querying the workspace size. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
-/* Measurement knobs of that form (process-global): "warps" 16 | 32 | 0 = built-in choice; "areas" 2 | 4 partial
- * areas, 0 = built-in choice; "probe" 1 = stream-only launch (the arithmetic of every unit is skipped, so the
- * results are WRONG by design: it shows what the slot ring alone can stream), 0 = normal. */
+/* Measurement knobs (process-global): "single" 0 = intent_b200_weight_only_int4_matmul_* never runs a problem
+ * of two to eight rows as a table of one (1 = it does: the default); "slots" = upper limit on the slot ring
+ * (8 .. 64, 0 = built-in choice); "probe" 1 = the arithmetic of every unit is skipped, 2 = the reduction too,
+ * 3 = only the packed weights are loaded, 4 / 5 = arithmetic skipped and the reduction stops after the segment
+ * sums / before the cross-CTA hand-over.  Every probe value but 0 gives WRONG results by design: such launches
+ * only show where the time goes. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value);
+/* Measurement only, no counterpart in the reference: the bare skeleton of the decode kernels - one CTA per SM,
+ * a ring of `slots` 4 KiB shared-memory slots filled by TMA boxes of 32 x 32 words, no arithmetic - streams
+ * `planes` contiguous [rows][cols] int32 matrices once and returns the milliseconds of that launch (or minus a
+ * status code).  sync_mode adds, every sync_every-th unit of a CTA: 1 = __threadfence(); 2 = eight 16-byte
+ * stores + atom.acq_rel.gpu; 3 = the stores + a relaxed atomic; 4 = the stores + atom.release.gpu; 5 = the
+ * stores + a relaxed reduction; 0 = nothing.  rows, cols multiples of 32; slots 16, 32 or 48; scratch = at
+ * least 8192 + SMs * 8192 bytes of zero-filled device memory (word 0 is non-zero afterwards if a wait gave up). */
+INTENT_B200_API double intent_b200_ring_probe_ms(const void* matrices, int32_t planes, int32_t rows, int32_t cols,
+                                                 int32_t slots, int32_t sync_mode, int32_t sync_every, void* scratch,
+                                                 void* stream);
 
 /* ------------------------------------------------------------------------
  * Tiled copy of a packed int4 weight for the tensor-core kernels.  The caller-visible format stays the

@@ -188,3 +188,26 @@ def test_table_entry_through_raw_c_abi(cuda_device):
     assert int(workspace[:4].view(torch.int32)[0]) == 0                                               # status word
     rows[1].K = 14336 + 8                                                                             # not a multiple of the group
     assert entry(rows, 2, 128, 8, ctypes.c_void_p(workspace.data_ptr()), need, stream) == 3
+
+
+def test_ring_probe_entry(cuda_device):
+    """The measurement entry behind the decode kernels' design notes: streams matrices through the bare slot
+    ring and returns a time; its bounded waits leave the status word at zero."""
+    import ctypes
+
+    from intent_b200.runtime import native
+    probe = native.library().intent_b200_ring_probe_ms
+    probe.restype = ctypes.c_double
+    probe.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                      ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    matrices = torch.randint(0, 2 ** 31 - 1, (3, 96, 512), dtype=torch.int32, device=cuda_device)
+    scratch = torch.zeros(8192 + sms * 8192, dtype=torch.uint8, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    for slots, mode in ((16, 0), (32, 3), (48, 2), (32, 1), (16, 5), (32, 4)):
+        ms = probe(matrices.data_ptr(), 3, 96, 512, slots, mode, 2, scratch.data_ptr(), stream)
+        assert ms > 0
+        assert int(scratch[:4].view(torch.int32).item()) == 0
+    assert probe(matrices.data_ptr(), 3, 96, 500, 16, 0, 2, scratch.data_ptr(), stream) < 0     # cols not a multiple of 32
+    assert probe(matrices.data_ptr(), 3, 96, 512, 24, 0, 2, scratch.data_ptr(), stream) < 0      # slots not a multiple of 16
+    assert probe(None, 3, 96, 512, 16, 0, 2, scratch.data_ptr(), stream) < 0
