@@ -503,8 +503,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
     e2e_s = reduce_max(e2e_s, world, device)
 
     # The headline is a decode step served the fastest way the library offers for it: both projections in one
-    # table launch, or one launch per projection (for more than two rows per problem the single-problem
-    # kernel is still the faster one); the line says which.
+    # table launch, or one launch per projection; the line says which.
     table_ms, table_launches = elapsed_ms, launches
     best = "table_one_launch_per_step"
     if single_ms is not None and single_ms < elapsed_ms:
@@ -543,7 +542,7 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
                      "traffic": None, "traffic_note": "see profiles/ for the ncu capture of this kernel",
                      "peak_source": peaks["source"], "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "algorithmic_bytes_per_launch": per_launch_bytes,
-                     "kernel": "w4a16_table_kernel" if single_launch else "w4a16_stream_kernel",
+                     "kernel": "w4a16_ride_kernel" if single_launch or M >= 2 else "w4a16_stream_kernel",
                      "us_per_launch": round(per_launch_s * 1e6, 3),
                      "us_per_projection": round(ms_per_step * 1e3 / len(DECODE_SHAPES), 3)},
         "headline_mode": best,

@@ -12,41 +12,39 @@
 // rows (256 k, 4 KiB) and the units of a problem are split evenly over the CTAs (+-1).  A CTA owns a
 // ring of S shared-memory slots (S is chosen per launch); unit number g of the CTA's sequence - the
 // concatenation of its shares of all problems - lands in slot g % S through one 128B-swizzled TMA box
-// (plus a box of its scales) on the slot's mbarrier, is consumed by ring warp g % RING, and that warp
-// then requests unit g + S into the same slot, whichever problem it belongs to.
+// (plus a box of its scales) on the slot's mbarrier, and the warp that consumed it requests unit g + S
+// into the same slot, whichever problem that belongs to.
 //
-// Unit order inside a problem.  K is cut into chunk blocks of `cb` chunks (cb = all chunks when the
-// activations of the whole K range fit in shared memory, smaller for larger M); units are numbered
-// block-major, then column tile, then chunk.  A CTA's share is therefore a run of whole "spans"
-// (one column tile x one chunk block) plus a partial span at either end, and the activations it needs
-// are those of at most a few neighbouring chunk blocks: they are staged once per problem, permuted to
-// the nibble-pair order (w4a16_expand.cuh), together with the per-group correction sums.
+// Two kernels share this frame.
 //
-// Reduction over K, fixed order (bitwise reproducible):
+// w4a16_ride_kernel (problems of at most eight rows; described in full above its definition): every
+// unit's TMA transaction also brings the 256 activations per row it needs, so nothing is staged and
+// there is no CTA-wide barrier after start-up; the unit-to-problem bookkeeping is a schedule in shared
+// memory built once; ring warps take units by ticket; a span's K range is one piece ("chunk block").
+//
+// w4a16_table_kernel (more rows, or every problem when the ride-along kernel is switched off): K is
+// cut into chunk blocks of `cb` chunks (cb = all chunks when the activations of the whole K range fit
+// in shared memory, smaller for larger M); units are numbered block-major, then column tile, then
+// chunk.  A CTA's share is therefore a run of whole "spans" (one column tile x one chunk block) plus a
+// partial span at either end, and the activations it needs are those of at most a few neighbouring
+// chunk blocks: they are staged once per problem, permuted to the nibble-pair order
+// (w4a16_expand.cuh), together with the per-group correction sums, between two CTA-wide barriers.
+// Its reduction over K, fixed order (bitwise reproducible):
 //   1. units of one span inside one CTA: per-unit partials [M x 32] f32 in shared memory, a shared
 //      ticket per span, the warp with the last ticket adds them in chunk order;
-//   2. a span shared by neighbouring CTAs: each publishes ONE partial to global scratch; staged form:
-//      and takes a ticket on the span's global counter, the last one adds the partials in CTA order;
-//      ride-along form: the CTA that holds the span's end hands its own sum to its reducer warp, which
-//      waits for the others' and adds them in CTA order (the ring warps never wait for global memory);
+//   2. a span shared by neighbouring CTAs: each publishes ONE partial to global scratch and takes a
+//      ticket on the span's global counter; the last one adds the partials in CTA order;
 //   3. several chunk blocks: the block sums of a column tile meet the same way on the tile's counter
 //      and are added in block order.
+//
 // No memory fence at GPU scope anywhere: such a fence makes the SM wait for all its loads in flight
-// (measured on a bare ring: two per 48 units cost a quarter of the stream).  Published partials carry
-// their own validity instead (publish / take_published).  Counters and scratch are left at zero for
-// the next launch.  Partial spans at the ends of a CTA's share are processed first.
+// (measured on a bare ring, ring_probe.cu: two per 48 units cost a quarter of the stream).  Partial
+// sums published for another CTA carry their own validity instead (publish / take_published), and
+// tickets are relaxed atomics.  Counters and scratch are left at zero for the next launch.  Partial
+// spans at the ends of a CTA's share are processed first.
 //
-// Two forms of the kernel.  STAGED (above): a CTA-wide barrier on either side of the staging of every
-// problem.  RIDE (problems of at most two rows): every unit's TMA transaction also brings the 256
-// activations per row it needs, the consuming warp derives the correction sums of its unit from them, and
-// nothing is staged - so there is no CTA-wide barrier after start-up and the warps drift apart instead of
-// re-synchronising at every problem (a ring whose slots are all requested and consumed in lock-step leaves
-// HBM idle while it computes).  Per-problem partial areas rotate through two buffers; a warp writes its
-// first partial of problem i + 2 only after every ring warp has left problem i (a bounded wait on a shared
-// counter).  The last warp of the CTA is the reducer of cut spans and takes no units.
-//
-// Every mbarrier wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the
-// workspace's status word, the CTA skips its remaining units (still meeting its barriers) and exits.
+// Every wait is bounded; a wait that gives up records INTENT_B200_ERR_TIMEOUT in the workspace's
+// status word, the CTA skips its remaining units (still meeting its barriers) and exits.
 #include <type_traits>
 
 #include "common.cuh"

@@ -154,8 +154,9 @@ def set_launch_overlap(enabled: bool) -> None:
 
 
 def set_ride_along(enabled: bool) -> None:
-    """Process-wide: problems of at most two rows use the barrier-free form of the table kernel in which
-    every unit brings its own activations (the default); False forces the staged form for them too.  For
-    measurement and tests; set it before ``prepare`` (the workspace layout depends on it)."""
+    """Process-wide: problems of at most eight rows run in the ride-along kernel, in which every unit brings
+    its own activations and no CTA-wide barrier separates the problems (the default); False forces the staged
+    kernel for them too.  For measurement and tests; set it before ``prepare`` (the workspace layout depends
+    on it)."""
     native.check(native.library().intent_b200_w4a16_gemv_table_ride(1 if enabled else 0),
                  "intent_b200_w4a16_gemv_table_ride")
