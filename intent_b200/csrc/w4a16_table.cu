@@ -596,14 +596,18 @@ w4a16_table_kernel(const __grid_constant__ TableMaps maps, const __grid_constant
 // ---------------------------------------------------------------------------------------------
 constexpr int kRideRows = 8;
 
-template <typename T, int STEPS>
+// UR = packed rows of a unit: 32 (a unit is 4 KiB of weights, as in the other kernels) or 64 (8 KiB: the
+// bookkeeping of a unit is paid once per 8 KiB; measured slower, only reachable through the tune entry).
+template <typename T, int STEPS, int UR>
 __global__ void __launch_bounds__(1024, 1)
 w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
   constexpr int THREADS = 1024, RING = 31;
   constexpr int RPG = 4 * STEPS;        // packed rows per quantisation group
-  constexpr int GPC = kRows / RPG;      // groups per unit
+  constexpr int GPC = UR / RPG;         // groups per unit
   constexpr int CP = 8;                 // row pitch of the correction table
   constexpr int kScaleBytes = GPC * 64;
+  constexpr int kUnitBytes = UR * kCols * 4;   // packed weights of a unit
+  constexpr int kHalves = UR / 32;             // activation boxes per unit (a TMA box is at most 256 elements wide)
   extern __shared__ unsigned char smem_raw[];
   __shared__ Share shares[kMaxProblems];
   __shared__ int acc_first[kMaxProblems];      // index of the problem's first segment accumulator
@@ -623,7 +627,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const int S = p.slots;
-  const uint32_t scale_base = base + uint32_t(S) * kWeightBytes;
+  const uint32_t scale_base = base + uint32_t(S) * kUnitBytes;
   const uint32_t bars = scale_base + uint32_t(S) * kScaleBytes;
   volatile int* uses = reinterpret_cast<volatile int*>(base_ptr + p.uses_offset);   // refills requested so far, per slot
   float* corr = reinterpret_cast<float*>(base_ptr + p.corr_offset);
@@ -642,17 +646,23 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
     const uint32_t bar = bars + slot * 8u;
     if (p.probe >= 3) {   // measurement: the packed weights alone
       if (what & 1) {
-        mbar_expect_tx(bar, kWeightBytes);
-        tma_load_2d(base + slot * kWeightBytes, &maps.w[i], tile * kCols, chunk * kRows, bar);
+        mbar_expect_tx(bar, kUnitBytes);
+        tma_load_2d(base + slot * kUnitBytes, &maps.w[i], tile * kCols, chunk * UR, bar);
       }
       return;
     }
     if (what & 1) {
-      mbar_expect_tx(bar, kWeightBytes + GPC * 64 + rows * 512u);
-      tma_load_2d(base + slot * kWeightBytes, &maps.w[i], tile * kCols, chunk * kRows, bar);
+      mbar_expect_tx(bar, kUnitBytes + GPC * 64 + rows * (512u * kHalves));
+      tma_load_2d(base + slot * kUnitBytes, &maps.w[i], tile * kCols, chunk * UR, bar);
       tma_load_2d(scale_base + slot * kScaleBytes, &maps.s[i], tile * kCols, chunk * GPC, bar);
     }
-    if (what & 2) tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes), &maps.x[i], chunk * 256, 0, bar);
+    if (what & 2) {
+      // the unit's activations: per half of the unit a box [rows][256 values]
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h)
+        tma_load_2d(xbox_base + slot * uint32_t(p.xbox_bytes) + uint32_t(h) * rows * 512u, &maps.x[i],
+                    (chunk * kHalves + h) * 256, 0, bar);
+    }
   };
   // this CTA's share of problem q (everything but its place in the sequence)
   auto share_of = [&](const TableProblem& q) {
@@ -865,9 +875,10 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       }
       break;
     }
-    const uint32_t wslot = base + slot * kWeightBytes;
+    const uint32_t wslot = base + slot * kUnitBytes;
     const uint32_t sslot = scale_base + slot * kScaleBytes;
     const uint32_t xslot = xbox_base + slot * uint32_t(p.xbox_bytes);
+    const uint32_t xhalf = uint32_t(M) * 512u;   // bytes of one activation box
     float facc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) facc[i] = 0.f;
@@ -876,8 +887,9 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
       // lane L takes packed row L of the unit's activations (8 values of one row of X), puts it back in the
       // nibble-pair order the MMA fragments are read in, and the rows of a group (RPG adjacent lanes) add
       // their share of the correction sum  - sum_k x[m,k] * (bias_k + 8)  with a fixed-order butterfly
-      for (int m = 0; m < M; ++m) {
-        const uint32_t addr = xslot + uint32_t(m) * 512u + uint32_t(lane) * 16u;
+      for (int mh = 0; mh < M * kHalves; ++mh) {
+        const int m = kHalves == 1 ? mh : mh >> 1, h = kHalves == 1 ? 0 : mh & 1;
+        const uint32_t addr = xslot + uint32_t(h) * xhalf + uint32_t(m) * 512u + uint32_t(lane) * 16u;
         const uint4 val = lds128(addr);
         uint4 o;
         o.x = prmt(val.x, val.z, 0x5410);                        // (k0, k4)
@@ -890,7 +902,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
                         Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
 #pragma unroll
         for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
-        if ((lane % RPG) == 0) my_corr[(lane / RPG) * CP + m] = -partial;
+        if ((lane % RPG) == 0) my_corr[((h * 32 + lane) / RPG) * CP + m] = -partial;
       }
       __syncwarp();
       // Rows of X beyond M: the lanes that would hold them read row M - 1 instead.  An MMA output column depends
@@ -911,7 +923,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
           const uint32_t off = STEPS >= 2 ? off_of[i] + uint32_t(gi * RPG * 128)
                                           : uint32_t(row) * 128u + (uint32_t(g ^ (row & 7)) << 4);
           const uint4 w = lds128(wslot + off);
-          const uint4 b = lds128(xrow + uint32_t(row) * 16u);
+          const uint4 b = lds128(xrow + uint32_t(row >> 5) * xhalf + uint32_t(row & 31) * 16u);
           uint32_t c0[4], c1[4], c2[4], c3[4];
           Expand<T>::word(w.x, magic_a, magic_b, c0);
           Expand<T>::word(w.y, magic_a, magic_b, c1);
@@ -1109,24 +1121,30 @@ struct ProblemPlan {
   int chunks, tiles, cb, nblocks, units, each, extra, maxp;
   bool ride;                                     // the ride-along form (no staging, no CTA barriers)
   int segments, sequence;                        // ride-along form: segment accumulators and schedule entries (worst CTA)
+  int unit_rows;                                 // packed rows of a unit: 32, or 64 in the ride-along form for few rows
   size_t xs_bytes, corr_bytes, part_bytes;       // shared memory this problem needs (worst CTA)
   size_t counters1, counters2, scratch1, scratch2, bytes;   // workspace layout (offsets) and size
 };
 
 // One slot of the ring: the packed weights, the unit's scales, the mbarrier and the use count.
-size_t slot_bytes(int group_size) { return size_t(kWeightBytes) + size_t(256 / group_size) * 64 + 8 + 4; }
+size_t slot_bytes(int group_size, int unit_rows = kRows) {
+  return size_t(unit_rows) * kCols * 4 + size_t(unit_rows * 8 / group_size) * 64 + 8 + 4;
+}
 // alignment slack + smallest ring + span tickets (one row per problem) + finished counters + rounding of the regions
 size_t fixed_bytes(int group_size) {
   return 1024 + size_t(kMinSlots) * slot_bytes(group_size) + 256 + kMaxProblems * kMaxSpans * 4 + 64 + 128;
 }
-constexpr size_t kRideCorrBytes = 32 * 8 * 8 * 4;    // ride-along form: per-warp correction sums, widest case (g32)
-constexpr int kMinRideSlots = 20;                    // the ride-along form is planned only if this many slots fit
+// ride-along form: per-warp correction sums of the unit in hand (32 warps x groups of a unit x 8 rows)
+size_t ride_corr_bytes(int group_size, int unit_rows) { return size_t(32) * (unit_rows * 8 / group_size) * 8 * 4; }
+int g_table_unit_rows = 0;   // 64 = the ride-along form uses 64-row units for problems of up to four rows; for measurement
+// the ride-along form is planned only if this many slots fit (about 80 KB of packed weights in flight per SM)
+int min_ride_slots(int unit_rows) { return unit_rows == 64 ? 12 : 20; }
 // ride-along form: what a launch needs in shared memory besides its slots
 int ride_chains(int rows) { return rows <= 2 ? 8 : 4; }        // chains per segment
 int ride_ring_shift(int rows) { return rows <= 4 ? 4 : 3; }     // log2 of the chain sets that exist at a time
-size_t ride_other_bytes(size_t sequence, int rows) {
+size_t ride_other_bytes(size_t sequence, int rows, size_t corr_bytes) {
   const size_t sets = size_t(1) << ride_ring_shift(rows);
-  return 1024 + 512 + kRideCorrBytes + sets * (ride_chains(rows) * (size_t(rows) * kCols * 4 + 4) + 4) + sequence * 16;
+  return 1024 + 512 + corr_bytes + sets * (ride_chains(rows) * (size_t(rows) * kCols * 4 + 4) + 4) + sequence * 16;
 }
 
 // Spans a CTA may touch and rows it must stage, worst case over CTAs, for a chunk-block size.
@@ -1143,29 +1161,42 @@ void share_bounds(int tiles, int chunks, int cb, int n_max, int* blocks_touched,
 bool plan_problem(int M, int K, int N, int group_size, int grid, bool allow_ride, ProblemPlan* out) {
   ProblemPlan q{};
   const size_t smem_budget = size_t(kSmemLimit) - fixed_bytes(group_size);
-  q.tiles = (N + kCols - 1) / kCols;
-  q.chunks = (K / 8 + kRows - 1) / kRows;
-  if ((long long)q.tiles * q.chunks > (1ll << 30)) return false;   // unit numbers are 32-bit
-  q.units = q.tiles * q.chunks;
-  q.each = q.units / grid;
-  q.extra = q.units % grid;
-  const int n_max = q.each + (q.extra ? 1 : 0);
+  int n_max = 0;
+  const auto geometry = [&](int unit_rows) {
+    q.unit_rows = unit_rows;
+    q.tiles = (N + kCols - 1) / kCols;
+    q.chunks = (K / 8 + unit_rows - 1) / unit_rows;
+    if ((long long)q.tiles * q.chunks > (1ll << 30)) return false;   // unit numbers are 32-bit
+    q.units = q.tiles * q.chunks;
+    q.each = q.units / grid;
+    q.extra = q.units % grid;
+    n_max = q.each + (q.extra ? 1 : 0);
+    return true;
+  };
+  // ride-along form: the activations travel with every unit, the whole K range is one chunk block.  Units of
+  // 64 packed rows (the bookkeeping of a unit paid once per 8 KiB) are built but not chosen: measured slower
+  // (M = 1: 6.6 against 6.5 us per projection in a long table, 10.7 against 9.6 with one launch per step;
+  // M = 4: 9.1 against 7.7) - fewer slots than ring warps, and a longer wait for the first unit of a launch.
+  q.ride = false;
+  for (int unit_rows : {64, 32}) {
+    if (!allow_ride || M > kRideRows || q.ride) break;
+    if (unit_rows == 64 && (M > 4 || g_table_unit_rows != 64)) continue;
+    if (!geometry(unit_rows)) return false;
+    int blocks, spans;
+    share_bounds(q.tiles, q.chunks, q.chunks, n_max, &blocks, &spans);
+    q.segments = spans;
+    q.sequence = n_max;
+    q.ride = n_max < 65536 && size_t(min_ride_slots(unit_rows)) * (slot_bytes(group_size, unit_rows) + size_t(M) * unit_rows * 16) +
+                                      ride_other_bytes(n_max, M, ride_corr_bytes(group_size, unit_rows)) <=
+                                  size_t(kSmemLimit);
+  }
+  if (!q.ride && !geometry(kRows)) return false;
   q.part_bytes = size_t(n_max) * M * kCols * 4;
   const int rpg = group_size / 8;
   int cb = q.chunks;
-  {
-    // ride-along form: the activations travel with every unit, the whole K range is one chunk block
-    int blocks, spans;
-    share_bounds(q.tiles, q.chunks, cb, n_max, &blocks, &spans);
-    q.segments = spans;
-    q.sequence = n_max;
-    q.ride = allow_ride && M <= kRideRows && n_max < 65536 &&
-             size_t(kMinRideSlots) * (slot_bytes(group_size) + size_t(M) * 512) + ride_other_bytes(n_max, M) <=
-                 size_t(kSmemLimit);
-  }
   if (q.ride) {
     q.xs_bytes = 0;
-    q.corr_bytes = kRideCorrBytes;
+    q.corr_bytes = ride_corr_bytes(group_size, q.unit_rows);
     q.part_bytes = 0;
   } else {
     // the largest chunk block whose staged activations (all blocks a CTA can touch) fit beside the rest
@@ -1250,9 +1281,9 @@ int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t s
   return launch_status();
 }
 
-template <typename T, int STEPS>
+template <typename T, int STEPS, int UR>
 int launch_ride(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
-  auto kernel = w4a16_ride_kernel<T, STEPS>;
+  auto kernel = w4a16_ride_kernel<T, STEPS, UR>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return cuda_status(e);
   cudaLaunchConfig_t config = {};
@@ -1348,21 +1379,25 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     size_t xs_max = 0, corr_max = 0, part_max = 0, sequence = 0, segments = 0;
     int n = 0, mb = 1, i = begin, rows_max = 0;
     bool ride = false;
+    int unit_rows = kRows;
     for (; i < count && n < kMaxProblems; ++i) {
       const int index = order[i];
       const HostProblem& h = problems[index];
       if (h.M <= 0 || h.N <= 0) continue;   // nothing to compute
       const ProblemPlan& q = plans[index];
-      if (n == 0) ride = q.ride;
-      if (q.ride != ride) break;            // a launch is one form of the kernel
+      if (n == 0) {
+        ride = q.ride;
+        unit_rows = q.unit_rows;
+      }
+      if (q.ride != ride || q.unit_rows != unit_rows) break;   // a launch is one form of the kernel
       {
         const size_t xs = q.xs_bytes > xs_max ? q.xs_bytes : xs_max;
         const size_t corr_b = q.corr_bytes > corr_max ? q.corr_bytes : corr_max;
         const size_t part_b = q.part_bytes > part_max ? q.part_bytes : part_max;
         const int rows = int(h.M) > rows_max ? int(h.M) : rows_max;
         if (ride) {
-          if (n > 0 && size_t(kMinRideSlots) * (slot_bytes(group_size) + size_t(rows) * 512) +
-                               ride_other_bytes(sequence + q.sequence, rows) >
+          if (n > 0 && size_t(min_ride_slots(unit_rows)) * (slot_bytes(group_size, unit_rows) + size_t(rows) * unit_rows * 16) +
+                               ride_other_bytes(sequence + q.sequence, rows, q.corr_bytes) >
                            size_t(kSmemLimit))
             break;
         } else if (n > 0 && xs + corr_b + part_b > behind_ring) {
@@ -1396,10 +1431,10 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
       d.scratch1 = reinterpret_cast<float*>(ws + offsets[index] + q.scratch1);
       d.scratch2 = reinterpret_cast<float*>(ws + offsets[index] + q.scratch2);
       if (!make_tensor_map_2d(&maps.w[n], CU_TENSOR_MAP_DATA_TYPE_INT32, h.w, uint64_t(h.K / 8), uint64_t(h.N),
-                              uint64_t(h.N) * 4, kRows, kCols, CU_TENSOR_MAP_SWIZZLE_128B,
+                              uint64_t(h.N) * 4, uint32_t(unit_rows), kCols, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B) ||
           !make_tensor_map_2d(&maps.s[n], xt, h.s, uint64_t(h.K / group_size), uint64_t(h.N), uint64_t(h.N) * 2,
-                              uint32_t(256 / group_size), kCols, CU_TENSOR_MAP_SWIZZLE_NONE))
+                              uint32_t(unit_rows * 8 / group_size), kCols, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INTENT_B200_ERR_UNSUPPORTED;
       if (ride && !make_tensor_map_2d(&maps.x[n], xt, h.x, uint64_t(h.M), uint64_t(h.K), uint64_t(h.K) * 2,
                                       uint32_t(h.M), 256, CU_TENSOR_MAP_SWIZZLE_NONE))
@@ -1428,14 +1463,14 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     p.status = reinterpret_cast<int*>(ws);
     // As many slots as fit beside this launch's other regions, up to the built-in choice.
     const auto round16 = [](size_t v) { return (v + 15) & ~size_t(15); };
-    p.xbox_bytes = ride ? rows_max * 512 : 0;
+    p.xbox_bytes = ride ? rows_max * unit_rows * 16 : 0;
     p.part_depth = 1;
     {
-      const size_t others = ride ? ride_other_bytes(sequence, rows_max)
+      const size_t others = ride ? ride_other_bytes(sequence, rows_max, corr_max)
                                  : 1024 + 256 + size_t(kMaxSpans) * 4 + 64 + 128 + round16(corr_max) + round16(xs_max) +
                                        round16(part_max);
       if (others >= size_t(kSmemLimit)) return INTENT_B200_ERR_UNSUPPORTED;
-      size_t slots = (size_t(kSmemLimit) - others) / (slot_bytes(group_size) + p.xbox_bytes);
+      size_t slots = (size_t(kSmemLimit) - others) / (slot_bytes(group_size, unit_rows) + p.xbox_bytes);
       // Staged form: a whole number of slots per warp (every slot then always belongs to the same warp, and no
       // warp has to check who used a slot before it).  Ride-along form: one slot per ring warp; measured on
       // M = 1, a deeper ring (40 slots) does not stream faster and a shallower one (24) hardly slower.
@@ -1450,7 +1485,7 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
       p.slots = int(slots);
       p.magic_slots = uint32_t(((1ll << 32) + p.slots - 1) / p.slots);
     }
-    size_t offset = size_t(p.slots) * (slot_bytes(group_size) - 4);
+    size_t offset = size_t(p.slots) * (slot_bytes(group_size, unit_rows) - 4);
     offset = (offset + 15) & ~size_t(15);
     p.uses_offset = int(offset);
     offset += size_t(p.slots) * 4;
@@ -1483,9 +1518,14 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
            : steps == 2 ? launch_table<T, MB_, 2>(maps, p, grid, smem, stream)           \
                         : launch_table<T, MB_, 1>(maps, p, grid, smem, stream);
     if (ride) {
-      status = steps == 4   ? launch_ride<T, 4>(maps, p, grid, smem, stream)
-               : steps == 2 ? launch_ride<T, 2>(maps, p, grid, smem, stream)
-                            : launch_ride<T, 1>(maps, p, grid, smem, stream);
+      if (unit_rows == 64)
+        status = steps == 4   ? launch_ride<T, 4, 64>(maps, p, grid, smem, stream)
+                 : steps == 2 ? launch_ride<T, 2, 64>(maps, p, grid, smem, stream)
+                              : launch_ride<T, 1, 64>(maps, p, grid, smem, stream);
+      else
+        status = steps == 4   ? launch_ride<T, 4, 32>(maps, p, grid, smem, stream)
+                 : steps == 2 ? launch_ride<T, 2, 32>(maps, p, grid, smem, stream)
+                              : launch_ride<T, 1, 32>(maps, p, grid, smem, stream);
     } else if (mb == 1) {
       IB200_TABLE_STEPS(1)
     } else {
@@ -1593,7 +1633,9 @@ extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
 }
 
 // Measurement knobs (process-global): "single" 0 = the single-problem entries never run as a table of one;
-// "slots" = upper limit on the ring's slots (0 = the built-in choice);
+// "slots" = upper limit on the ring's slots (0 = the built-in choice); "unit_rows" 64 = the ride-along kernel
+// uses units of 64 packed rows for problems of up to four rows (0 = built-in choice: 32; set it before querying
+// the workspace size);
 // "probe" 1 = every unit's arithmetic is skipped, 2 = the reduction too, 3 = only the packed weights are loaded,
 // 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over
 // (the results are WRONG by design for every value but 0: these launches only show where the time goes).
@@ -1606,6 +1648,10 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
   };
   if (is("single") && (value == 0 || value == 1)) {
     ib200::g_single_through_table = value;
+    return INTENT_B200_OK;
+  }
+  if (is("unit_rows") && (value == 0 || value == 64)) {
+    ib200::g_table_unit_rows = value;
     return INTENT_B200_OK;
   }
   if (is("slots") && (value == 0 || (value >= 8 && value <= 64))) {
