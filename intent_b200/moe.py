@@ -232,6 +232,19 @@ class MoEW4A16FFN:
                            full_positions, y, clear_positions)
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device):
+    """One extra stream per device for work that may overlap a contraction (created on first use)."""
+    import torch
+
+    key = torch.device(device).index
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[key]
+
+
 @dataclass
 class PreparedFusedFFN:
     """The chain with the weighted combine inside the down projection's epilogue (top_k <= 2)."""
@@ -254,14 +267,25 @@ class PreparedFusedFFN:
                 event.record()
                 marks.append(event)
 
+        import torch
+
+        side = None
+        if not accumulate:
+            # y is cleared on a second stream while the alignment, the gather and the up|gate contraction run:
+            # the fill is bound by HBM writes, the contraction by the tensor pipe (works inside a stream capture)
+            current = torch.cuda.current_stream(self.y.device)
+            side = _side_stream(self.y.device)
+            side.wait_stream(current)
+            with torch.cuda.stream(side):
+                self.y.zero_()
         mark()
         self.align.launch()
         mark()
         self.gather_call.launch()
         mark()
         self.up_call.launch()
-        if not accumulate:
-            self.y.zero_()
+        if side is not None:
+            current.wait_stream(side)
         mark()
         self.scatter_call.launch()
         mark()
