@@ -176,7 +176,9 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
 /* Measurement knobs (process-global): "single" 0 = intent_b200_weight_only_int4_matmul_* never runs a problem
  * of two to eight rows as a table of one (1 = it does: the default); "slots" = upper limit on the slot ring
  * (8 .. 64, 0 = built-in choice); "unit_rows" 64 = units of 64 packed rows for problems of up to four rows
- * (measured slower; 0 = the built-in 32; set it before querying the workspace size); "probe" 1 = the arithmetic of every unit is skipped, 2 = the reduction too,
+ * (measured slower; 0 = the built-in 32; set it before querying the workspace size); "corr_mma" 1 / 0 = the
+ * ride-along kernel takes its per-group correction sums from two extra MMAs per step / adds them up from the
+ * activations, -1 = built-in choice (MMAs for three rows and more); "probe" 1 = the arithmetic of every unit is skipped, 2 = the reduction too,
  * 3 = only the packed weights are loaded, 4 / 5 = arithmetic skipped and the reduction stops after the segment
  * sums / before the cross-CTA hand-over.  Every probe value but 0 gives WRONG results by design: such launches
  * only show where the time goes. */

@@ -598,7 +598,10 @@ constexpr int kRideRows = 8;
 
 // UR = packed rows of a unit: 32 (a unit is 4 KiB of weights, as in the other kernels) or 64 (8 KiB: the
 // bookkeeping of a unit is paid once per 8 KiB; measured slower, only reachable through the tune entry).
-template <typename T, int STEPS, int UR>
+// CORR_MMA (problems of three rows and more): the per-group correction sums come from two extra MMAs per step
+// whose weight operand is the constant bias, instead of being added up row by row from the activations (which
+// costs as many instructions per row as the whole permutation).
+template <typename T, int STEPS, int UR, bool CORR_MMA>
 __global__ void __launch_bounds__(1024, 1)
 w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant__ TableParams p) {
   constexpr int THREADS = 1024, RING = 31;
@@ -846,6 +849,9 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   }
   float* my_corr = corr + warp * (GPC * CP);  // this warp's correction sums of the unit in hand
   const bool skip_math = p.probe >= 1 && p.probe <= 5;
+  // the bias of an expanded nibble as a weight operand: even pairs (k0,k4), (k2,k6) and odd pairs (k1,k5), (k3,k7)
+  const uint32_t bias_even = uint32_t(Elem<T>::from_float(Expand<T>::kEven)) * 0x00010001u;
+  const uint32_t bias_odd = uint32_t(Elem<T>::from_float(Expand<T>::kOdd)) * 0x00010001u;
 
   for (;;) {
     if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
@@ -898,11 +904,13 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
         o.w = Expand<T>::scale_odd(prmt(val.y, val.w, 0x7632));  // (k3, k7)
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
                      : "memory");
-        float partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
-                        Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
+        if (!CORR_MMA) {
+          float partial = Expand<T>::kEven * (pair_sum<T>(o.x) + pair_sum<T>(o.z)) +
+                          Expand<T>::kOdd * (pair_sum<T>(o.y) + pair_sum<T>(o.w));
 #pragma unroll
-        for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
-        if ((lane % RPG) == 0) my_corr[((h * 32 + lane) / RPG) * CP + m] = -partial;
+          for (int d = RPG / 2; d >= 1; d >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, d);
+          if ((lane % RPG) == 0) my_corr[((h * 32 + lane) / RPG) * CP + m] = -partial;
+        }
       }
       __syncwarp();
       // Rows of X beyond M: the lanes that would hold them read row M - 1 instead.  An MMA output column depends
@@ -911,7 +919,11 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
 #pragma unroll
       for (int gi = 0; gi < GPC; ++gi) {
         float gacc[8];
-        {
+        float cacc[4] = {0.f, 0.f, 0.f, 0.f};   // CORR_MMA: sum over the group of bias_k * x[m, k] (every row the same)
+        if (CORR_MMA) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gacc[i] = 0.f;
+        } else {
           // (entries of rows >= M hold stale values: they only reach accumulator rows that are never stored)
           const float2 c = *reinterpret_cast<const float2*>(&my_corr[gi * CP + 2 * t]);
 #pragma unroll
@@ -935,6 +947,14 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
           Elem<T>::mma16816(a23, c2[0], c3[0], c2[1], c3[1], b.x, b.y);
           Elem<T>::mma16816(a01, c0[2], c1[2], c0[3], c1[3], b.z, b.w);
           Elem<T>::mma16816(a23, c2[2], c3[2], c2[3], c3[3], b.z, b.w);
+          if (CORR_MMA) {
+            Elem<T>::mma16816(cacc, bias_even, bias_even, bias_odd, bias_odd, b.x, b.y);
+            Elem<T>::mma16816(cacc, bias_even, bias_even, bias_odd, bias_odd, b.z, b.w);
+          }
+        }
+        if (CORR_MMA) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gacc[i] -= cacc[i & 1];
         }
         uint2 s;  // this lane's four column scales of the group (zero outside the matrix)
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(s.x), "=r"(s.y) : "r"(sslot + gi * 64 + g * 8));
@@ -1254,6 +1274,7 @@ int validate(const HostProblem& h, int group_size) {
 }
 
 int g_table_probe = 0;
+int g_table_corr_mma = -1;   // ride-along kernel: correction sums by MMA (1), from the activations (0), built-in choice (-1)
 int g_table_slots = 0;     // upper limit on the ring's slots (0 = the built-in choice); for measurement
 
 template <typename T, int MB, int STEPS>
@@ -1281,9 +1302,9 @@ int launch_table(const TableMaps& maps, const TableParams& p, int grid, size_t s
   return launch_status();
 }
 
-template <typename T, int STEPS, int UR>
+template <typename T, int STEPS, int UR, bool CORR_MMA>
 int launch_ride(const TableMaps& maps, const TableParams& p, int grid, size_t smem, cudaStream_t stream) {
-  auto kernel = w4a16_ride_kernel<T, STEPS, UR>;
+  auto kernel = w4a16_ride_kernel<T, STEPS, UR, CORR_MMA>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return cuda_status(e);
   cudaLaunchConfig_t config = {};
@@ -1518,14 +1539,19 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
            : steps == 2 ? launch_table<T, MB_, 2>(maps, p, grid, smem, stream)           \
                         : launch_table<T, MB_, 1>(maps, p, grid, smem, stream);
     if (ride) {
+      const bool corr_mma = g_table_corr_mma < 0 ? rows_max >= 3 : g_table_corr_mma != 0;
       if (unit_rows == 64)
-        status = steps == 4   ? launch_ride<T, 4, 64>(maps, p, grid, smem, stream)
-                 : steps == 2 ? launch_ride<T, 2, 64>(maps, p, grid, smem, stream)
-                              : launch_ride<T, 1, 64>(maps, p, grid, smem, stream);
+        status = steps == 4   ? launch_ride<T, 4, 64, false>(maps, p, grid, smem, stream)
+                 : steps == 2 ? launch_ride<T, 2, 64, false>(maps, p, grid, smem, stream)
+                              : launch_ride<T, 1, 64, false>(maps, p, grid, smem, stream);
+      else if (corr_mma)
+        status = steps == 4   ? launch_ride<T, 4, 32, true>(maps, p, grid, smem, stream)
+                 : steps == 2 ? launch_ride<T, 2, 32, true>(maps, p, grid, smem, stream)
+                              : launch_ride<T, 1, 32, true>(maps, p, grid, smem, stream);
       else
-        status = steps == 4   ? launch_ride<T, 4, 32>(maps, p, grid, smem, stream)
-                 : steps == 2 ? launch_ride<T, 2, 32>(maps, p, grid, smem, stream)
-                              : launch_ride<T, 1, 32>(maps, p, grid, smem, stream);
+        status = steps == 4   ? launch_ride<T, 4, 32, false>(maps, p, grid, smem, stream)
+                 : steps == 2 ? launch_ride<T, 2, 32, false>(maps, p, grid, smem, stream)
+                              : launch_ride<T, 1, 32, false>(maps, p, grid, smem, stream);
     } else if (mb == 1) {
       IB200_TABLE_STEPS(1)
     } else {
@@ -1635,7 +1661,8 @@ extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
 // Measurement knobs (process-global): "single" 0 = the single-problem entries never run as a table of one;
 // "slots" = upper limit on the ring's slots (0 = the built-in choice); "unit_rows" 64 = the ride-along kernel
 // uses units of 64 packed rows for problems of up to four rows (0 = built-in choice: 32; set it before querying
-// the workspace size);
+// the workspace size); "corr_mma" 1 / 0 = the ride-along kernel takes the correction sums from extra MMAs / adds
+// them up from the activations, -1 = built-in choice (MMAs for three rows and more);
 // "probe" 1 = every unit's arithmetic is skipped, 2 = the reduction too, 3 = only the packed weights are loaded,
 // 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over
 // (the results are WRONG by design for every value but 0: these launches only show where the time goes).
@@ -1652,6 +1679,10 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
   }
   if (is("unit_rows") && (value == 0 || value == 64)) {
     ib200::g_table_unit_rows = value;
+    return INTENT_B200_OK;
+  }
+  if (is("corr_mma") && value >= -1 && value <= 1) {
+    ib200::g_table_corr_mma = value;
     return INTENT_B200_OK;
   }
   if (is("slots") && (value == 0 || (value >= 8 && value <= 64))) {
