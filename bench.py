@@ -539,7 +539,12 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config, "notes": notes,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4),
-                     "traffic": None, "traffic_note": "see profiles/ for the ncu capture of this kernel",
+                     # ncu capture of the M = 1 step (one table launch of both projections, one GPU):
+                     # dram__bytes_read + dram__bytes_write = 60,649,984 + 103,936 (profiles/w4a16_ride_kernel_decode_gemv.md)
+                     "traffic": 60753920 if (M == 1 and best == "table_one_launch_per_step") else None,
+                     "traffic_note": ("ncu capture of the M = 1 table launch on one GPU (every rank runs the same "
+                                      "launch)" if (M == 1 and best == "table_one_launch_per_step")
+                                      else "captured for the M = 1 table launch only; see profiles/"),
                      "peak_source": peaks["source"], "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "algorithmic_bytes_per_launch": per_launch_bytes,
                      "kernel": "w4a16_ride_kernel" if single_launch or M >= 2 else "w4a16_stream_kernel",
