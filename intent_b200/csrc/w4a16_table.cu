@@ -87,18 +87,22 @@ struct TableParams {
   int twos_complement;
   int overlap;
   int* status;
-  // shared-memory layout behind the slot ring, sized for the largest problem of the table
-  int corr_offset, xs_offset, span_offset, part_offset;
-  // ride-along form: every unit brings its own activations (box of M x 256 values behind the scales)
-  int xbox_offset, xbox_bytes, finished_offset, part_stride;
-  int part_depth;     // ride-along form: partial areas the problems rotate through (2 or 4)
-  int slots;          // slots of the ring (as many as fit beside the other regions)
-  uint32_t magic_slots;
-  int uses_offset;    // per slot: how many times it has been requested (read only when slots % warps != 0)
-  int sched_offset;   // w4a16_ride_kernel: the CTA's schedule, 16 bytes per unit of its whole sequence
-  int chains, chain_shift;   // w4a16_ride_kernel: chains per segment (a power of two) and its logarithm
-  int acc_ring_shift;        // w4a16_ride_kernel: log2 of the number of segments whose chains exist at a time
-  int probe;          // measurement only: 1 = skip the arithmetic of every unit (stream and reduction traffic only)
+  // shared-memory layout behind the slot ring (byte offsets from the 1 KiB-aligned base), sized for the launch:
+  //   corr   correction sums (staged kernel: per staged group; ride-along kernel: per warp, of the unit in hand)
+  //   xs     staged kernel: the staged activations
+  //   span   staged kernel: span tickets; ride-along kernel: the chains' turn counters, then the sets' `done`
+  //   part   staged kernel: per-unit partial sums; ride-along kernel: the chains' accumulators
+  //   uses   per slot: how many refills have been requested (read when a slot is not tied to one warp)
+  //   xbox   ride-along kernel: per slot, the unit's activations ([rows][256] per 32 packed rows)
+  //   sched  ride-along kernel: the CTA's schedule, 16 bytes per unit of its whole sequence
+  int corr_offset, xs_offset, span_offset, part_offset, uses_offset, xbox_offset, sched_offset;
+  int xbox_bytes;            // bytes of one slot's activations
+  int part_stride;           // floats between partial areas (staged) / between chain accumulators (ride-along)
+  int slots;                 // slots of the ring
+  uint32_t magic_slots;      // ceil(2^32 / slots)
+  int chains, chain_shift;   // ride-along kernel: chains per segment (a power of two) and its logarithm
+  int acc_ring_shift;        // ride-along kernel: log2 of the number of segments whose chains exist at a time
+  int probe;                 // measurement only (intent_b200_w4a16_gemv_table_tune): parts of the work skipped
 };
 
 struct TableMaps {
@@ -1485,7 +1489,6 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     // As many slots as fit beside this launch's other regions, up to the built-in choice.
     const auto round16 = [](size_t v) { return (v + 15) & ~size_t(15); };
     p.xbox_bytes = ride ? rows_max * unit_rows * 16 : 0;
-    p.part_depth = 1;
     {
       const size_t others = ride ? ride_other_bytes(sequence, rows_max, corr_max)
                                  : 1024 + 256 + size_t(kMaxSpans) * 4 + 64 + 128 + round16(corr_max) + round16(xs_max) +
@@ -1519,8 +1522,6 @@ int run_table(const HostProblem* problems, int count, int group_size, int zero_p
     const size_t sets = size_t(1) << p.acc_ring_shift;
     p.span_offset = int(offset);    // staged: span tickets; ride-along: the chains' turn counters, then the sets' `done`
     offset += round16(ride ? sets * (p.chains + 1) * 4 : size_t(kMaxSpans) * 4);
-    p.finished_offset = int(offset);
-    offset += 64;
     p.corr_offset = int(offset);
     offset += round16(corr_max);
     p.xs_offset = int(offset);
