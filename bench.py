@@ -918,7 +918,19 @@ def run_moe(args, rank: int, world: int, device):
     pinned_l, pinned_x = logits.pin_memory(), x.pin_memory()
     pinned_y = torch.empty((t_local, hidden), dtype=torch.float32).pin_memory()
 
+    pipelined = None
+    if world == 1 and args.moe_e2e_pieces > 1:
+        from intent_b200.moe import HostPipelinedFFN
+
+        # host tensors in, host result out: pieces of the batch upload, run and download on three streams
+        pipelined = HostPipelinedFFN(tokens=tokens, hidden=hidden, intermediate=inter, experts=experts,
+                                     chunks=args.moe_e2e_pieces, block_size=args.moe_block,
+                                     target=ib.B200Target(device.index)).bind(*weights)
+
     def e2e_step():
+        if pipelined is not None:
+            pipelined.run(pinned_l, pinned_x, pinned_y)
+            return
         if world > 1 and args.moe_exchange == "peer":
             y = forward(pinned_l, pinned_x)
         else:
@@ -1376,6 +1388,9 @@ def main() -> int:
     parser.add_argument("--attach", default="all",
                         help="'all', 'none' or a comma list of decode,decode_m4,decode_m8,w8a8,moe: the other "
                              "configurations measured in the same run and attached to the prefill line")
+    parser.add_argument("--moe-e2e-pieces", type=int, default=8,
+                        help="MoE end-to-end path on one GPU: pieces of the token batch whose upload, FFN and "
+                             "download overlap (intent_b200.moe.HostPipelinedFFN); 1 = the whole batch at once")
     parser.add_argument("--e2e-chunks", type=int, default=8,
                         help="pieces per rank of the pipelined end-to-end path of the dense programs")
     parser.add_argument("--moe-block", type=int, default=128, choices=[128, 256],

@@ -333,3 +333,82 @@ class PreparedFFN:
         (self.combine_call if accumulate else self.overwrite_call).launch()   # overwrite: y is not read or cleared
         mark()
         return self.y
+
+
+class HostPipelinedFFN:
+    """The MoE FFN for inputs and results that live in (pinned) host memory: the tokens are cut into ``chunks``
+    pieces and, for every piece, the upload of its rows and logits, the routed FFN and the download of its f32
+    result run on three streams, so that the copies of neighbouring pieces overlap the contractions.  Tokens are
+    independent of one another in this FFN (every row meets its experts' weights alone), so every piece gives the
+    bits the whole batch gives.
+
+    ``run(logits, x, out)`` takes host tensors ``logits [T, E] f32``, ``x [T, H]`` and ``out [T, H] f32`` (pinned
+    for the copies to be asynchronous) and returns after the last piece has arrived in ``out``."""
+
+    def __init__(self, *, tokens, hidden, intermediate, experts, chunks=4, top_k=2, group_size=128, zero_point=8,
+                 act_dtype="bf16", block_size=128, target: B200Target | None = None):
+        import torch
+
+        if chunks < 1 or tokens % chunks:
+            raise ValueError("the token count must be a multiple of the number of pieces")
+        self.tokens, self.chunks, self.piece = tokens, chunks, tokens // chunks
+        self.hidden, self.experts = hidden, experts
+        self.ffn = MoEW4A16FFN(tokens=self.piece, hidden=hidden, intermediate=intermediate, experts=experts,
+                               top_k=top_k, group_size=group_size, zero_point=zero_point, act_dtype=act_dtype,
+                               block_size=block_size, target=target)
+        self.device = torch.device("cuda", (target or B200Target()).device)
+        self._rows = torch.bfloat16 if act_dtype == "bf16" else torch.float16
+        self._bound = None
+
+    def bind(self, up_gate_packed, up_gate_scales, down_packed, down_scales):
+        """Bind the expert weights and allocate the pieces' device buffers (once)."""
+        import torch
+
+        pieces = []
+        for _ in range(self.chunks):
+            logits = torch.empty((self.piece, self.experts), dtype=torch.float32, device=self.device)
+            x = torch.empty((self.piece, self.hidden), dtype=self._rows, device=self.device)
+            y = torch.empty((self.piece, self.hidden), dtype=torch.float32, device=self.device)
+            router = self.ffn.router.prepare(logits)
+            ids, weights = router.result()
+            chain = self.ffn.prepare(x, ids, weights, up_gate_packed, up_gate_scales, down_packed, down_scales, y)
+            pieces.append({"logits": logits, "x": x, "y": y, "router": router, "chain": chain,
+                           "uploaded": torch.cuda.Event(), "computed": torch.cuda.Event(),
+                           "downloaded": torch.cuda.Event(), "used": False})
+        self._bound = pieces
+        self._upload, self._download = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        return self
+
+    def run(self, logits, x, out):
+        import torch
+
+        if self._bound is None:
+            raise RuntimeError("bind() the expert weights first")
+        if logits.shape[0] != self.tokens or x.shape[0] != self.tokens or out.shape[0] != self.tokens:
+            raise ValueError(f"expected {self.tokens} token rows")
+        compute = torch.cuda.current_stream(self.device)
+        for index, piece in enumerate(self._bound):
+            rows = slice(index * self.piece, (index + 1) * self.piece)
+            with torch.cuda.stream(self._upload):
+                if piece["used"]:
+                    self._upload.wait_event(piece["computed"])       # the previous run no longer reads these inputs
+                piece["logits"].copy_(logits[rows], non_blocking=True)
+                piece["x"].copy_(x[rows], non_blocking=True)
+                piece["uploaded"].record(self._upload)
+            compute.wait_event(piece["uploaded"])
+            if piece["used"]:
+                compute.wait_event(piece["downloaded"])              # the previous result has left y
+            piece["router"].launch()
+            piece["chain"].launch()
+            piece["computed"].record(compute)
+            with torch.cuda.stream(self._download):
+                self._download.wait_event(piece["computed"])
+                out[rows].copy_(piece["y"], non_blocking=True)
+                piece["downloaded"].record(self._download)
+            piece["used"] = True
+        self._download.synchronize()
+        return out
+
+    def check(self) -> None:
+        for piece in self._bound or ():
+            piece["chain"].up_call.check()

@@ -206,3 +206,31 @@ def test_grouped_projection_stage_by_stage(cuda_device):
                                         group_size=128, zero_point=8)
     ref = oracle.silu_and_mul(gate_up)
     assert max_abs_rel(hidden_act[:n].float().cpu(), ref) <= 2e-2
+
+
+def test_host_pipelined_ffn_gives_the_whole_batch_bits(cuda_device):
+    """Host tensors in and out, the batch cut into pieces that upload, run and download on three streams:
+    tokens do not interact in this FFN, so the pieces give the bits the whole batch gives."""
+    from intent_b200.moe import HostPipelinedFFN
+    tokens, hidden, intermediate, experts = 512, 512, 256, 8
+    data, ids, weights = _ffn_case(tokens, hidden, intermediate, experts, torch.bfloat16, seed=5)
+    dev = {k: v.to(cuda_device) for k, v in data.items()}
+    whole = MoEW4A16FFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts,
+                        target=ib.B200Target(0))
+    got_ids, got_weights = whole.route(dev["logits"])
+    expected = whole(dev["x"], got_ids, got_weights, dev["up_gate_packed"], dev["up_gate_scales"],
+                     dev["down_packed"], dev["down_scales"]).cpu()
+    piped = HostPipelinedFFN(tokens=tokens, hidden=hidden, intermediate=intermediate, experts=experts, chunks=4,
+                             target=ib.B200Target(0)).bind(dev["up_gate_packed"], dev["up_gate_scales"],
+                                                           dev["down_packed"], dev["down_scales"])
+    logits, x = data["logits"].pin_memory(), data["x"].pin_memory()
+    out = torch.empty((tokens, hidden), dtype=torch.float32).pin_memory()
+    for _ in range(3):                       # buffers are reused from run to run
+        out.zero_()
+        piped.run(logits, x, out)
+        assert torch.equal(out, expected)
+    piped.check()
+    with pytest.raises(ValueError):
+        piped.run(logits[:100], x[:100], out[:100])
+    with pytest.raises(ValueError):
+        HostPipelinedFFN(tokens=510, hidden=hidden, intermediate=intermediate, experts=experts, chunks=4)
