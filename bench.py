@@ -562,6 +562,10 @@ def run_decode(args, rank: int, world: int, device, M: int | None = None, weight
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    # the step's results for the first weight copy (the oracle's weights), for the parity check of the CPU leg
+    step_calls[0].launch()
+    torch.cuda.synchronize()
+    line["_results"] = [y.cpu() for y in step_calls[0].results()]
     return line
 
 
@@ -1051,7 +1055,8 @@ def cpu_decode(M: int, steps: int, warmup: int, budget_s: float, inputs=None):
     import oracle
 
     cores = _cpu_threads()
-    host = decode_inputs(M)
+    # the activations of this batch size against the weights the GPU arm streams (those of decode_inputs(1))
+    host = [(x, p, s) for (x, _, _), (_, p, s) in zip(decode_inputs(M), decode_inputs(1))]
 
     def step(divisor: int):
         out = []
@@ -1066,7 +1071,8 @@ def cpu_decode(M: int, steps: int, warmup: int, budget_s: float, inputs=None):
     return {"value": decode_bytes(M) / divisor / seconds / 1e9, "unit": "GB/s", "cores": cores,
             "sample": f"{steps} steps of {what} (M={M}, both projections; the weight is dequantised inside every "
                       f"call, as in the reference's torch implementation), torch CPU, {cores} threads",
-            "ms_per_step": seconds * 1e3, "steps": steps, "fraction": 1.0 / divisor, "result": None}
+            "ms_per_step": seconds * 1e3, "steps": steps, "fraction": 1.0 / divisor,
+            "result": result if divisor == 1 else None}
 
 
 def cpu_prefill(steps: int, warmup: int, budget_s: float, inputs=None):
@@ -1187,6 +1193,10 @@ def parity_against_cpu(leg: dict, gpu_result) -> dict | None:
     reference = leg.get("result")
     if reference is None or gpu_result is None:
         return None
+    if isinstance(reference, (list, tuple)):      # several outputs per step (the decode step's projections)
+        parts = [parity_against_cpu({"result": r}, g) for r, g in zip(reference, gpu_result)]
+        worst = max(parts, key=lambda part: part["max_abs_rel"])
+        return dict(worst, outputs_compared=len(parts), ok=all(part["ok"] for part in parts))
     rows = reference.shape[0]
     got = gpu_result[:rows].float()
     scale = reference.float().abs().max().item() or 1.0
@@ -1462,7 +1472,8 @@ def main() -> int:
         return 0
     cpu_wanted = rank == 0 and world == 1 and not args.no_cpu_baseline
     if args.workload == "decode":
-        line, extra = run_decode(args, rank, world, device), {}
+        line = run_decode(args, rank, world, device)
+        extra = {"y": line.pop("_results", None)}
     else:
         runner = {"prefill": run_prefill, "w8a8": run_w8a8, "moe": run_moe, "grouped": run_grouped}[args.workload]
         line, extra = runner(args, rank, world, device)
@@ -1485,8 +1496,9 @@ def main() -> int:
             M = {"decode": 1, "decode_m4": 4, "decode_m8": 8}[name]
             if weights is None:
                 weights = DecodeWeights(device)
-            produce = (lambda M=M: (run_decode(sub_args, rank, world, device, M=M, weights=weights, steps=200,
-                                               load_seconds=0.5), {}))
+            def produce(M=M):
+                sub = run_decode(sub_args, rank, world, device, M=M, weights=weights, steps=200, load_seconds=0.5)
+                return sub, {"y": sub.pop("_results", None)}
             workload, budget = "decode", 6.0
         elif name == "w8a8":
             weights = None
