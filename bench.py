@@ -643,7 +643,7 @@ def run_prefill(args, rank: int, world: int, device):
         "e2e": {"value": round(flops / (e2e_s / e2e_steps) / 1e12, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": pipeline.h2d_bytes, "d2h_bytes_per_step": pipeline.d2h_bytes,
                 "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "steps": e2e_steps,
-                "path": f"intent_b200.distributed.ColumnShardedRows: {pipeline.chunks} pieces of {pipeline.piece} "
+                "path": f"intent_b200.distributed.ColumnShardedRows: pieces of {pipeline.sizes} "
                         "rows per rank, upload / " + ("all-gather over NVLink / " if world > 1 else "") +
                         "GEMM / download overlapped on three streams"},
         "gpu_launches": int(launches), "clocks": clocks,

@@ -50,15 +50,32 @@ class ColumnShardedRows:
       * with more than one rank every piece is all-gathered over NVLink (NCCL) into a local buffer, so each
         row crosses PCIe once on the whole node and the contraction reads local memory only;
       * the contraction of piece i runs on the compute stream while piece i+1 uploads and the result of
-        piece i-1 downloads on a third stream (PCIe is full duplex).
+        piece i-1 downloads on a third stream (PCIe is full duplex);
+      * the first and the last pieces are smaller than the rest (``taper``): the pipeline is bound by the
+        uploads, and what it adds to them is the upload of the first piece plus the contraction and the
+        download of the last one.
 
     Gathered pieces hold rows ``{r*M/world + i*piece .. }`` of every rank r; the result rows are copied back
     to exactly those rows of the pinned output.  Every buffer and prepared call is built once here; ``run``
     neither allocates nor validates.  Nothing here runs on one GPU only: no load is a multicast load.
     """
 
+    @staticmethod
+    def piece_rows(rows: int, world: int, chunks: int, taper: bool = True) -> list:
+        """Rows of every piece PER RANK.  ``chunks`` sets the size of a full piece (rows / chunks over all
+        ranks); with ``taper`` the first and the last full piece are each cut into a quarter and three quarters,
+        the quarter outermost (8192 rows, 8 chunks: 256, 768, 1024 x 6, 768, 256)."""
+        local = rows // world
+        chunks = max(1, min(chunks, local // 128 or 1))
+        while local % chunks:
+            chunks -= 1
+        piece = local // chunks
+        if not taper or chunks < 4 or piece % 4:
+            return [piece] * chunks
+        return [piece // 4, piece - piece // 4] + [piece] * (chunks - 2) + [piece - piece // 4, piece // 4]
+
     def __init__(self, artifact, resident: tuple, *, rows: int, width: int, n_local: int, in_dtype, out_dtype,
-                 device, chunks: int = 8, group=None):
+                 device, chunks: int = 8, group=None, taper: bool = True):
         import torch
         import torch.distributed as dist
 
@@ -69,21 +86,20 @@ class ColumnShardedRows:
             raise ValueError("the row count must be a multiple of the number of ranks")
         self.rows, self.width, self.n_local = rows, width, n_local
         self.local_rows = rows // self.world
-        chunks = max(1, min(chunks, self.local_rows // 128 or 1))
-        while self.local_rows % chunks:
-            chunks -= 1
-        self.chunks, self.piece = chunks, self.local_rows // chunks
+        self.sizes = self.piece_rows(rows, self.world, chunks, taper)
+        self.starts = [sum(self.sizes[:i]) for i in range(len(self.sizes))]
+        self.chunks = chunks = len(self.sizes)
         self.device = device
-        gathered = self.piece * self.world
-        self._mine = [torch.empty((self.piece, width), dtype=in_dtype, device=device) for _ in range(chunks)]
+        self._mine = [torch.empty((size, width), dtype=in_dtype, device=device) for size in self.sizes]
         self._x = (self._mine if self.world == 1 else
-                   [torch.empty((gathered, width), dtype=in_dtype, device=device) for _ in range(chunks)])
-        self._y = [torch.empty((gathered, n_local), dtype=out_dtype, device=device) for _ in range(chunks)]
+                   [torch.empty((size * self.world, width), dtype=in_dtype, device=device) for size in self.sizes])
+        self._y = [torch.empty((size * self.world, n_local), dtype=out_dtype, device=device) for size in self.sizes]
         self._calls = []
         for i, (x, y) in enumerate(zip(self._x, self._y)):
             # rows of piece i, in the order the gathered buffer holds them: rank 0's rows first
-            index = torch.cat([torch.arange(r * self.local_rows + i * self.piece,
-                                            r * self.local_rows + (i + 1) * self.piece) for r in range(self.world)])
+            index = torch.cat([torch.arange(r * self.local_rows + self.starts[i],
+                                            r * self.local_rows + self.starts[i] + self.sizes[i])
+                               for r in range(self.world)])
             operands = [o.tensor[index.to(o.tensor.device)].contiguous() if isinstance(o, RowAligned) else o
                         for o in resident]
             self._calls.append(artifact.prepare(x, *operands, outputs=(y,)))
@@ -111,11 +127,11 @@ class ColumnShardedRows:
         first_row = self.rank * self.local_rows
         self._upload.wait_stream(compute)
         for i in range(self.chunks):
-            begin = first_row + i * self.piece
+            begin, size = first_row + self.starts[i], self.sizes[i]
             with torch.cuda.stream(self._upload):
                 if not self._first:
                     self._upload.wait_event(self._used[i])
-                self._mine[i].copy_(host_x[begin:begin + self.piece], non_blocking=True)
+                self._mine[i].copy_(host_x[begin:begin + size], non_blocking=True)
                 self._uploaded[i].record(self._upload)
             compute.wait_event(self._uploaded[i])
             if self.world > 1:
@@ -128,9 +144,8 @@ class ColumnShardedRows:
             with torch.cuda.stream(self._download):
                 self._download.wait_event(self._computed[i])
                 for r in range(self.world):
-                    row = r * self.local_rows + i * self.piece
-                    host_y[row:row + self.piece].copy_(self._y[i][r * self.piece:(r + 1) * self.piece],
-                                                       non_blocking=True)
+                    row = r * self.local_rows + self.starts[i]
+                    host_y[row:row + size].copy_(self._y[i][r * size:(r + 1) * size], non_blocking=True)
                 self._released[i].record(self._download)
         compute.wait_stream(self._download)
         self._first = False

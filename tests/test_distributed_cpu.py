@@ -22,6 +22,20 @@ def test_column_shard_covers_columns_once():
         column_shard(10, 2, 2)
 
 
+def test_pipeline_piece_rows_cover_the_rows_once():
+    """Piece sizes of the host-to-host pipeline of the column-sharded programs: every rank's rows exactly once,
+    the outermost pieces a quarter of a full one."""
+    from intent_b200.distributed import ColumnShardedRows
+    assert ColumnShardedRows.piece_rows(8192, 1, 8) == [256, 768, 1024, 1024, 1024, 1024, 1024, 1024, 768, 256]
+    assert ColumnShardedRows.piece_rows(8192, 2, 8) == [128, 384, 512, 512, 512, 512, 512, 512, 384, 128]
+    assert ColumnShardedRows.piece_rows(8192, 1, 8, taper=False) == [1024] * 8
+    assert ColumnShardedRows.piece_rows(4096, 8, 8) == [32, 96, 128, 128, 96, 32]   # (256 gathered rows at the ends)
+    assert ColumnShardedRows.piece_rows(384, 1, 8) == [128] * 3                      # too few pieces to taper
+    for rows, world, chunks in [(8192, 1, 8), (8192, 4, 8), (4096, 1, 16), (1000, 1, 8), (8192, 8, 3), (384, 1, 8)]:
+        sizes = ColumnShardedRows.piece_rows(rows, world, chunks)
+        assert sum(sizes) == rows // world and min(sizes) > 0
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

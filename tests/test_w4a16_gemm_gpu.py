@@ -142,3 +142,26 @@ def test_cta_pair_kernel_equals_single_cta_kernel(cuda_device, M, K, N):
     assert torch.equal(paired, single)
     ref = oracle.weight_only_int4_matmul(x, p, s, group_size=128, zero_point=8)
     assert max_abs_rel(paired.cpu(), ref) <= 2e-2
+
+
+def test_host_pipeline_of_row_pieces_gives_the_whole_product(cuda_device):
+    """ColumnShardedRows on one GPU: rows uploaded, multiplied and downloaded in (tapered) pieces give the bits
+    of one launch over all rows (a row's sums do not depend on which rows share its tile)."""
+    from intent_b200.distributed import ColumnShardedRows
+    M, K, N = 2048, 1024, 512
+    x, p, s = ib.workloads.w4a16_inputs(M, K, N, dtype=torch.bfloat16, group_size=128, seed=4)
+    artifact = ib.compile(ib.programs.weight_only_int4_matmul, target=ib.B200Target(0),
+                          constexprs={"GROUP_SIZE": 128, "ZERO_POINT": 8, "ACT_DTYPE": "bf16"})
+    pd, sd = p.to(cuda_device), s.to(cuda_device)
+    expected = artifact.run(x.to(cuda_device), pd, sd).cpu()
+    px = x.pin_memory()
+    py = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    for taper in (True, False):
+        pipeline = ColumnShardedRows(artifact, (pd, sd), rows=M, width=K, n_local=N, in_dtype=torch.bfloat16,
+                                     out_dtype=torch.bfloat16, device=cuda_device, chunks=8, taper=taper)
+        assert sum(pipeline.sizes) == M and (len(pipeline.sizes) == 10) == taper
+        for _ in range(2):                   # buffers are reused from run to run
+            py.zero_()
+            pipeline.run(px, py)
+            torch.cuda.synchronize()
+            assert torch.equal(py, expected)
