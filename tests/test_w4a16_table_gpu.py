@@ -211,3 +211,36 @@ def test_ring_probe_entry(cuda_device):
     assert probe(matrices.data_ptr(), 3, 96, 500, 16, 0, 2, scratch.data_ptr(), stream) < 0     # cols not a multiple of 32
     assert probe(matrices.data_ptr(), 3, 96, 512, 24, 0, 2, scratch.data_ptr(), stream) < 0      # slots not a multiple of 16
     assert probe(None, 3, 96, 512, 16, 0, 2, scratch.data_ptr(), stream) < 0
+
+
+@pytest.mark.parametrize("M,dtype,group", [(1, torch.float16, 128), (3, torch.bfloat16, 64), (8, torch.float16, 32)])
+def test_many_short_segments_recycle_the_chain_sets(cuda_device, M, dtype, group):
+    """Short K and very wide N: every unit (or every second one) is a segment of its own and a CTA meets far
+    more segments per launch than its ring of chain sets holds, so the sets are reused through their generation
+    counters; ragged N and K exercise the zero-filled edges of the TMA boxes."""
+    shapes = [(M, 256, 81920), (M, 384, 70008), (M, 512, 40000), (M, 4096, 14336), (M, 640, 33000), (M, 256, 8)]
+    host, dev = _problems(shapes, dtype, group, cuda_device, seed=40)
+    table = W4A16Table(group_size=group, zero_point=8, act_dtype="f16" if dtype == torch.float16 else "bf16",
+                       target=ib.B200Target(0))
+    call = table.prepare(dev)
+    assert call.single_launch
+    _check(call, host, group, 8, dtype)
+
+
+def test_eight_step_table_matches_per_step_tables(cuda_device):
+    """Sixteen problems in one call (two launches of eight) give, problem by problem, the bits of eight
+    two-problem calls: a problem's sums do not depend on its neighbours in the table."""
+    shapes = [(1, 4096, 14336), (1, 14336, 4096)] * 8
+    host, dev = _problems(shapes, torch.float16, 128, cuda_device, seed=7)
+    table = W4A16Table(group_size=128, zero_point=8, act_dtype="f16", target=ib.B200Target(0))
+    whole = table.prepare(dev)
+    before = native.launch_count()
+    whole.launch()
+    whole.check()
+    assert native.launch_count() - before == 2
+    for step in range(8):
+        pair = table.prepare(dev[2 * step:2 * step + 2])
+        pair.launch()
+        pair.check()
+        for y, expected in zip(pair.results(), whole.results()[2 * step:2 * step + 2]):
+            assert torch.equal(y, expected)
