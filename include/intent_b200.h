@@ -180,7 +180,7 @@ INTENT_B200_API int intent_b200_w4a16_gemv_table_ride(int32_t enable);
  * ride-along kernel takes its per-group correction sums from two extra MMAs per step / adds them up from the
  * activations, -1 = built-in choice (MMAs for three rows and more); "probe" 1 = the arithmetic of every unit is skipped, 2 = the reduction too,
  * 3 = only the packed weights are loaded, 4 / 5 = arithmetic skipped and the reduction stops after the segment
- * sums / before the cross-CTA hand-over.  Every probe value but 0 gives WRONG results by design: such launches
+ * sums / before the cross-CTA hand-over, 7 = the ride-along kernel returns at once.  Every probe value but 0 gives WRONG results by design: such launches
  * only show where the time goes. */
 INTENT_B200_API int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value);
 /* Measurement only, no counterpart in the reference: the bare skeleton of the decode kernels - one CTA per SM,

@@ -626,6 +626,7 @@ w4a16_ride_kernel(const __grid_constant__ TableMaps maps, const __grid_constant_
   __shared__ int mail_tail, mail_head;         // tickets given out / entries consumed
   __shared__ int next_unit;                    // the next unit of the CTA's sequence nobody has taken yet
 
+  if (p.probe == 7) return;   // measurement: what the bare launch of this kernel costs
   if (p.overlap) asm volatile("griddepcontrol.launch_dependents;");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -1665,7 +1666,8 @@ extern "C" int intent_b200_w4a16_gemv_table_overlap(int32_t enable) {
 // the workspace size); "corr_mma" 1 / 0 = the ride-along kernel takes the correction sums from extra MMAs / adds
 // them up from the activations, -1 = built-in choice (MMAs for three rows and more);
 // "probe" 1 = every unit's arithmetic is skipped, 2 = the reduction too, 3 = only the packed weights are loaded,
-// 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over
+// 4 / 5 = arithmetic skipped and the reduction stops after the segment sums / before the cross-CTA hand-over,
+// 7 = the ride-along kernel returns at once (what its bare launch costs)
 // (the results are WRONG by design for every value but 0: these launches only show where the time goes).
 extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value) {
   if (!knob) return INTENT_B200_ERR_NULL;
@@ -1690,7 +1692,7 @@ extern "C" int intent_b200_w4a16_gemv_table_tune(const char* knob, int32_t value
     ib200::g_table_slots = value;
     return INTENT_B200_OK;
   }
-  if (is("probe") && value >= 0 && value <= 5) {
+  if (is("probe") && ((value >= 0 && value <= 5) || value == 7)) {
     ib200::g_table_probe = value;
     return INTENT_B200_OK;
   }
