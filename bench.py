@@ -16,8 +16,8 @@ shapes and value distributions of the benchmark configurations):
   w8a8     int8 GEMM 4096x8192x8192 with the scaled bf16 epilogue, columns split.
   moe      16384-token top-2 MoE FFN with int4 experts; expert parallel for N > 1
            (--moe-exchange peer: rows and results move by direct NVLink stores and loads
-           between the ranks' buffers; nccl: all-to-all; --moe-graph: the peer step as one
-           CUDA graph).
+           between the ranks' buffers, the bound step replayed as one CUDA graph unless
+           --moe-eager; nccl: all-to-all).
   grouped  the reference's published dense grouped GEMM case (8 groups x 1024 rows,
            K=4096, N=14336, f16), columns split.
 
@@ -881,7 +881,7 @@ def run_moe(args, rank: int, world: int, device):
         def prepare(lg, xx):
             call = ep.prepare(lg, xx, *weights)
             bound.update(logits=lg, x=xx, call=call, phases=call.PHASES, marked=call.launch)
-            if not args.moe_graph:
+            if args.moe_eager:
                 return call.launch
             # the step holds no collective call (flag posts and bounded flag waits over peer memory),
             # so it can be replayed as one CUDA graph
@@ -973,7 +973,7 @@ def run_moe(args, rank: int, world: int, device):
     if world > 1:
         notes["exchange"] = ("rows written into the owners' buffers and results read back over NVLink peer memory; "
                               "three sync points per step as flag posts and bounded flag waits over peer memory, no "
-                              "collective call" + (", replayed as one CUDA graph" if args.moe_graph else "")
+                              "collective call" + ("" if args.moe_eager else ", replayed as one CUDA graph")
                               if args.moe_exchange == "peer" else
                               "NCCL all-to-all each way, fixed-capacity exchange (factor 1.5)")
     split = None
@@ -1420,12 +1420,13 @@ def main() -> int:
                         help="tensor-core W4A16 kernels read a tiled copy of the weight (intent_b200.prelayout) "
                              "instead of the reference [K/8, N] layout")
     parser.add_argument("--moe-eager", action="store_true",
-                        help="1 GPU: launch the bound MoE step eagerly instead of replaying it as one CUDA graph")
+                        help="launch the bound MoE step eagerly instead of replaying it as one CUDA graph (one GPU, "
+                             "and the peer exchange form on several)")
     parser.add_argument("--moe-graph", action="store_true",
-                        help="replay the expert-parallel step (peer exchange) as one CUDA graph")
+                        help="(the default now; kept so that older command lines still parse)")
     parser.add_argument("--no-decode", action="store_true", help="same as --attach none")
     parser.add_argument("--table-tune", default="",
-                        help="measurement knobs of the table kernel, e.g. 'warps=16,areas=4' "
+                        help="measurement knobs of the table kernel, e.g. 'slots=24,corr_mma=0' "
                              "(see intent_b200_w4a16_gemv_table_tune)")
     parser.add_argument("--probe-level", type=int, default=1,
                         help="decode 'probe' mode: 1 = arithmetic skipped, 2 = reduction skipped too, 3 = only the packed "
